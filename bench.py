@@ -1,0 +1,400 @@
+#!/usr/bin/env python
+"""Benchmark of the GGUF quantized-matmul decode path on B200.
+
+One "step" is one token's worth of quantized matmuls of a Llama-3-8B-shaped Q4_K_M model at batch 1: per layer
+attn_q/k/v, attn_output, ffn_gate/up/down, times 32 layers, plus the output head: 225 GEMVs over 4.88 GB of packed
+weights (every layer has its own weights, so each step streams far more than the 126 MB L2). Attention, norms and
+sampling are not part of the path and are not run. Weights are random well-formed GGUF blocks, activations ~N(0,1) bf16.
+
+  value     tok/s with inputs resident in HBM, timed with CUDA events over K steps (CUDA-graph replay of the step)
+  e2e       the same through the host-buffer call: every step copies the token's activations from pinned host memory
+            and reads the logits back
+  roofline  the dominant kernel (Q4_K GEMV, ffn_gate/up shape) timed alone over the 64 distinct gate/up weights
+  cpu_baseline / --impl reference   the CPU oracle (a C restatement of the reference's k_quants::matmul) on the host cores
+
+Prints one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "q4_k_m_decode_matmul_tok_per_s"
+UNIT = "tok/s"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as fh:
+            d = json.load(fh)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i",
+                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([f.strip() for f in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, s[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def random_blocks_device(torch, dtype, n, k, gen):
+    """Random well-formed packed blocks on the device, padded like the reference's device buffers."""
+    nb = n * (k // dtype.block_size)
+    bb = dtype.type_size
+    pad = 512 * bb // dtype.block_size
+    buf = torch.zeros(nb * bb + pad, dtype=torch.uint8, device="cuda")
+    raw = buf[: nb * bb].view(nb, bb)
+    raw.copy_(torch.randint(0, 256, (nb, bb), dtype=torch.uint8, device="cuda", generator=gen))
+
+    def half_bytes(lo, hi):
+        v = (torch.rand(nb, device="cuda", generator=gen) * (hi - lo) + lo).to(torch.float16)
+        return v.view(torch.uint8).view(nb, 2)
+
+    if dtype.name == "Q8_0":
+        raw[:, 0:2] = half_bytes(2e-4, 6e-4)
+    elif dtype.name == "Q4K":
+        raw[:, 0:2] = half_bytes(5e-5, 2e-4)
+        raw[:, 2:4] = half_bytes(5e-5, 2e-4)
+    else:
+        raw[:, 208:210] = half_bytes(-3e-5, 3e-5)
+    return buf
+
+
+def cpu_chain_sample(model, threads, seconds_budget=12.0):
+    """Times the CPU oracle on one layer's projections plus the output head at batch 1 and scales to a token.
+    Returns (tok/s, description)."""
+    import numpy as np
+    from oracle import kquants as kq
+    type_of = {"Q8_0": kq.Q8_0, "Q4K": kq.Q4_K, "Q6K": kq.Q6_K}
+    rng = np.random.default_rng(0)
+    projs = model.layer_projections()
+    head = model.output_projection()
+    # a 1/8 slice of the head keeps the sample's memory small; its time is scaled back up
+    head_rows = head.n // 8
+
+    def blocks(p, rows):
+        t = type_of[p.dtype.name]
+        nb = rows * (p.k // kq.BLOCK_ELEMS[t])
+        raw = rng.integers(0, 256, size=(nb, kq.BLOCK_BYTES[t]), dtype=np.uint8)
+        d = rng.uniform(5e-5, 2e-4, nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+        if t == kq.Q6_K:
+            raw[:, 208:210] = d
+        else:
+            raw[:, 0:2] = d
+            if t == kq.Q4_K:
+                raw[:, 2:4] = d
+        return t, raw.reshape(rows, -1)
+
+    layer_w = [blocks(p, p.n) for p in projs]
+    head_w = blocks(head, head_rows)
+    xs = {k: rng.standard_normal((1, k)).astype(np.float32) for k in {p.k for p in projs} | {head.k}}
+
+    def one_pass():
+        t0 = time.perf_counter()
+        for p, (t, w) in zip(projs, layer_w):
+            kq.matmul(t, xs[p.k], w, p.n, threads)
+        t_layer = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        kq.matmul(head_w[0], xs[head.k], head_w[1], head_rows, threads)
+        t_head = (time.perf_counter() - t0) * (head.n / head_rows)
+        return t_layer, t_head
+
+    one_pass()
+    best_layer, best_head = float("inf"), float("inf")
+    t_start = time.perf_counter()
+    reps = 0
+    while reps < 3 or (time.perf_counter() - t_start < seconds_budget and reps < 200):
+        tl, th = one_pass()
+        best_layer, best_head = min(best_layer, tl), min(best_head, th)
+        reps += 1
+    tok_s = 1.0 / (best_layer * model.layers + best_head)
+    desc = (f"1 of {model.layers} layers (7 projections) + 1/8 of the output head at batch 1, best of {reps} passes, "
+            f"scaled to a token; scalar/auto-vectorised C port of k_quants::matmul, {threads} threads")
+    return tok_s, desc
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's CPU path (oracle port; the Rust reference cannot be built here)."""
+    if rank != 0:
+        return
+    from oracle import kquants as kq
+    from inference_rs_b200 import workloads
+    threads = kq.max_threads()
+    model = workloads.LLAMA3_8B
+    vals = []
+    desc = ""
+    t0 = time.perf_counter()
+    for _ in range(args.warmup):
+        cpu_chain_sample(model, threads, seconds_budget=0.0)
+    for _ in range(args.steps):
+        v, desc = cpu_chain_sample(model, threads, seconds_budget=max(1.0, 60.0 / max(1, args.steps)))
+        vals.append(v)
+    value = max(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "llama3-8b Q4_K_M decode matmul chain, batch 1 (225 GEMVs, 4.88 GB of weights per token)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="also time every shape of the decode sweep")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import inference_rs_b200 as pkg
+    from inference_rs_b200 import ops, workloads
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    pkg.library()
+
+    model = workloads.LLAMA3_8B
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    projs = model.layer_projections()
+    head = model.output_projection()
+    layers = [[random_blocks_device(torch, p.dtype, p.n, p.k, gen) for p in projs] for _ in range(model.layers)]
+    head_w = random_blocks_device(torch, head.dtype, head.n, head.k, gen)
+    ks = sorted({p.k for p in projs} | {head.k})
+    x_host = {k: torch.randn(1, k, generator=torch.Generator().manual_seed(k)).to(torch.bfloat16).pin_memory() for k in ks}
+    x_dev = {k: v.cuda() for k, v in x_host.items()}
+    outs = [[torch.empty(1, p.n, dtype=torch.bfloat16, device="cuda") for p in projs] for _ in range(model.layers)]
+    logits = torch.empty(1, head.n, dtype=torch.bfloat16, device="cuda")
+    logits_host = torch.empty(1, head.n, dtype=torch.bfloat16).pin_memory()
+    launches_per_step = model.layers * len(projs) + 1
+    bytes_per_step = model.weight_bytes_per_token()
+
+    def step():
+        for li in range(model.layers):
+            for p, w, o in zip(projs, layers[li], outs[li]):
+                ops.gemv(p.dtype, w, x_dev[p.k], p.n, out=o)
+        ops.gemv(head.dtype, head_w, x_dev[head.k], head.n, out=logits)
+
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        step()  # first launch sets kernel attributes; must precede capture
+        stream.synchronize()
+        graph = None
+        if not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+
+        def run_step():
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        for _ in range(args.warmup):
+            run_step()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            ev0.record(stream)
+            for _ in range(args.steps):
+                run_step()
+            ev1.record(stream)
+            barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        ms_per_step = ms / args.steps
+        tok_s = world * 1000.0 / ms_per_step  # replicas: each rank decodes its own token stream
+
+        # ---- end to end: host buffers in, logits out, every step
+        def e2e_step():
+            for k in ks:
+                x_dev[k].copy_(x_host[k], non_blocking=True)
+            run_step()
+            logits_host.copy_(logits, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            e2e_step()
+            stream.synchronize()  # the caller reads the logits before the next token
+        e1.record(stream)
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([e2e_ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        e2e_tok_s = world * 1000.0 * args.steps / e2e_ms
+        h2d = sum(v.numel() * v.element_size() for v in x_host.values())
+        d2h = logits_host.numel() * logits_host.element_size()
+
+        # ---- roofline of the dominant kernel: Q4_K GEMV at the ffn_gate / ffn_up shape over 64 distinct weights
+        gate_idx = [i for i, p in enumerate(projs) if p.name in ("ffn_gate", "ffn_up")]
+        gp = projs[gate_idx[0]]
+        dom_ws = [layers[li][i] for li in range(model.layers) for i in gate_idx]
+        dom_out = torch.empty(1, gp.n, dtype=torch.bfloat16, device="cuda")
+        for w in dom_ws[:8]:
+            ops.gemv(gp.dtype, w, x_dev[gp.k], gp.n, out=dom_out)
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        r0.record(stream)
+        for _ in range(reps):
+            for w in dom_ws:
+                ops.gemv(gp.dtype, w, x_dev[gp.k], gp.n, out=dom_out)
+        r1.record(stream)
+        barrier()
+        dom_us = r0.elapsed_time(r1) * 1000.0 / (reps * len(dom_ws))
+        dom_bytes = gp.weight_bytes + gp.k * 2 + gp.n * 2
+        peak, peak_src = load_peaks()
+        achieved = dom_bytes / (dom_us * 1e-6) / 1e9
+
+        sweep = None
+        if args.sweep:
+            sweep = []
+            for dt in (pkg.GgmlDType.Q4K, pkg.GgmlDType.Q6K, pkg.GgmlDType.Q8_0):
+                for (k, n) in workloads.SWEEP_SHAPES:
+                    wbytes = n * dt.row_bytes(k)
+                    copies = max(2, min(8, int(600e6 // wbytes) + 1))
+                    ws = [random_blocks_device(torch, dt, n, k, gen) for _ in range(copies)]
+                    for b in (1, 4):
+                        xb = torch.randn(b, k, device="cuda", generator=gen).to(torch.bfloat16)
+                        ob = torch.empty(b, n, dtype=torch.bfloat16, device="cuda")
+                        for w in ws:
+                            ops.gemv(dt, w, xb, n, out=ob)
+                        barrier()
+                        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        iters = max(3, int(2e9 // (wbytes * copies)))
+                        s0.record(stream)
+                        for _ in range(iters):
+                            for w in ws:
+                                ops.gemv(dt, w, xb, n, out=ob)
+                        s1.record(stream)
+                        barrier()
+                        us = s0.elapsed_time(s1) * 1000.0 / (iters * copies)
+                        sweep.append({"type": dt.name, "k": k, "n": n, "b": b, "us": round(us, 2),
+                                      "GBps": round((wbytes + b * k * 2 + b * n * 2) / us / 1e3, 1)})
+                    del ws
+        status = pkg.kernel_library.device_status()
+
+    line = {
+        "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot, f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": "llama3-8b Q4_K_M decode matmul chain, batch 1 (225 GEMVs, 4.88 GB of weights per token)",
+                   "l2": "inputs larger than L2: every step streams 4.88 GB of distinct weights",
+                   "parallelism": "replicas only" if world > 1 else "1 gpu", "cuda_graph": graph is not None,
+                   "pdl": ops.get_option("pdl")},
+        "weights_GBps": bytes_per_step * (tok_s / world) / 1e9,
+        "hbm_frac_of_measured": bytes_per_step * (tok_s / world) / 1e9 / peak,
+        "hbm_frac_of_nominal_8TBps": bytes_per_step * (tok_s / world) / 8e12,
+        "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "gemv_staged_kernel<Q4_K, b=1, bf16>", "shape": f"K={gp.k} N={gp.n}",
+                     "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
+                     "us_per_launch": dom_us, "algorithmic_bytes": dom_bytes, "traffic": None},
+        "clocks": clocks.summary(),
+        "device_status": list(status),
+    }
+    if sweep is not None:
+        line["sweep"] = sweep
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import kquants as kq
+        threads = kq.max_threads()
+        v, desc = cpu_chain_sample(model, threads)
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,123 @@
+/*
+ * C ABI of libinferencequant_b200.so: sm_100a kernels for the GGUF quantized-weight matmul path
+ * (Q8_0 / Q4_K / Q6_K weights in their unchanged GGUF block layout).
+ *
+ * Part 1 re-exports, with identical names and argument lists, the `extern "C"` launchers the reference
+ * resolves with dlopen from `libinferencequant[_<type>].so` (crates/inference-tensor/src/kernel_library.rs:244-393,
+ * declarations in crates/inference-quant/src/gguf/ffi.rs). All pointers are DEVICE pointers owned by the caller,
+ * `stream` is a CUstream passed as void*, every launcher is asynchronous on that stream, allocates nothing, never
+ * synchronizes and returns nothing; `int` is 32 bits.
+ *
+ * Part 2 is this library's own status-returning API: 0 = ok, > 0 = a cudaError_t, < 0 = a B200Q_ERR_* code,
+ * with a thread-local message from b200q_last_error().
+ */
+#ifndef INFERENCEQUANT_B200_H
+#define INFERENCEQUANT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Part 1: the reference's launcher symbols
+ * ------------------------------------------------------------------------------------------------------------ */
+
+/* Loader handshake: the host refuses a library whose id differs from the one compiled into it
+ * (crates/inference-tensor/src/kernel_library.rs:8,288-297). */
+extern const char inference_kernel_build_id[];
+
+/* Activation rows -> Q8_1 blocks {f16 d; f16 sum(x); i8 qs[32]} (36 bytes per 32 values), each row padded with
+ * zeros from kx to kx_padded (a multiple of 32; the reference passes pad(kx, 512)). vy holds
+ * num_rows * kx_padded / 32 blocks. d = amax / 127, q = roundf(x / d).
+ * Replaces crates/inference-quant/src/gguf/ffi.rs:602-629 (kernel: kernels/cuda/mmvq_gguf/mmvq_quantize.cu:9-146). */
+void launch_mmvq_gguf_quantize_q8_1_bf16(const void* x, void* vy, int kx, int kx_padded, int num_rows, void* stream);
+void launch_mmvq_gguf_quantize_q8_1_f16(const void* x, void* vy, int kx, int kx_padded, int num_rows, void* stream);
+void launch_mmvq_gguf_quantize_q8_1_f32(const void* x, void* vy, int kx, int kx_padded, int num_rows, void* stream);
+
+/* Decode GEMV: dst[j * stride_col_dst + row] = sum_k W[row][k] * y[j][k] for j < b_size (1..8).
+ * vx: packed weights [nrows_x][ncols_x / block] blocks, rows contiguous; vy: Q8_1 blocks, row j at block
+ * j * stride_col_y; dst element type is the name's suffix.
+ * Replaces crates/inference-quant/src/gguf/ffi.rs:846-878 (kernels/cuda/mmvq_gguf/mmvq_gguf.cuh:688-759,1762-1834).
+ * The fast path needs vx 16-byte aligned with at least 16 readable bytes after the last block (the reference's
+ * device buffers carry 512 elements' worth of padding, crates/inference-tensor/src/quantized/cuda.rs:511-530) and
+ * ncols_x a multiple of 64; other inputs take a slower kernel. */
+void launch_mmvq_gguf_q8_0_bf16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
+                                      int stride_col_y, int stride_col_dst, int b_size, void* stream);
+void launch_mmvq_gguf_q8_0_f16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
+                                     int stride_col_y, int stride_col_dst, int b_size, void* stream);
+void launch_mmvq_gguf_q8_0_f32_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
+                                     int stride_col_y, int stride_col_dst, int b_size, void* stream);
+void launch_mmvq_gguf_q4_k_bf16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
+                                      int stride_col_y, int stride_col_dst, int b_size, void* stream);
+void launch_mmvq_gguf_q4_k_f16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
+                                     int stride_col_y, int stride_col_dst, int b_size, void* stream);
+void launch_mmvq_gguf_q4_k_f32_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
+                                     int stride_col_y, int stride_col_dst, int b_size, void* stream);
+void launch_mmvq_gguf_q6_k_bf16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
+                                      int stride_col_y, int stride_col_dst, int b_size, void* stream);
+void launch_mmvq_gguf_q6_k_f16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
+                                     int stride_col_y, int stride_col_dst, int b_size, void* stream);
+void launch_mmvq_gguf_q6_k_f32_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
+                                     int stride_col_y, int stride_col_dst, int b_size, void* stream);
+
+/* Prefill activation quantizer: rows -> 144-byte blocks of 128 values, block index (k / 128) * ne1 + row.
+ * D4 stores four f32 scales, DS4 four half2 (d, sum(x)). type_x: 0 = f32, 1 = f16, 30 = bf16. ne00 = row length,
+ * s01 = row stride in elements, ne0 = padded row length (multiple of 128), ne1 = rows; only ne2 = ne3 = 1.
+ * Replaces crates/inference-quant/src/gguf/ffi.rs:657-685 (kernels/cuda/mmq_gguf/mmq_quantize.cu:98-199). */
+void launch_mmq_quantize_q8_1_D4(const void* x, const int32_t* ids, void* vy, int type_x, int64_t ne00, int64_t s01,
+                                 int64_t s02, int64_t s03, int64_t ne0, int64_t ne1, int64_t ne2, int64_t ne3,
+                                 void* stream);
+void launch_mmq_quantize_q8_1_DS4(const void* x, const int32_t* ids, void* vy, int type_x, int64_t ne00, int64_t s01,
+                                  int64_t s02, int64_t s03, int64_t ne0, int64_t ne1, int64_t ne2, int64_t ne3,
+                                  void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Part 2: status-returning API
+ * ------------------------------------------------------------------------------------------------------------ */
+
+#define B200Q_OK 0
+#define B200Q_ERR_UNSUPPORTED (-1)   /* no kernel for this shape / type / alignment */
+#define B200Q_ERR_INVALID (-2)       /* bad argument */
+#define B200Q_ERR_DEVICE_STATUS (-3) /* a kernel recorded a failure in the device status word */
+#define B200Q_ERR_TOO_LARGE (-4)     /* beyond a fixed capacity */
+
+/* GGUF type ids (crates/inference-tensor/src/quantized/mod.rs:582-624) */
+#define B200Q_TYPE_Q8_0 8
+#define B200Q_TYPE_Q4_K 12
+#define B200Q_TYPE_Q6_K 14
+/* element types */
+#define B200Q_F32 0
+#define B200Q_F16 1
+#define B200Q_BF16 2
+
+const char* b200q_version(void);
+const char* b200q_last_error(void);
+
+/* Options: "pdl" (launch GEMVs and quantizers with programmatic stream serialization), "force_simple_gemv",
+ * "gemv_stage_bytes". get also answers "sm_count" and "smem_optin". */
+int b200q_set_option(const char* name, int value);
+int b200q_get_option(const char* name, int* value);
+
+/* The device status word {first failure code, block, detail, failures}: kernels never trap or spin without
+ * bound; a wait that gives up records here and the kernel returns. Reading synchronizes the device. */
+int b200q_device_status(unsigned int out[4]);
+int b200q_reset_device_status(void);
+/* First non-zero status a void launcher of part 1 produced since the last call, then cleared. */
+int b200q_take_launch_status(void);
+
+/* One-launch decode GEMV on unquantized activations: x [b_size][stride_x] and dst [b_size][stride_dst] both of
+ * element type `elem`; activations are quantized to Q8_1 in the kernel's prologue with the same arithmetic as
+ * launch_mmvq_gguf_quantize_q8_1_*, so results equal the two-launch protocol bit for bit.
+ * Host-side counterpart in the reference: fast_mmvq::plain (crates/inference-quant/src/gguf/fast_mmvq.rs:477-665). */
+int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
+               int b_size, void* stream);
+
+/* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment} */
+int b200q_gemv_plan(int type, int K, int N, int b_size, int out[8]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INFERENCEQUANT_B200_H */

@@ -1,0 +1,103 @@
+// The status-returning half of the C ABI (include/inferencequant_b200.h): options, status words, and the
+// one-launch GEMV that quantizes activations in its prologue.
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "runtime.h"
+
+namespace b200q {
+int gemv_q4_k(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
+int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
+int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
+void gemv_describe(int type, int K, int N, int b, int* out);
+
+static thread_local char t_error[256] = "";
+int set_error(int code, const char* msg) {
+    std::snprintf(t_error, sizeof t_error, "%s", msg);
+    return code;
+}
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+// Checked by the reference's loader against the id compiled into the host
+// (crates/inference-tensor/src/kernel_library.rs:288-297). A host built for this library bakes the same string.
+extern const char inference_kernel_build_id[] = "b200q-sm100a-0.1";
+
+const char* b200q_version(void) { return "0.1.0"; }
+const char* b200q_last_error(void) { return t_error; }
+
+int b200q_set_option(const char* name, int value) {
+    RuntimeInfo& rt = runtime_info_mut();
+    if (!std::strcmp(name, "pdl")) rt.use_pdl = value;
+    else if (!std::strcmp(name, "force_simple_gemv")) rt.force_simple = value;
+    else if (!std::strcmp(name, "gemv_stage_bytes")) {
+        if (value < 1024) return set_error(B200Q_ERR_INVALID, "gemv_stage_bytes must be >= 1024");
+        rt.gemv_stage_target = value;
+    } else {
+        return set_error(B200Q_ERR_INVALID, "unknown option");
+    }
+    return B200Q_OK;
+}
+
+int b200q_get_option(const char* name, int* value) {
+    const RuntimeInfo& rt = runtime_info();
+    if (!std::strcmp(name, "pdl")) *value = rt.use_pdl;
+    else if (!std::strcmp(name, "force_simple_gemv")) *value = rt.force_simple;
+    else if (!std::strcmp(name, "gemv_stage_bytes")) *value = rt.gemv_stage_target;
+    else if (!std::strcmp(name, "sm_count")) *value = rt.sm_count;
+    else if (!std::strcmp(name, "smem_optin")) *value = rt.smem_optin;
+    else return set_error(B200Q_ERR_INVALID, "unknown option");
+    return B200Q_OK;
+}
+
+// Copies the device status word {code, block, detail, count} of the current device to `out` (synchronizes the device).
+int b200q_device_status(unsigned int out[4]) {
+    unsigned int* p = status_ptr();
+    if (!p) return set_error(B200Q_ERR_INVALID, "no CUDA device");
+    cudaError_t e = cudaMemcpy(out, p, 4 * sizeof(unsigned int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return set_error((int)e, cudaGetErrorString(e));
+    return B200Q_OK;
+}
+
+int b200q_reset_device_status(void) {
+    unsigned int* p = status_ptr();
+    if (!p) return set_error(B200Q_ERR_INVALID, "no CUDA device");
+    cudaError_t e = cudaMemset(p, 0, 4 * sizeof(unsigned int));
+    if (e != cudaSuccess) return set_error((int)e, cudaGetErrorString(e));
+    return B200Q_OK;
+}
+
+// First non-zero status a void launcher produced since the last call (then cleared).
+int b200q_take_launch_status(void) { return take_launch_status(); }
+
+int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
+               int b_size, void* stream) {
+    if (!w || !x || !dst) return set_error(B200Q_ERR_INVALID, "null pointer");
+    if (b_size < 1 || b_size > 8) return set_error(B200Q_ERR_UNSUPPORTED, "b200q_gemv takes 1..8 activation rows");
+    if (K <= 0 || K % type_block_elems(type) != 0) return set_error(B200Q_ERR_INVALID, "K is not a multiple of the block size");
+    int rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (type == TYPE_Q4_K) rc = gemv_q4_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, 1, s);
+    else if (type == TYPE_Q6_K) rc = gemv_q6_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, 1, s);
+    else if (type == TYPE_Q8_0) rc = gemv_q8_0(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, 1, s);
+    else return set_error(B200Q_ERR_UNSUPPORTED, "weight type is not Q8_0, Q4_K or Q6_K");
+    take_launch_status();
+    if (rc == B200Q_ERR_UNSUPPORTED)
+        return set_error(rc, "no one-launch GEMV for this shape or alignment: quantize to Q8_1 and use launch_mmvq_gguf_*_plain");
+    if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemv failed");
+    return B200Q_OK;
+}
+
+// out[8] = {staged, grid, smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment}
+int b200q_gemv_plan(int type, int K, int N, int b_size, int out[8]) {
+    if (type_block_bytes(type) == 0 || K <= 0 || K % type_block_elems(type) != 0 || b_size < 1 || b_size > 8)
+        return set_error(B200Q_ERR_INVALID, "bad shape");
+    gemv_describe(type, K, N, b_size, out);
+    return B200Q_OK;
+}
+
+}  // extern "C"

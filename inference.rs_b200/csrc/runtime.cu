@@ -1,0 +1,65 @@
+// Host-side state shared by the launchers (see runtime.h).
+#include "runtime.h"
+
+#include <atomic>
+#include <cstdlib>
+
+namespace b200q {
+
+__device__ unsigned int g_status_word[4] = {0, 0, 0, 0};
+
+static RuntimeInfo g_rt = {0, 0, 0, 0, 0, 24 * 1024};
+static std::atomic<int> g_launch_status{0};
+
+static void query_device() {
+    int dev = 0;
+    int sm = 0, optin = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) {
+        cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+    } else {
+        cudaGetLastError();
+    }
+    // B200 values when no device can be asked (planning on a CPU-only host)
+    g_rt.sm_count = sm > 0 ? sm : 148;
+    g_rt.smem_optin = optin > 0 ? optin : 227 * 1024;
+    g_rt.smem_per_sm = per_sm > 0 ? per_sm : 228 * 1024;
+    if (const char* e = std::getenv("B200Q_PDL")) g_rt.use_pdl = std::atoi(e);
+    if (const char* e = std::getenv("B200Q_GEMV_STAGE_BYTES")) {
+        int v = std::atoi(e);
+        if (v >= 1024) g_rt.gemv_stage_target = v;
+    }
+}
+
+RuntimeInfo& runtime_info_mut() {
+    if (g_rt.sm_count == 0) query_device();
+    return g_rt;
+}
+const RuntimeInfo& runtime_info() { return runtime_info_mut(); }
+
+unsigned int* status_ptr() {
+    static unsigned int* cached[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        cached[dev] = static_cast<unsigned int*>(p);
+    }
+    return cached[dev];
+}
+
+int note_launch_status(int status) {
+    if (status != 0) {
+        int expected = 0;
+        g_launch_status.compare_exchange_strong(expected, status);
+    }
+    return status;
+}
+int take_launch_status() { return g_launch_status.exchange(0); }
+
+}  // namespace b200q

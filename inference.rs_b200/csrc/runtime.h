@@ -1,0 +1,31 @@
+// Host-side state shared by the launchers: device properties, tuning knobs, and the last launch status.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace b200q {
+
+// status codes of the b200q_* API (0 = ok, > 0 = a cudaError_t, < 0 = one of these)
+enum : int {
+    B200Q_OK = 0,
+    B200Q_ERR_UNSUPPORTED = -1,   // shape / type / alignment this library has no kernel for
+    B200Q_ERR_INVALID = -2,       // bad argument
+    B200Q_ERR_DEVICE_STATUS = -3, // a kernel recorded a failure in the device status word
+    B200Q_ERR_TOO_LARGE = -4,     // beyond a fixed capacity
+};
+
+struct RuntimeInfo {
+    int sm_count;
+    int smem_optin;        // max dynamic shared memory per CTA
+    int smem_per_sm;       // shared memory per SM
+    int use_pdl;           // launch with programmatic stream serialization
+    int force_simple;      // route every GEMV to the simple kernel (testing)
+    int gemv_stage_target; // bytes per shared-memory stage the GEMV planner aims at
+};
+
+const RuntimeInfo& runtime_info();
+RuntimeInfo& runtime_info_mut();
+unsigned int* status_ptr();          // device address of the status word of the current device (cached)
+int note_launch_status(int status);  // remembers the first non-zero status; returns its argument
+int take_launch_status();            // returns and clears it
+
+}  // namespace b200q

@@ -1,0 +1,109 @@
+"""torch-tensor front end of the C ABI: device memory and streams come from torch, the arithmetic from the library.
+
+Every function launches on torch's current CUDA stream and raises if the kernel library is unavailable.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import kernel_library as kl
+from .dtypes import (ELEM_BF16, ELEM_F16, ELEM_F32, ELEM_TAG, MATRIX_ROW_PADDING, MMQ_TYPE_X, GgmlDType, pad)
+
+_ELEM_OF = {torch.float32: ELEM_F32, torch.float16: ELEM_F16, torch.bfloat16: ELEM_BF16}
+
+
+def elem_of(dtype: torch.dtype) -> int:
+    try:
+        return _ELEM_OF[dtype]
+    except KeyError:
+        raise TypeError(f"activations must be f32, f16 or bf16, not {dtype}") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("expected a CUDA tensor")
+        if not t.is_contiguous():
+            raise ValueError("expected a contiguous tensor")
+
+
+def upload_weights(packed: np.ndarray | torch.Tensor, dtype: GgmlDType, device="cuda") -> torch.Tensor:
+    """Packed GGUF blocks -> device buffer followed by 512 elements' worth of zero bytes, as the reference's
+    `load_quantized` does (crates/inference-tensor/src/quantized/cuda.rs:511-530)."""
+    if isinstance(packed, np.ndarray):
+        packed = torch.from_numpy(np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1))
+    packed = packed.reshape(-1)
+    padding = MATRIX_ROW_PADDING * dtype.type_size // dtype.block_size
+    buf = torch.zeros(packed.numel() + padding, dtype=torch.uint8, device=device)
+    buf[: packed.numel()].copy_(packed)
+    return buf
+
+
+def quantize_q8_1(x: torch.Tensor, k_padded: int | None = None) -> torch.Tensor:
+    """`launch_mmvq_gguf_quantize_q8_1_<dtype>`: x [rows, k] -> uint8 [rows, k_padded / 32 * 36]."""
+    _require_cuda(x)
+    rows, k = x.shape
+    k_padded = pad(k, MATRIX_ROW_PADDING) if k_padded is None else k_padded
+    out = torch.empty((rows, k_padded // 32 * 36), dtype=torch.uint8, device=x.device)
+    fn = getattr(kl.library(), f"launch_mmvq_gguf_quantize_q8_1_{ELEM_TAG[elem_of(x.dtype)]}")
+    fn(x.data_ptr(), out.data_ptr(), k, k_padded, rows, _stream())
+    return out
+
+
+def quantize_mmq_q8_1(x: torch.Tensor, layout: str, k_padded: int | None = None) -> torch.Tensor:
+    """`launch_mmq_quantize_q8_1_{D4,DS4}`: x [rows, k] -> uint8 [k_padded / 128, rows, 144]."""
+    _require_cuda(x)
+    rows, k = x.shape
+    k_padded = pad(pad(k, MATRIX_ROW_PADDING), 128) if k_padded is None else k_padded
+    out = torch.empty((k_padded // 128, rows, 144), dtype=torch.uint8, device=x.device)
+    fn = getattr(kl.library(), f"launch_mmq_quantize_q8_1_{layout}")
+    fn(x.data_ptr(), None, out.data_ptr(), MMQ_TYPE_X[elem_of(x.dtype)], k, k, 0, 0, k_padded, rows, 1, 1, _stream())
+    return out
+
+
+def mmvq_plain(dtype: GgmlDType, w: torch.Tensor, vy: torch.Tensor, n: int, k: int, b: int,
+               out_dtype: torch.dtype, k_padded: int | None = None) -> torch.Tensor:
+    """`launch_mmvq_gguf_<type>_<out>_plain` on Q8_1 blocks `vy`; returns [b, n]."""
+    _require_cuda(w, vy)
+    k_padded = pad(k, MATRIX_ROW_PADDING) if k_padded is None else k_padded
+    dst = torch.empty((b, n), dtype=out_dtype, device=w.device)
+    fn = getattr(kl.library(), f"launch_mmvq_gguf_{dtype.tag}_{ELEM_TAG[elem_of(out_dtype)]}_plain")
+    fn(w.data_ptr(), vy.data_ptr(), dst.data_ptr(), k, n, k_padded // 32, n, b, _stream())
+    rc = kl.library().b200q_take_launch_status()
+    if rc:
+        raise kl.KernelLibraryError(f"launch_mmvq_gguf_{dtype.tag}_*_plain failed with status {rc}")
+    return dst
+
+
+def gemv(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """`b200q_gemv`: one launch, activations quantized in the kernel's prologue. x [b, k] -> [b, n] of x's dtype."""
+    _require_cuda(w, x)
+    b, k = x.shape
+    dst = torch.empty((b, n), dtype=x.dtype, device=x.device) if out is None else out
+    kl.check(kl.library().b200q_gemv(int(dtype), elem_of(x.dtype), w.data_ptr(), x.data_ptr(), dst.data_ptr(), k, n,
+                                     x.stride(0), dst.stride(0), b, _stream()), "b200q_gemv")
+    return dst
+
+
+def gemv_plan(dtype: GgmlDType, k: int, n: int, b: int) -> dict:
+    out = (C.c_int * 8)()
+    kl.check(kl.library().b200q_gemv_plan(int(dtype), k, n, b, C.byref(out)), "b200q_gemv_plan")
+    keys = ("staged", "grid", "smem", "stages", "rows_per_stage", "warps_per_row", "stage_bytes", "row_align")
+    return dict(zip(keys, (int(v) for v in out)))
+
+
+def set_option(name: str, value: int) -> None:
+    kl.check(kl.library().b200q_set_option(name.encode(), int(value)), f"b200q_set_option({name})")
+
+
+def get_option(name: str) -> int:
+    v = C.c_int()
+    kl.check(kl.library().b200q_get_option(name.encode(), C.byref(v)), f"b200q_get_option({name})")
+    return int(v.value)

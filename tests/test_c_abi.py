@@ -1,0 +1,74 @@
+"""The C-ABI library loads and exports every symbol include/inferencequant_b200.h declares (no compute here)."""
+import os
+import re
+
+import pytest
+
+import inference_rs_b200 as pkg
+from inference_rs_b200 import kernel_library as kl
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "inferencequant_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = set(re.findall(r"\b((?:launch|b200q)_[A-Za-z0-9_]+)\s*\(", text))
+    names |= set(re.findall(r"extern const char (\w+)\[\]", text))
+    return names
+
+
+def test_header_and_loader_agree():
+    declared = _declared_symbols()
+    assert declared, "no declarations parsed"
+    known = set(kl.SYMBOLS) | set(kl.DATA_SYMBOLS)
+    assert declared == known, (sorted(declared - known), sorted(known - declared))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = pkg.library()  # raises if any symbol is missing
+    for name in _declared_symbols():
+        if name in kl.DATA_SYMBOLS:
+            continue
+        assert getattr(lib, name) is not None
+    assert kl.build_id().startswith("b200q-sm100a")
+    assert lib.b200q_version().decode().count(".") == 2
+
+
+def test_missing_library_is_an_error_not_a_fallback(monkeypatch, tmp_path):
+    monkeypatch.setattr(kl, "_lib", None)
+    monkeypatch.setattr(kl, "HERE", str(tmp_path))
+    monkeypatch.delenv("INFERENCE_KERNEL_DIR", raising=False)
+    with pytest.raises(kl.KernelLibraryError, match="no CPU fallback"):
+        kl.library()
+
+
+def test_kernel_dir_env_takes_precedence(monkeypatch, tmp_path):
+    monkeypatch.setenv("INFERENCE_KERNEL_DIR", str(tmp_path))
+    assert kl.search_paths()[0] == os.path.join(str(tmp_path), "sm100a", kl.LIB_NAME)
+
+
+def test_options_and_errors_round_trip():
+    from inference_rs_b200 import ops
+    ops.set_option("pdl", 0)
+    assert ops.get_option("pdl") == 0
+    with pytest.raises(kl.KernelLibraryError, match="unknown option"):
+        ops.set_option("no_such_option", 1)
+    assert ops.get_option("sm_count") > 0
+
+
+@pytest.mark.parametrize("tag,k,n,b", [("Q4K", 4096, 4096, 1), ("Q6K", 14336, 4096, 4), ("Q8_0", 4096, 128256, 8),
+                                       ("Q6K", 768, 100, 1), ("Q4K", 28672, 8192, 1)])
+def test_gemv_plans_respect_hardware_limits(tag, k, n, b):
+    from inference_rs_b200 import ops
+    dt = pkg.GgmlDType[tag]
+    plan = ops.gemv_plan(dt, k, n, b)
+    if not plan["staged"]:
+        return
+    assert plan["smem"] <= 227 * 1024
+    assert 2 <= plan["stages"] <= 8
+    assert plan["rows_per_stage"] % plan["row_align"] == 0
+    assert (plan["rows_per_stage"] * plan["warps_per_row"]) % 8 == 0 or plan["warps_per_row"] == 1
+    assert plan["stage_bytes"] >= plan["rows_per_stage"] * dt.row_bytes(k) + 16
+    assert (plan["row_align"] * dt.row_bytes(k)) % 16 == 0
+    assert 1 <= plan["grid"] <= 148 * 2

@@ -1,0 +1,157 @@
+"""GPU parity of the decode GEMV, through the C ABI, against the CPU oracle.
+
+Two comparisons per case:
+  * against the kernels' own arithmetic on the same Q8_1 blocks, accumulated in double: only f32 rounding and
+    summation order may differ, so the bound is tight (2e-5 of the largest output, plus output rounding);
+  * against the reference CPU path (Q8_K / Q8_0 activations, integer vec_dot): 1e-2 relative / 1e-3 absolute, stated
+    as max|d| <= 1e-3 + 1e-2 max|ref| (the form the reference's own GPU tests use,
+    crates/inference-quant/src/gguf/mod.rs:998-1037); the element-wise pass rate is reported too.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import kquants as kq
+
+from inference_rs_b200 import ops
+from gpu_util import (DT, TORCH_DTYPES, TYPES, as_f32_numpy, assert_device_ok, elementwise_pass_rate, random_packed,
+                      seeded_acts, seeded_weights)
+
+pytestmark = pytest.mark.gpu
+
+OUT_EPS = {"f32": 0.0, "f16": 2.0 ** -11, "bf16": 2.0 ** -8}
+
+
+def run_case(type_id, n, k, b, dtype, packed=None, simple=False, seed=0):
+    tdt = TORCH_DTYPES[dtype]
+    if packed is None:
+        packed = kq.quantize(type_id, seeded_weights(n, k, 1000 + seed))
+    x = seeded_acts(b, k, 2000 + seed, tdt)
+    w_dev = ops.upload_weights(packed, DT[type_id])
+    x_dev = x.cuda()
+    ops.set_option("force_simple_gemv", 1 if simple else 0)
+    try:
+        vy = ops.quantize_q8_1(x_dev)
+        got2 = ops.mmvq_plain(DT[type_id], w_dev, vy, n, k, b, tdt)
+        got1 = None if simple else ops.gemv(DT[type_id], w_dev, x_dev, n)
+    finally:
+        ops.set_option("force_simple_gemv", 0)
+    torch.cuda.synchronize()
+    xf = as_f32_numpy(x)
+    k_padded = (k + 511) // 512 * 512
+    acts = kq.quantize_q8_1_mmvq(xf, k_padded)
+    assert np.array_equal(vy.cpu().numpy(), acts)
+    same_math = kq.matmul_q8_1(type_id, acts, b, k, k_padded, packed, n)
+    cpu_path = kq.matmul(type_id, xf, packed, n)
+    g2 = as_f32_numpy(got2).astype(np.float64)
+    scale = np.abs(same_math).max() + 1e-30
+    tight = 2e-5 * scale + OUT_EPS[dtype] * np.abs(same_math) * 1.01
+    bad = np.abs(g2 - same_math) > tight + 1e-30
+    assert not bad.any(), (f"{kq.TYPE_NAMES[type_id]} n={n} k={k} b={b} {dtype}: {bad.sum()} outputs off, worst "
+                           f"{np.abs(g2 - same_math).max():.3e} vs scale {scale:.3e}; first at {np.argwhere(bad)[:4].tolist()}")
+    err = np.abs(g2 - cpu_path).max()
+    assert err <= 1e-3 + 1e-2 * np.abs(cpu_path).max(), f"vs reference CPU path: {err}"
+    if got1 is not None:
+        assert torch.equal(got1, got2), "one-launch GEMV differs from quantize + GEMV"
+    assert_device_ok()
+    return elementwise_pass_rate(g2, cpu_path)
+
+
+@pytest.mark.parametrize("type_id", TYPES)
+@pytest.mark.parametrize("b", [1, 2, 3, 4, 5, 8])
+def test_small_shapes_all_batches(type_id, b):
+    for n, k in [(48, 512), (130, 1024), (7, 256), (1, 768), (1000, 768)]:
+        if k % 64:
+            continue
+        run_case(type_id, n, k, b, "f32", seed=b)
+
+
+@pytest.mark.parametrize("type_id", TYPES)
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_output_types(type_id, dtype):
+    run_case(type_id, 300, 2048, 2, dtype)
+
+
+@pytest.mark.parametrize("type_id", TYPES)
+def test_simple_kernel_matches_too(type_id):
+    run_case(type_id, 333, 1024, 3, "f32", simple=True)
+    run_case(type_id, 48, 512, 1, "bf16", simple=True)
+
+
+def test_k_not_multiple_of_64_takes_the_simple_kernel():
+    # K = 96 (Q8_0 only: 32-value blocks) is not a multiple of 64, so the staged kernel declines; the two-launch
+    # path must still be right
+    type_id = kq.Q8_0
+    packed = kq.quantize(type_id, seeded_weights(100, 96, 5))
+    x = seeded_acts(2, 96, 6, torch.float32)
+    w_dev = ops.upload_weights(packed, DT[type_id])
+    vy = ops.quantize_q8_1(x.cuda())
+    got = ops.mmvq_plain(DT[type_id], w_dev, vy, 100, 96, 2, torch.float32)
+    ref = kq.matmul_q8_1(type_id, vy.cpu().numpy(), 2, 96, 512, packed, 100)
+    np.testing.assert_allclose(as_f32_numpy(got), ref, rtol=0, atol=2e-5 * np.abs(ref).max())
+
+
+def test_config1_q4k_4096_by_the_oracle_quantizer():
+    """BASELINE config 1: f32 weight 4096x4096 ~N(0,0.02) seed 0 -> Q4_K; f32 activations ~N(0,1) 1x4096 and 16x4096."""
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(4096, 4096, generator=g) * 0.02).numpy()
+    packed = kq.quantize(kq.Q4_K, w)
+    rate1 = run_case(kq.Q4_K, 4096, 4096, 1, "f32", packed=packed, seed=1)
+    # 16 rows go through the GEMV two batches of 8 at the C ABI
+    rate8 = run_case(kq.Q4_K, 4096, 4096, 8, "f32", packed=packed, seed=2)
+    print(f"element-wise 1e-2/1e-3 pass rate vs CPU path: b=1 {rate1:.4f}, b=8 {rate8:.4f}")
+
+
+SWEEP = [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096), (4096, 128256)]
+
+
+@pytest.mark.parametrize("type_id", TYPES)
+@pytest.mark.parametrize("k,n", SWEEP)
+def test_decode_sweep_shapes(type_id, k, n):
+    """BASELINE config 2 shapes at batch 1 and 4, bf16, on random well-formed blocks."""
+    packed = random_packed(type_id, n, k, seed=n + k)
+    run_case(type_id, n, k, 1, "bf16", packed=packed, seed=7)
+    run_case(type_id, n, k, 4, "bf16", packed=packed, seed=8)
+
+
+@pytest.mark.parametrize("type_id", TYPES)
+def test_batch_rows_are_independent(type_id):
+    """Size-independent property: row j of a batch equals the same row run alone, bit for bit."""
+    n, k = 4096, 4096
+    packed = random_packed(type_id, n, k, seed=42)
+    w_dev = ops.upload_weights(packed, DT[type_id])
+    x = seeded_acts(8, k, 9, torch.bfloat16).cuda()
+    full = ops.gemv(DT[type_id], w_dev, x, n)
+    for j in (0, 3, 7):
+        alone = ops.gemv(DT[type_id], w_dev, x[j:j + 1].contiguous(), n)
+        assert torch.equal(alone[0], full[j])
+    # and the result does not depend on how rows are staged
+    ops.set_option("gemv_stage_bytes", 8 * 1024)
+    try:
+        other = ops.gemv(DT[type_id], w_dev, x, n)
+    finally:
+        ops.set_option("gemv_stage_bytes", 24 * 1024)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(as_f32_numpy(other), as_f32_numpy(full), rtol=2 ** -7, atol=1e-3)
+    assert_device_ok()
+
+
+def test_zero_activations_and_zero_weights():
+    n, k = 64, 512
+    for type_id in TYPES:
+        packed = kq.quantize(type_id, np.zeros((n, k), np.float32))
+        w_dev = ops.upload_weights(packed, DT[type_id])
+        x = seeded_acts(2, k, 1, torch.float32).cuda()
+        assert not ops.gemv(DT[type_id], w_dev, x, n).any()
+        packed = kq.quantize(type_id, seeded_weights(n, k, 1))
+        w_dev = ops.upload_weights(packed, DT[type_id])
+        assert not ops.gemv(DT[type_id], w_dev, torch.zeros_like(x), n).any()
+    assert_device_ok()
+
+
+def test_unsupported_batch_is_refused():
+    from inference_rs_b200 import kernel_library as kl
+    w_dev = ops.upload_weights(random_packed(kq.Q4_K, 8, 256, 1), DT[kq.Q4_K])
+    x = torch.zeros(9, 256, device="cuda")
+    with pytest.raises(kl.KernelLibraryError, match="1..8"):
+        ops.gemv(DT[kq.Q4_K], w_dev, x, 8)
