@@ -112,6 +112,78 @@ def random_blocks_device(torch, dtype, n, k, gen):
     return buf
 
 
+def time_launch_list(torch, stream, launches, reps):
+    """Captures the launches (callables on the current stream) into one CUDA graph, replays it `reps` times and
+    returns the mean device time of one launch in microseconds (CUDA events on `stream`)."""
+    for fn in launches:
+        fn()  # eager once: first-launch attribute set-up may not run under capture
+    stream.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        for fn in launches:
+            fn()
+    g.replay()
+    stream.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        g.replay()
+    e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) * 1000.0 / (reps * len(launches))
+
+
+def run_single(args):
+    """--single TYPE K N B: one GEMV shape over rotating weight copies (> L2 in total); prints one JSON line. This is
+    the small case profiler captures run on."""
+    import torch
+
+    import inference_rs_b200 as pkg
+    from inference_rs_b200 import ops
+
+    tname, k, n, b = args.single[0], int(args.single[1]), int(args.single[2]), int(args.single[3])
+    dt = {"q4_k": pkg.GgmlDType.Q4K, "q6_k": pkg.GgmlDType.Q6K, "q8_0": pkg.GgmlDType.Q8_0}[tname]
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    wbytes = n * dt.row_bytes(k)
+    copies = args.copies or max(2, min(64, int(400e6 // wbytes) + 1))
+    ws = [random_blocks_device(torch, dt, n, k, gen) for _ in range(copies)]
+    x = torch.randn(b, k, device="cuda", generator=gen).to(torch.bfloat16)
+    out = torch.empty(b, n, dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        if args.two_launch:
+            def mk(w):
+                def fn():
+                    vy = ops.quantize_q8_1(x)
+                    ops.mmvq_plain(dt, w, vy, n, k, b, torch.bfloat16)
+                return fn
+        else:
+            def mk(w):
+                return lambda: ops.gemv(dt, w, x, n, out=out)
+        launches = [mk(w) for w in ws]
+        if args.no_graph:
+            for fn in launches:
+                fn()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                for fn in launches:
+                    fn()
+            e1.record(stream)
+            stream.synchronize()
+            us = e0.elapsed_time(e1) * 1000.0 / (args.steps * len(launches))
+        else:
+            us = time_launch_list(torch, stream, launches, args.steps)
+    peak, src = load_peaks()
+    alg = wbytes + b * k * 2 + b * n * 2
+    print(json.dumps({"single": tname, "k": k, "n": n, "b": b, "copies": copies, "us_per_launch": us,
+                      "GBps": alg / us / 1e3, "frac_of_" + src: alg / us / 1e3 / peak, "algorithmic_bytes": alg,
+                      "plan": ops.gemv_plan(dt, k, n, b), "device_status": list(pkg.kernel_library.device_status())}),
+          flush=True)
+
+
 def cpu_chain_sample(model, threads, seconds_budget=12.0):
     """Times the CPU oracle on one layer's projections plus the output head at batch 1 and scales to a token.
     Returns (tok/s, description)."""
@@ -197,12 +269,16 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time every shape of the decode sweep")
+    ap.add_argument("--single", nargs=4, metavar=("TYPE", "K", "N", "B"), help="time one GEMV shape only (q4_k|q6_k|q8_0)")
+    ap.add_argument("--copies", type=int, default=0, help="--single: number of rotating weight copies")
+    ap.add_argument("--two-launch", action="store_true", help="--single: quantize launcher + GEMV launcher instead of one launch")
+    ap.add_argument("--pdl", type=int, default=None, help="programmatic dependent launch on/off")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -212,6 +288,12 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.pdl is not None:
+        from inference_rs_b200 import ops as _ops
+        _ops.set_option("pdl", args.pdl)
+    if args.single:
+        run_single(args)
         return
 
     import torch
@@ -271,16 +353,17 @@ def main():
                 dist.barrier()
             torch.cuda.synchronize()
 
+        clocks = ClockSampler(local_rank)
+        clocks.__enter__()
         for _ in range(args.warmup):
             run_step()
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clocks:
-            ev0.record(stream)
-            for _ in range(args.steps):
-                run_step()
-            ev1.record(stream)
-            barrier()
+        ev0.record(stream)
+        for _ in range(args.steps):
+            run_step()
+        ev1.record(stream)
+        barrier()
         ms = ev0.elapsed_time(ev1)
         if world > 1:
             t = torch.tensor([ms], device="cuda")
@@ -320,21 +403,12 @@ def main():
         gp = projs[gate_idx[0]]
         dom_ws = [layers[li][i] for li in range(model.layers) for i in gate_idx]
         dom_out = torch.empty(1, gp.n, dtype=torch.bfloat16, device="cuda")
-        for w in dom_ws[:8]:
-            ops.gemv(gp.dtype, w, x_dev[gp.k], gp.n, out=dom_out)
-        barrier()
-        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 3
-        r0.record(stream)
-        for _ in range(reps):
-            for w in dom_ws:
-                ops.gemv(gp.dtype, w, x_dev[gp.k], gp.n, out=dom_out)
-        r1.record(stream)
-        barrier()
-        dom_us = r0.elapsed_time(r1) * 1000.0 / (reps * len(dom_ws))
+        dom_us = time_launch_list(torch, stream, [(lambda w=w: ops.gemv(gp.dtype, w, x_dev[gp.k], gp.n, out=dom_out))
+                                                  for w in dom_ws], 10)
         dom_bytes = gp.weight_bytes + gp.k * 2 + gp.n * 2
         peak, peak_src = load_peaks()
         achieved = dom_bytes / (dom_us * 1e-6) / 1e9
+        clocks.__exit__(None, None, None)
 
         sweep = None
         if args.sweep:
@@ -344,21 +418,11 @@ def main():
                     wbytes = n * dt.row_bytes(k)
                     copies = max(2, min(8, int(600e6 // wbytes) + 1))
                     ws = [random_blocks_device(torch, dt, n, k, gen) for _ in range(copies)]
-                    for b in (1, 4):
+                    for b in (1, 4, 8):
                         xb = torch.randn(b, k, device="cuda", generator=gen).to(torch.bfloat16)
                         ob = torch.empty(b, n, dtype=torch.bfloat16, device="cuda")
-                        for w in ws:
-                            ops.gemv(dt, w, xb, n, out=ob)
-                        barrier()
-                        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        iters = max(3, int(2e9 // (wbytes * copies)))
-                        s0.record(stream)
-                        for _ in range(iters):
-                            for w in ws:
-                                ops.gemv(dt, w, xb, n, out=ob)
-                        s1.record(stream)
-                        barrier()
-                        us = s0.elapsed_time(s1) * 1000.0 / (iters * copies)
+                        iters = max(3, int(3e9 // (wbytes * copies)))
+                        us = time_launch_list(torch, stream, [(lambda w=w: ops.gemv(dt, w, xb, n, out=ob)) for w in ws], iters)
                         sweep.append({"type": dt.name, "k": k, "n": n, "b": b, "us": round(us, 2),
                                       "GBps": round((wbytes + b * k * 2 + b * n * 2) / us / 1e3, 1)})
                     del ws

