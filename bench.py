@@ -279,6 +279,7 @@ def main():
     ap.add_argument("--copies", type=int, default=0, help="--single: number of rotating weight copies")
     ap.add_argument("--two-launch", action="store_true", help="--single: quantize launcher + GEMV launcher instead of one launch")
     ap.add_argument("--pdl", type=int, default=None, help="programmatic dependent launch on/off")
+    ap.add_argument("--stage-bytes", type=int, default=None, help="GEMV planner: target bytes per shared-memory stage")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -292,6 +293,9 @@ def main():
     if args.pdl is not None:
         from inference_rs_b200 import ops as _ops
         _ops.set_option("pdl", args.pdl)
+    if args.stage_bytes is not None:
+        from inference_rs_b200 import ops as _ops
+        _ops.set_option("gemv_stage_bytes", args.stage_bytes)
     if args.single:
         run_single(args)
         return
@@ -422,6 +426,10 @@ def main():
                         xb = torch.randn(b, k, device="cuda", generator=gen).to(torch.bfloat16)
                         ob = torch.empty(b, n, dtype=torch.bfloat16, device="cuda")
                         iters = max(3, int(3e9 // (wbytes * copies)))
+                        if not ops.gemv_plan(dt, k, n, b)["staged"]:
+                            sweep.append({"type": dt.name, "k": k, "n": n, "b": b, "us": None, "GBps": None,
+                                          "note": "activations do not fit beside the ring: two-launch path only"})
+                            continue
                         us = time_launch_list(torch, stream, [(lambda w=w: ops.gemv(dt, w, xb, n, out=ob)) for w in ws], iters)
                         sweep.append({"type": dt.name, "k": k, "n": n, "b": b, "us": round(us, 2),
                                       "GBps": round((wbytes + b * k * 2 + b * n * 2) / us / 1e3, 1)})

@@ -107,6 +107,11 @@ int b200q_reset_device_status(void);
 /* First non-zero status a void launcher of part 1 produced since the last call, then cleared. */
 int b200q_take_launch_status(void);
 
+/* Diagnostics. `dev` is device memory for records * 16 uint64; every following GEMV launch takes the next record
+ * (wrapping) and its first / last CTA write %globaltimer nanoseconds {start, barriers ready, activations staged,
+ * first stage landed, done} into slots [0..4] / [8..12]. records = 0 switches it off. */
+int b200q_set_trace_buffer(void* dev, int records);
+
 /* One-launch decode GEMV on unquantized activations: x [b_size][stride_x] and dst [b_size][stride_dst] both of
  * element type `elem`; activations are quantized in the kernel's prologue.
  *   act_quant 0: to Q8_1 with the arithmetic of launch_mmvq_gguf_quantize_q8_1_*, so results equal the two-launch
@@ -118,8 +123,9 @@ int b200q_take_launch_status(void);
 int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
                int b_size, int act_quant, void* stream);
 
-/* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment} */
-int b200q_gemv_plan(int type, int K, int N, int b_size, int out[8]);
+/* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,
+ *        item slots per lane, register-resident slots} */
+int b200q_gemv_plan(int type, int K, int N, int b_size, int out[10]);
 
 #ifdef __cplusplus
 }

@@ -71,6 +71,14 @@ int b200q_reset_device_status(void) {
     return B200Q_OK;
 }
 
+// Diagnostics: `dev` points at records * 16 u64 of device memory; every following GEMV launch takes the next record
+// and its first / last CTA write nanosecond timestamps {start, barriers ready, activations staged, first stage
+// landed, done} at [0..4] / [8..12]. records = 0 switches tracing off.
+int b200q_set_trace_buffer(void* dev, int records) {
+    set_trace_buffer(static_cast<unsigned long long*>(dev), dev ? records : 0);
+    return B200Q_OK;
+}
+
 // First non-zero status a void launcher produced since the last call (then cleared).
 int b200q_take_launch_status(void) { return take_launch_status(); }
 
@@ -94,8 +102,9 @@ int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int 
     return B200Q_OK;
 }
 
-// out[8] = {staged, grid, smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment}
-int b200q_gemv_plan(int type, int K, int N, int b_size, int out[8]) {
+// out[10] = {staged, grid, smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,
+//            item slots per lane, register-resident slots}
+int b200q_gemv_plan(int type, int K, int N, int b_size, int out[10]) {
     if (type_block_bytes(type) == 0 || K <= 0 || K % type_block_elems(type) != 0 || b_size < 1 || b_size > 8)
         return set_error(B200Q_ERR_INVALID, "bad shape");
     gemv_describe(type, K, N, b_size, out);

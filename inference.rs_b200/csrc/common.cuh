@@ -165,6 +165,33 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Explicit shared-space loads on 32-bit shared addresses: keeps the compiler from falling back to generic loads
+// (64-bit address arithmetic, long-scoreboard latency) for pointers it cannot prove to be shared.
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint32_t v;
+    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t a) { return __uint_as_float(lds32(a)); }
+
+// int -> float without the conversion unit: exact for |v| < 2^22 (adds v ulps to 1.5 * 2^23, then subtracts it)
+__device__ __forceinline__ float int_to_float_small(int v) { return __int_as_float(0x4B400000 + v) - 12582912.0f; }
+
 // An aligned 32-bit word read at a 2-byte-aligned address: two aligned loads and a funnel shift.
 __device__ __forceinline__ uint32_t funnel16(uint32_t lo, uint32_t hi, uint32_t shift_bits) {
     return __funnelshift_r(lo, hi, shift_bits);

@@ -3,17 +3,21 @@
 // (crates/inference-quant/kernels/cuda/mmvq_gguf/mmvq_gguf.cuh:688-759, launcher :1762-1834).
 //
 // Design (HBM-bound; no tensor cores):
-//  * Weight rows are contiguous, so the matrix is one byte stream. Each CTA owns a contiguous range of rows and
-//    streams it through a ring of shared-memory stages with 1-D bulk (TMA) copies issued by one producer thread;
-//    full/empty mbarriers hand stages to eight consumer warps. Many KB per SM stay in flight with no registers
-//    spent on it, and the 2-byte-aligned Q6_K / Q8_0 blocks need no aligned global loads.
-//  * Activations are staged once per CTA in shared memory as 80-byte records per 64 values
-//    {i8 q[64]; f32 d[2]; f32 d*sum(q)[2]}: the 80-byte stride makes the 128-bit reads conflict-free. They come
-//    either from Q8_1 blocks written by the quantize launcher (the reference's two-launch protocol) or straight from
-//    bf16/f16/f32 rows (quantized in the prologue with the same formula, one launch).
-//  * Consumers unpack nibbles and 6-bit scales in registers, use dp4a on 4 packed int8, fold scales in f32 and
-//    reduce with warp shuffles; rows longer than one warp's worth are split across warps and combined through a
-//    small shared array in a fixed order, so results are deterministic.
+//  * Weight rows are contiguous, so the matrix is one byte stream. One persistent CTA per SM owns a contiguous range
+//    of rows and streams it through a ring of shared-memory stages with 1-D bulk (TMA) copies issued by one producer
+//    thread; full/empty mbarriers hand stages to sixteen consumer warps. Many KB per SM stay in flight with no
+//    registers spent on it, and the 2-byte-aligned Q6_K / Q8_0 blocks need no aligned global loads.
+//  * A row is cut into work items of 128 values (half a superblock, or four Q8_0 blocks); a warp covers a
+//    4096-wide row alone, wider rows are shared by several warps. Each lane owns the same item slots for the whole
+//    kernel, so for 1-2 activation rows its quantized activations stay in registers; larger batches read them from
+//    shared memory, where they are staged once per CTA as 80-byte records per 64 values
+//    {i8 q[64]; f32 d[2]; f32 d*sum(q)[2]} (the 80-byte stride makes the 128-bit reads conflict-free).
+//    Activations come either from Q8_1 blocks written by the quantize launcher (the reference's two-launch protocol)
+//    or straight from bf16/f16/f32 rows, quantized in the prologue (one launch).
+//  * Consumers unpack nibbles and 6-bit scales in registers, use dp4a on 4 packed int8, fold the sub-block scales
+//    as integers and the block scales in f32, and reduce with warp shuffles. Warps run independently (no CTA-wide
+//    barrier per stage); a row shared by several warps is combined by whichever of them arrives last, adding the
+//    partial sums in a fixed order, so results are deterministic.
 //  * Every mbarrier wait is bounded and reports through the device status word.
 #pragma once
 #include "common.cuh"
@@ -21,8 +25,9 @@
 
 namespace b200q {
 
-constexpr int GEMV_CONSUMER_WARPS = 8;
-constexpr int GEMV_THREADS = (GEMV_CONSUMER_WARPS + 1) * 32;
+constexpr int GEMV_CONSUMER_WARPS = 16;
+constexpr int GEMV_CONSUMER_THREADS = GEMV_CONSUMER_WARPS * 32;
+constexpr int GEMV_THREADS = GEMV_CONSUMER_THREADS + 32;
 constexpr int GEMV_MAX_STAGES = 8;
 constexpr int ACT_REC_BYTES = 80;  // i8 q[64]; f32 d[2]; f32 ds[2]
 
@@ -30,14 +35,15 @@ enum ActMode : int { ACT_Q8_1 = 0, ACT_RAW_Q8_1 = 1, ACT_RAW_CPU = 2 };
 
 struct GemvParams {
     const uint8_t* w;   // packed weights, row-major blocks, 16-byte aligned, >= 16 readable bytes after the end
-    const void* act;    // Q8_1 blocks [B][stride_act] (ACT_Q8_1) or raw rows [B][stride_act elements] (ACT_RAW)
+    const void* act;    // Q8_1 blocks [B][stride_act] (ACT_Q8_1) or raw rows [B][stride_act elements]
     void* dst;          // [B][stride_dst]
     int K, N;
     int stride_act;
     int stride_dst;
     int row_bytes;
-    int rows_per_stage;  // R: rows one stage holds (multiple of row_align and of consumer_warps / warps_per_row)
-    int warps_per_row;   // power of two <= 8
+    int rows_per_stage;  // R: rows one stage holds (multiple of row_align and of the number of row groups)
+    int warps_per_row;   // WPR: power of two <= 16; 16 / WPR row groups work on different rows at once
+    int items_per_lane;  // IPL: item slots of one lane: item = (warp % WPR) * 32 + lane + j * 32 * WPR, j < IPL
     int row_align;       // rows per 16-byte-aligned unit of the byte stream
     int nstages;
     int stage_bytes;     // multiple of 128
@@ -45,10 +51,22 @@ struct GemvParams {
     int use_pdl;
     int act_vec;         // raw activations: rows are 16-byte aligned
     unsigned int* status;  // device status word
+    unsigned long long* trace;  // optional: 8 timestamps (ns) written by the first and the last CTA, or nullptr
 };
 
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define GEMV_TRACE(slot)                                                                                   \
+    do {                                                                                                   \
+        if (p.trace != nullptr && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))            \
+            p.trace[(blockIdx.x == 0 ? 0 : 8) + (slot)] = global_timer_ns();                               \
+    } while (0)
+
 // ---------------------------------------------------------------------------------------------
-// Activation staging
+// Activation staging (generic stores into shared memory; read back with explicit shared loads)
 // ---------------------------------------------------------------------------------------------
 
 // From Q8_1 blocks: one thread per 32-value block.
@@ -62,16 +80,17 @@ __device__ __forceinline__ void stage_acts_q8_1(uint8_t* acts, const uint8_t* vy
         const uint32_t* src = reinterpret_cast<const uint32_t*>(vy + ((size_t)b * stride_blocks + kb) * Q8_1_BYTES);
         uint8_t* rec = acts + ((size_t)b * nrec + (kb >> 1)) * ACT_REC_BYTES;
         const int h = kb & 1;
-        const uint32_t ds = src[0];
+        uint32_t v[9];
+#pragma unroll
+        for (int j = 0; j < 9; ++j) v[j] = src[j];
         int sum = 0;
         uint32_t* qdst = reinterpret_cast<uint32_t*>(rec + 32 * h);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const uint32_t v = src[1 + j];
-            qdst[j] = v;
-            sum = dp4a_ss(0x01010101u, v, sum);
+            qdst[j] = v[1 + j];
+            sum = dp4a_ss(0x01010101u, v[1 + j], sum);
         }
-        const float d = half_bits_to_float(ds);
+        const float d = half_bits_to_float(v[0]);
         reinterpret_cast<float*>(rec + 64)[h] = d;
         reinterpret_cast<float*>(rec + 72)[h] = d * (float)sum;
     }
@@ -144,7 +163,7 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
         float v[8];
         load8<src_t>(x + (size_t)b * stride_elems + 8 * c, vec, v);
         int q[8];
-        float d_store, d_used;
+        float d_used;
         if (PER_256) {
             float amax = 0.0f, mx = 0.0f;
 #pragma unroll
@@ -161,14 +180,13 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
             if (amax == 0.0f) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) q[j] = 0;
-                d_store = 0.0f;
+                d_used = 0.0f;
             } else {
                 const float iscale = -127.0f / mx;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) q[j] = (int)fminf(fmaxf(roundf(iscale * v[j]), -128.0f), 127.0f);
-                d_store = 1.0f / iscale;
+                d_used = 1.0f / iscale;
             }
-            d_used = d_store;
         } else {
             float amax = 0.0f;
 #pragma unroll
@@ -184,8 +202,7 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
 #pragma unroll
                 for (int j = 0; j < 8; ++j) q[j] = amax == 0.0f ? 0 : (int)roundf(v[j] / d);
             }
-            d_store = __half2float(__float2half_rn(d));
-            d_used = d_store;
+            d_used = __half2float(__float2half_rn(d));
         }
         int sum = 0;
 #pragma unroll
@@ -207,180 +224,223 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
 }
 
 // ---------------------------------------------------------------------------------------------
-// Per-type decoders. `rowp` points at a weight row inside a shared-memory stage; `item` indexes the row's
-// work items; acts points at record 0 of activation row 0; nrec = K / 64.
+// Per-type work items: one item = 128 consecutive values of a row (half a superblock; four Q8_0 blocks), matched by
+// activation records 2*item and 2*item+1. All addresses are 32-bit shared-space addresses.
+//   Weights<TYPE>::load(row_addr, item)   reads one item of a weight row from a stage
+//   Acts<TYPE>::load(act_row_addr, item)  reads the matching quantized activations of one activation row
+//   dot(W, A)                             their contribution to the output, in f32
 // ---------------------------------------------------------------------------------------------
+template <int TYPE> struct Weights;
+template <int TYPE> struct Acts;
 
-// Q4_K: 4 items per superblock; item (s, c) is the 64 values of chunk c: 32 bytes of nibbles, low nibbles are
-// sub-block 2c, high nibbles sub-block 2c+1. Activation record index == item index.
-template <int B>
-__device__ __forceinline__ void q4k_item(const uint8_t* rowp, int item, const uint8_t* acts, int nrec, float (&acc)[B]) {
-    const int s = item >> 2, c = item & 3;
-    const uint8_t* sb = rowp + s * Q4_K_BYTES;
-    const uint4 hdr = *reinterpret_cast<const uint4*>(sb);
-    const uint4 w0 = *reinterpret_cast<const uint4*>(sb + 16 + 32 * c);
-    const uint4 w1 = *reinterpret_cast<const uint4*>(sb + 32 + 32 * c);
-    // 6-bit scale / min of sub-blocks 2c, 2c+1 (crates/inference-tensor/src/quantized/utils.rs:119-129)
-    const int sh = (c & 1) * 16;
-    const uint32_t a1 = hdr.y >> sh, a2 = hdr.z >> sh, a3 = hdr.w >> sh;
-    uint32_t scp, mp;
-    if (c < 2) {
-        scp = a1 & 0x3f3fu;
-        mp = a2 & 0x3f3fu;
-    } else {
-        scp = (a3 & 0x0f0fu) | ((a1 >> 2) & 0x3030u);
-        mp = ((a3 >> 4) & 0x0f0fu) | ((a2 >> 2) & 0x3030u);
-    }
-    const float d = half_bits_to_float(hdr.x), dmin = half_bits_to_float(hdr.x >> 16);
-    const float wsc0 = d * (float)(scp & 0xffu);
-    const float wsc1 = d * (float)(scp >> 8) * 0.0625f;  // high nibbles are used as 16 * q
-    const float wm0 = dmin * (float)(mp & 0xffu);
-    const float wm1 = dmin * (float)(mp >> 8);
-    const uint32_t wl[8] = {w0.x & 0x0f0f0f0fu, w0.y & 0x0f0f0f0fu, w0.z & 0x0f0f0f0fu, w0.w & 0x0f0f0f0fu,
-                            w1.x & 0x0f0f0f0fu, w1.y & 0x0f0f0f0fu, w1.z & 0x0f0f0f0fu, w1.w & 0x0f0f0f0fu};
-    const uint32_t wh[8] = {w0.x & 0xf0f0f0f0u, w0.y & 0xf0f0f0f0u, w0.z & 0xf0f0f0f0u, w0.w & 0xf0f0f0f0u,
-                            w1.x & 0xf0f0f0f0u, w1.y & 0xf0f0f0f0u, w1.z & 0xf0f0f0f0u, w1.w & 0xf0f0f0f0u};
+// two 80-byte activation records in registers: 128 int8 and, per 32 of them, d and d * sum(q)
+struct ActPair {
+    uint32_t q[32];
+    float d[4], ds[4];
+    __device__ __forceinline__ void load(uint32_t act_row, int item) {
+        const uint32_t rec = act_row + (uint32_t)item * (2 * ACT_REC_BYTES);
 #pragma unroll
-    for (int b = 0; b < B; ++b) {
-        const uint8_t* rec = acts + ((size_t)b * nrec + item) * ACT_REC_BYTES;
-        const uint4 q0 = *reinterpret_cast<const uint4*>(rec);
-        const uint4 q1 = *reinterpret_cast<const uint4*>(rec + 16);
-        const uint4 q2 = *reinterpret_cast<const uint4*>(rec + 32);
-        const uint4 q3 = *reinterpret_cast<const uint4*>(rec + 48);
-        const float4 f = *reinterpret_cast<const float4*>(rec + 64);
-        int dl = 0, dh = 0;
-        dl = dp4a_us(wl[0], q0.x, dl); dl = dp4a_us(wl[1], q0.y, dl); dl = dp4a_us(wl[2], q0.z, dl); dl = dp4a_us(wl[3], q0.w, dl);
-        dl = dp4a_us(wl[4], q1.x, dl); dl = dp4a_us(wl[5], q1.y, dl); dl = dp4a_us(wl[6], q1.z, dl); dl = dp4a_us(wl[7], q1.w, dl);
-        dh = dp4a_us(wh[0], q2.x, dh); dh = dp4a_us(wh[1], q2.y, dh); dh = dp4a_us(wh[2], q2.z, dh); dh = dp4a_us(wh[3], q2.w, dh);
-        dh = dp4a_us(wh[4], q3.x, dh); dh = dp4a_us(wh[5], q3.y, dh); dh = dp4a_us(wh[6], q3.z, dh); dh = dp4a_us(wh[7], q3.w, dh);
-        acc[b] += wsc0 * (f.x * (float)dl) + wsc1 * (f.y * (float)dh) - (wm0 * f.z + wm1 * f.w);
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t a = rec + r * ACT_REC_BYTES;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 v = lds128(a + 16 * j);
+                q[16 * r + 4 * j + 0] = v.x; q[16 * r + 4 * j + 1] = v.y; q[16 * r + 4 * j + 2] = v.z; q[16 * r + 4 * j + 3] = v.w;
+            }
+            const uint4 f = lds128(a + 64);
+            d[2 * r] = __uint_as_float(f.x); d[2 * r + 1] = __uint_as_float(f.y);
+            ds[2 * r] = __uint_as_float(f.z); ds[2 * r + 1] = __uint_as_float(f.w);
+        }
     }
-}
-__device__ __forceinline__ int q4k_items(int K) { return K / 64; }
+};
 
-// Reads `N` consecutive 32-bit words starting at the 2-byte-aligned shared address p.
+// ---- Q4_K: item (s, h) = chunks c = 2h, 2h+1 of superblock s: 64 bytes of nibbles; in chunk c the low nibbles are
+// sub-block 2c and the high nibbles sub-block 2c+1.
+template <> struct Weights<TYPE_Q4_K> {
+    uint32_t w[16];
+    uint32_t sc4, m4;  // the four 6-bit scales / mins of sub-blocks 4h .. 4h+3, one per byte
+    float d, dmin;
+    __device__ __forceinline__ void load(uint32_t row_addr, int item) {
+        const int s = item >> 1, h = item & 1;
+        const uint32_t sb = row_addr + s * Q4_K_BYTES;
+        const uint4 hdr = lds128(sb);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 v = lds128(sb + 16 + 64 * h + 16 * j);
+            w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+        }
+        // 6-bit scales and mins (crates/inference-tensor/src/quantized/utils.rs:119-129), four at a time
+        if (h == 0) {
+            sc4 = hdr.y & 0x3f3f3f3fu;
+            m4 = hdr.z & 0x3f3f3f3fu;
+        } else {
+            sc4 = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+            m4 = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+        }
+        d = half_bits_to_float(hdr.x);
+        dmin = half_bits_to_float(hdr.x >> 16);
+    }
+};
+template <> struct Acts<TYPE_Q4_K> : ActPair {};
+__device__ __forceinline__ float dot(const Weights<TYPE_Q4_K>& W, const Acts<TYPE_Q4_K>& A) {
+    float accd = 0.0f, accm = 0.0f;
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+        int dl0 = 0, dl1 = 0, dh0 = 0, dh1 = 0;  // two chains per half keep the dp4a pipe busy
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            dl0 = dp4a_us(W.w[8 * cc + j] & 0x0f0f0f0fu, A.q[16 * cc + j], dl0);
+            dl1 = dp4a_us(W.w[8 * cc + 4 + j] & 0x0f0f0f0fu, A.q[16 * cc + 4 + j], dl1);
+            dh0 = dp4a_us(W.w[8 * cc + j] & 0xf0f0f0f0u, A.q[16 * cc + 8 + j], dh0);       // 16 * high nibble
+            dh1 = dp4a_us(W.w[8 * cc + 4 + j] & 0xf0f0f0f0u, A.q[16 * cc + 12 + j], dh1);
+        }
+        const int sc_lo = (int)((W.sc4 >> (16 * cc)) & 0xffu), sc_hi = (int)((W.sc4 >> (16 * cc + 8)) & 0xffu);
+        const int m_lo = (int)((W.m4 >> (16 * cc)) & 0xffu), m_hi = (int)((W.m4 >> (16 * cc + 8)) & 0xffu);
+        // integer scale folding: |sc * dot| <= 63 * 32 * 15 * 127 < 2^22
+        accd += A.d[2 * cc] * int_to_float_small(sc_lo * (dl0 + dl1));
+        accd += A.d[2 * cc + 1] * int_to_float_small(sc_hi * ((dh0 + dh1) >> 4));
+        accm += int_to_float_small(m_lo) * A.ds[2 * cc] + int_to_float_small(m_hi) * A.ds[2 * cc + 1];
+    }
+    return W.d * accd - W.dmin * accm;
+}
+
+// Reads N consecutive 32-bit words starting at the 2-byte-aligned shared address a.
 template <int N>
-__device__ __forceinline__ void load_words_u16aligned(const uint8_t* p, uint32_t (&out)[N]) {
-    const uint32_t addr = smem_u32(p);
-    const uint32_t shift = (addr & 2u) * 8u;
-    const uint32_t* a = reinterpret_cast<const uint32_t*>(p - (addr & 2u));
-    uint32_t prev = a[0];
+__device__ __forceinline__ void lds_words_u16aligned(uint32_t a, uint32_t (&out)[N]) {
+    const uint32_t shift = (a & 2u) * 8u;
+    const uint32_t base = a & ~3u;
+    uint32_t prev = lds32(base);
 #pragma unroll
     for (int i = 0; i < N; ++i) {
-        const uint32_t next = a[i + 1];
-        out[i] = funnel16(prev, next, shift);
+        const uint32_t next = lds32(base + 4 * (i + 1));
+        out[i] = __funnelshift_r(prev, next, shift);
         prev = next;
     }
 }
 
-// Q6_K: 8 items per superblock; item (s, n, u): half n, bytes l = 8u..8u+7 of that half: 8 values from each of the
-// four 32-value quarters (crates/inference-tensor/src/quantized/k_quants.rs:2661-2677). Weights are rebuilt as
-// 4 * (q - 32) in a signed byte: ((q ^ 32) << 2) reinterpreted, so no subtraction and one signed dp4a.
-template <int B>
-__device__ __forceinline__ void q6k_item(const uint8_t* rowp, int item, const uint8_t* acts, int nrec, float (&acc)[B]) {
-    const int s = item >> 3, n = (item >> 2) & 1, u = item & 3;
-    const uint8_t* sb = rowp + s * Q6_K_BYTES;
-    uint32_t qla[2], qlb[2], qh[2], scw[2];
-    load_words_u16aligned<2>(sb + 64 * n + 8 * u, qla);        // ql[64n + l]: quarters 0 (low nibble), 2 (high)
-    load_words_u16aligned<2>(sb + 64 * n + 32 + 8 * u, qlb);   // ql[64n + 32 + l]: quarters 1, 3
-    load_words_u16aligned<2>(sb + 128 + 32 * n + 8 * u, qh);   // qh[32n + l]: 2 bits per quarter
-    load_words_u16aligned<2>(sb + 192 + 8 * n, scw);           // scales[8n .. 8n+7]
-    const float d = half_bits_to_float(*reinterpret_cast<const unsigned short*>(sb + 208)) * 0.25f;
-    // scale of quarter qd, 16-group u/2: scales[8n + 2*qd + (u >> 1)]
-    const int sbyte = (u >> 1);
-    float wsc[4];
-#pragma unroll
-    for (int qd = 0; qd < 4; ++qd) {
-        const int idx = 2 * qd + sbyte;  // 0..7
-        const uint32_t word = idx < 4 ? scw[0] : scw[1];
-        const int sc = (int)(int8_t)((word >> (8 * (idx & 3))) & 0xffu);
-        wsc[qd] = d * (float)sc;
+// ---- Q6_K: item (s, n) = half n of superblock s: ql[64n..], qh[32n..], scales[8n..]; byte l of the half holds
+// one value of each of the four 32-value quarters (crates/inference-tensor/src/quantized/k_quants.rs:2661-2677).
+// Weights are rebuilt as 4 * (q - 32) in a signed byte: ((q ^ 32) << 2) reinterpreted, so no subtraction and one
+// signed dp4a; the factor 4 is folded into d.
+template <> struct Weights<TYPE_Q6_K> {
+    uint32_t ql[16], qh[8], scw[2];
+    float d;
+    __device__ __forceinline__ void load(uint32_t row_addr, int item) {
+        const int s = item >> 1, n = item & 1;
+        const uint32_t sb = row_addr + s * Q6_K_BYTES;
+        lds_words_u16aligned<16>(sb + 64 * n, ql);
+        lds_words_u16aligned<8>(sb + 128 + 32 * n, qh);
+        lds_words_u16aligned<2>(sb + 192 + 8 * n, scw);
+        d = half_bits_to_float(lds16(sb + 208)) * 0.25f;
     }
-    uint32_t wq[4][2];
+};
+// the 128 activations of half n in order: quarter qd = values 32*qd .. 32*qd+31 = words 8*qd .. 8*qd+7
+template <> struct Acts<TYPE_Q6_K> {
+    uint32_t q[32];
+    float d[4];
+    __device__ __forceinline__ void load(uint32_t act_row, int item) {
+        const uint32_t rec = act_row + (uint32_t)item * (2 * ACT_REC_BYTES);
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        const uint32_t la = qla[t], lb = qlb[t], h = qh[t];
-        wq[0][t] = ((la << 2) & 0x3c3c3c3cu) | (((h << 6) & 0xc0c0c0c0u) ^ 0x80808080u);
-        wq[1][t] = ((lb << 2) & 0x3c3c3c3cu) | (((h << 4) & 0xc0c0c0c0u) ^ 0x80808080u);
-        wq[2][t] = ((la >> 2) & 0x3c3c3c3cu) | (((h << 2) & 0xc0c0c0c0u) ^ 0x80808080u);
-        wq[3][t] = ((lb >> 2) & 0x3c3c3c3cu) | ((h & 0xc0c0c0c0u) ^ 0x80808080u);
-    }
-    // activations: quarter qd of half n of superblock s is 32-value block 8s + 4n + qd = record 4s + 2n + (qd>>1),
-    // half (qd & 1); this item uses its bytes 8u..8u+7
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t a = rec + r * ACT_REC_BYTES;
 #pragma unroll
-    for (int b = 0; b < B; ++b) {
-        const uint8_t* rec0 = acts + ((size_t)b * nrec + 4 * s + 2 * n) * ACT_REC_BYTES;
-        float part = 0.0f;
-#pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-            const uint8_t* rec = rec0 + (qd >> 1) * ACT_REC_BYTES;
-            const uint2 q = *reinterpret_cast<const uint2*>(rec + 32 * (qd & 1) + 8 * u);
-            const float d8 = reinterpret_cast<const float*>(rec + 64)[qd & 1];
-            int dot = dp4a_ss(wq[qd][0], q.x, 0);
-            dot = dp4a_ss(wq[qd][1], q.y, dot);
-            part += wsc[qd] * (d8 * (float)dot);
+            for (int j = 0; j < 4; ++j) {
+                const uint4 v = lds128(a + 16 * j);
+                q[16 * r + 4 * j + 0] = v.x; q[16 * r + 4 * j + 1] = v.y; q[16 * r + 4 * j + 2] = v.z; q[16 * r + 4 * j + 3] = v.w;
+            }
+            const uint2 f = lds64(a + 64);
+            d[2 * r] = __uint_as_float(f.x); d[2 * r + 1] = __uint_as_float(f.y);
         }
-        acc[b] += part;
     }
-}
-__device__ __forceinline__ int q6k_items(int K) { return K / 32; }
-
-// Q8_0: one item per 64 values = two 34-byte blocks; activation record index == item index.
-template <int B>
-__device__ __forceinline__ void q80_item(const uint8_t* rowp, int item, const uint8_t* acts, int nrec, float (&acc)[B]) {
-    const uint8_t* blk = rowp + item * (2 * Q8_0_BYTES);
-    uint32_t w[17];
-    load_words_u16aligned<17>(blk, w);  // 68 bytes: d0 q0[32] d1 q1[32]
-    // block 0: d in the low half of w[0], qs = bytes 2..33; block 1: d at byte 34 (high half of w[8]), qs bytes 36..67
-    const float d0 = half_bits_to_float(w[0]);
-    const float d1 = half_bits_to_float(w[8] >> 16);
-    uint32_t qa[8];
+};
+__device__ __forceinline__ float dot(const Weights<TYPE_Q6_K>& W, const Acts<TYPE_Q6_K>& A) {
+    int acc[4][2];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) qa[j] = __funnelshift_r(w[j], w[j + 1], 16);
+    for (int qd = 0; qd < 4; ++qd) acc[qd][0] = acc[qd][1] = 0;
 #pragma unroll
-    for (int b = 0; b < B; ++b) {
-        const uint8_t* rec = acts + ((size_t)b * nrec + item) * ACT_REC_BYTES;
-        const uint4 q0 = *reinterpret_cast<const uint4*>(rec);
-        const uint4 q1 = *reinterpret_cast<const uint4*>(rec + 16);
-        const uint4 q2 = *reinterpret_cast<const uint4*>(rec + 32);
-        const uint4 q3 = *reinterpret_cast<const uint4*>(rec + 48);
-        const float4 f = *reinterpret_cast<const float4*>(rec + 64);
-        int da = 0, db = 0;
-        da = dp4a_ss(qa[0], q0.x, da); da = dp4a_ss(qa[1], q0.y, da); da = dp4a_ss(qa[2], q0.z, da); da = dp4a_ss(qa[3], q0.w, da);
-        da = dp4a_ss(qa[4], q1.x, da); da = dp4a_ss(qa[5], q1.y, da); da = dp4a_ss(qa[6], q1.z, da); da = dp4a_ss(qa[7], q1.w, da);
-        db = dp4a_ss(w[9], q2.x, db); db = dp4a_ss(w[10], q2.y, db); db = dp4a_ss(w[11], q2.z, db); db = dp4a_ss(w[12], q2.w, db);
-        db = dp4a_ss(w[13], q3.x, db); db = dp4a_ss(w[14], q3.y, db); db = dp4a_ss(w[15], q3.z, db); db = dp4a_ss(w[16], q3.w, db);
-        acc[b] += d0 * (f.x * (float)da) + d1 * (f.y * (float)db);
+    for (int t = 0; t < 8; ++t) {  // bytes l = 4t .. 4t+3 of the half; 16-value group g = t / 4
+        const uint32_t la = W.ql[t], lb = W.ql[8 + t], h = W.qh[t];
+        const uint32_t w0 = ((la << 2) & 0x3c3c3c3cu) | (((h << 6) & 0xc0c0c0c0u) ^ 0x80808080u);
+        const uint32_t w1 = ((lb << 2) & 0x3c3c3c3cu) | (((h << 4) & 0xc0c0c0c0u) ^ 0x80808080u);
+        const uint32_t w2 = ((la >> 2) & 0x3c3c3c3cu) | (((h << 2) & 0xc0c0c0c0u) ^ 0x80808080u);
+        const uint32_t w3 = ((lb >> 2) & 0x3c3c3c3cu) | ((h & 0xc0c0c0c0u) ^ 0x80808080u);
+        const int g = t >> 2;
+        acc[0][g] = dp4a_ss(w0, A.q[t], acc[0][g]);
+        acc[1][g] = dp4a_ss(w1, A.q[8 + t], acc[1][g]);
+        acc[2][g] = dp4a_ss(w2, A.q[16 + t], acc[2][g]);
+        acc[3][g] = dp4a_ss(w3, A.q[24 + t], acc[3][g]);
     }
+    float part = 0.0f;
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd) {  // scales[8n + 2*qd + g]
+        const uint32_t word = qd < 2 ? W.scw[0] : W.scw[1];
+        const int s0 = (int)(int8_t)((word >> (16 * (qd & 1))) & 0xffu);
+        const int s1 = (int)(int8_t)((word >> (16 * (qd & 1) + 8)) & 0xffu);
+        part += A.d[qd] * (float)(s0 * acc[qd][0] + s1 * acc[qd][1]);
+    }
+    return W.d * part;
 }
-__device__ __forceinline__ int q80_items(int K) { return K / 64; }
 
-template <int TYPE, int B>
-__device__ __forceinline__ void decode_item(const uint8_t* rowp, int item, const uint8_t* acts, int nrec, float (&acc)[B]) {
-    if (TYPE == TYPE_Q4_K) q4k_item<B>(rowp, item, acts, nrec, acc);
-    else if (TYPE == TYPE_Q6_K) q6k_item<B>(rowp, item, acts, nrec, acc);
-    else q80_item<B>(rowp, item, acts, nrec, acc);
-}
-template <int TYPE>
-__device__ __forceinline__ int items_per_row(int K) {
-    return TYPE == TYPE_Q4_K ? q4k_items(K) : (TYPE == TYPE_Q6_K ? q6k_items(K) : q80_items(K));
+// ---- Q8_0: item = four 34-byte blocks.
+template <> struct Weights<TYPE_Q8_0> {
+    uint32_t q[32];
+    float d[4];
+    __device__ __forceinline__ void load(uint32_t row_addr, int item) {
+        uint32_t w[34];
+        lds_words_u16aligned<34>(row_addr + (uint32_t)item * (4 * Q8_0_BYTES), w);  // 136 bytes
+        // block b starts at byte 34 b: f16 d, then 32 quants
+        d[0] = half_bits_to_float(w[0]);
+        d[1] = half_bits_to_float(w[8] >> 16);
+        d[2] = half_bits_to_float(w[17]);
+        d[3] = half_bits_to_float(w[25] >> 16);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            q[j] = __funnelshift_r(w[j], w[j + 1], 16);             // bytes 2 .. 33
+            q[8 + j] = w[9 + j];                                    // bytes 36 .. 67
+            q[16 + j] = __funnelshift_r(w[17 + j], w[18 + j], 16);  // bytes 70 .. 101
+            q[24 + j] = w[26 + j];                                  // bytes 104 .. 135
+        }
+    }
+};
+template <> struct Acts<TYPE_Q8_0> : ActPair {};
+__device__ __forceinline__ float dot(const Weights<TYPE_Q8_0>& W, const Acts<TYPE_Q8_0>& A) {
+    float part = 0.0f;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        int v0 = 0, v1 = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v0 = dp4a_ss(W.q[8 * b + j], A.q[8 * b + j], v0);
+            v1 = dp4a_ss(W.q[8 * b + 4 + j], A.q[8 * b + 4 + j], v1);
+        }
+        part += W.d[b] * (A.d[b] * int_to_float_small(v0 + v1));
+    }
+    return part;
 }
 
 // ---------------------------------------------------------------------------------------------
-// The kernel
+// The kernel. NREG = item slots per lane whose activations live in registers (0: read from shared memory each time).
+//
+// Lanes and items: a row has K / 128 items. With >= 32 items a row is shared by WPR warps (slice = warp % WPR) and a
+// lane owns items slice*32 + lane + j*32*WPR, j < IPL. With fewer, a warp works on 32 / islots rows at once
+// (islots = items rounded up to a power of two): lane = rsub * islots + item.
 // ---------------------------------------------------------------------------------------------
-template <int TYPE, int B, typename dst_t, int ACT, typename act_t>
-__global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_staged_kernel(const GemvParams p) {
+template <int TYPE, int B, typename dst_t, int ACT, typename act_t, int NREG>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + GEMV_MAX_STAGES;
     uint8_t* acts = smem + 128;
-    float* partial = reinterpret_cast<float*>(acts + p.act_bytes);                    // [2][R][WPR][B]
-    const int partial_floats = p.warps_per_row > 1 ? 2 * p.rows_per_stage * p.warps_per_row * B : 0;
-    uint8_t* ring = acts + p.act_bytes + ((partial_floats * 4 + 127) & ~127);
+    const int S = p.nstages, R = p.rows_per_stage, WPR = p.warps_per_row, IPL = p.items_per_lane;
+    // cross-warp combine (WPR > 1): per stage and row, WPR partial sums per activation row and an arrival counter
+    float* partial = reinterpret_cast<float*>(acts + p.act_bytes);  // [S][R][WPR][B]
+    const int partial_floats = WPR > 1 ? S * R * WPR * B : 0;
+    int* counters = reinterpret_cast<int*>(partial + partial_floats);  // [S][R]
+    const int counter_ints = WPR > 1 ? S * R : 0;
+    uint8_t* ring = acts + p.act_bytes + (((partial_floats + counter_ints) * 4 + 127) & ~127);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int S = p.nstages, R = p.rows_per_stage, WPR = p.warps_per_row;
+    GEMV_TRACE(0);
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
@@ -389,7 +449,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_staged_kernel(const Gemv
         }
         mbar_init_fence();
     }
+    for (int i = tid; i < counter_ints; i += GEMV_THREADS) counters[i] = 0;
     __syncthreads();
+    GEMV_TRACE(1);
 
     // this CTA's rows: a contiguous run of 16-byte-aligned units
     const long long units = (p.N + p.row_align - 1) / p.row_align;
@@ -434,66 +496,122 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_staged_kernel(const Gemv
     // ---------------- consumers ----------------
     if (p.use_pdl) grid_dependency_wait();
     if (ACT == ACT_Q8_1)
-        stage_acts_q8_1<B>(acts, reinterpret_cast<const uint8_t*>(p.act), p.K, p.stride_act, tid, GEMV_CONSUMER_WARPS * 32);
+        stage_acts_q8_1<B>(acts, reinterpret_cast<const uint8_t*>(p.act), p.K, p.stride_act, tid, GEMV_CONSUMER_THREADS);
     else
         stage_acts_raw<B, act_t, TYPE, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.stride_act, p.act_vec != 0, tid,
-                                            GEMV_CONSUMER_WARPS * 32);
-    named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
+                                            GEMV_CONSUMER_THREADS);
+    named_bar_sync(1, GEMV_CONSUMER_THREADS);
     if (p.use_pdl) grid_launch_dependents();
+    GEMV_TRACE(2);
 
     const int nrec = p.K / 64;
-    const int items = items_per_row<TYPE>(p.K);
-    const int rows_per_pass = GEMV_CONSUMER_WARPS / WPR;
-    const int wrow = warp / WPR, wslice = warp % WPR;
+    const int items = p.K / 128;
+    int islots = 32;                       // lanes that share one row inside a warp
+    while (islots > 1 && (islots >> 1) >= items) islots >>= 1;
+    const int rpw = 32 / islots;           // rows a warp works on at once
+    const int lane_i = lane & (islots - 1), lane_r = lane / islots;
+    const int nrg = GEMV_CONSUMER_WARPS / WPR;  // warp groups working on different rows
+    const int wgroup = warp / WPR, wslice = warp % WPR;
+    const int row_slot = wgroup * rpw + lane_r;  // this lane's row within a pass of nrg * rpw rows
+    const int rows_per_pass = nrg * rpw;
+    const int item0 = wslice * 32 + lane_i;
+    const int item_step = 32 * WPR;
+    const uint32_t acts_addr = smem_u32(acts);
+    const uint32_t ring_addr = smem_u32(ring);
+    const uint32_t act_row_bytes = (uint32_t)nrec * ACT_REC_BYTES;
     dst_t* dst = reinterpret_cast<dst_t*>(p.dst);
-    bool alive = true;
 
+    Acts<TYPE> areg[NREG > 0 ? B : 1][NREG > 0 ? NREG : 1];
+    if (NREG > 0) {
+#pragma unroll
+        for (int b = 0; b < B; ++b)
+#pragma unroll
+            for (int j = 0; j < (NREG > 0 ? NREG : 1); ++j)
+                if (item0 + j * item_step < items) areg[b][j].load(acts_addr + b * act_row_bytes, item0 + j * item_step);
+    }
+
+    bool alive = true;
     for (int it = 0; it < niter; ++it) {
         const int s = it % S;
         if (alive && !mbar_wait_bounded(&full[s], (it / S) & 1)) {
             record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, it);
-            alive = false;
+            alive = false;  // keep arriving so that the others are not held up, but compute nothing
         }
-        // a failed wait is warp-uniform (every lane polls the same barrier); the warp keeps arriving so that
-        // the others are not held up, but computes nothing
-        const uint8_t* st = ring + (size_t)s * p.stage_bytes;
+        if (it == 0) GEMV_TRACE(3);
+        const uint32_t st = ring_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
         const int rbase = row0 + it * R;
         const int rows_here = min(R, row1 - rbase);
-        float* part = partial + (size_t)(it & 1) * R * WPR * B;
-        for (int pass = 0; pass * rows_per_pass < rows_here; ++pass) {
-            const int r_in = pass * rows_per_pass + wrow;
+        for (int pass0 = 0; pass0 < rows_here; pass0 += rows_per_pass) {  // warp-uniform trip count
+            const int r_in = pass0 + row_slot;
+            const bool has_row = r_in < rows_here;
             float acc[B];
 #pragma unroll
             for (int b = 0; b < B; ++b) acc[b] = 0.0f;
-            if (alive && r_in < rows_here) {
-                const uint8_t* rowp = st + (size_t)r_in * p.row_bytes;
-                for (int item = wslice * 32 + lane; item < items; item += 32 * WPR)
-                    decode_item<TYPE, B>(rowp, item, acts, nrec, acc);
-            }
+            if (alive && has_row) {
+                const uint32_t row_addr = st + (uint32_t)r_in * (uint32_t)p.row_bytes;
+                if (NREG > 0) {
 #pragma unroll
-            for (int b = 0; b < B; ++b) acc[b] = warp_sum(acc[b]);
-            if (lane == 0 && r_in < rows_here) {
+                    for (int j = 0; j < (NREG > 0 ? NREG : 1); ++j) {
+                        const int item = item0 + j * item_step;
+                        if (item < items) {
+                            Weights<TYPE> W;
+                            W.load(row_addr, item);
+#pragma unroll
+                            for (int b = 0; b < B; ++b) acc[b] += dot(W, areg[b][j]);
+                        }
+                    }
+                } else {
+                    for (int j = 0; j < IPL; ++j) {
+                        const int item = item0 + j * item_step;
+                        if (item < items) {
+                            Weights<TYPE> W;
+                            W.load(row_addr, item);
+#pragma unroll
+                            for (int b = 0; b < B; ++b) {
+                                Acts<TYPE> A;
+                                A.load(acts_addr + b * act_row_bytes, item);
+                                acc[b] += dot(W, A);
+                            }
+                        }
+                    }
+                }
+            }
+            // reduce over the lanes that share the row
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) {
+                if (m < islots) {
+#pragma unroll
+                    for (int b = 0; b < B; ++b) acc[b] += __shfl_xor_sync(0xffffffffu, acc[b], m);
+                }
+            }
+            if (lane_i == 0 && has_row) {
                 if (WPR == 1) {
 #pragma unroll
                     for (int b = 0; b < B; ++b) dst[(size_t)b * p.stride_dst + rbase + r_in] = from_float<dst_t>(acc[b]);
                 } else {
+                    // the last of the WPR warps to arrive adds the partial sums in slice order and writes the row
+                    float* part = partial + ((size_t)(s * R + r_in) * WPR) * B;
 #pragma unroll
-                    for (int b = 0; b < B; ++b) part[((size_t)r_in * WPR + wslice) * B + b] = acc[b];
+                    for (int b = 0; b < B; ++b) part[wslice * B + b] = acc[b];
+                    __threadfence_block();
+                    const int arrived = atomicAdd(&counters[s * R + r_in], 1);
+                    if (arrived == WPR - 1) {
+                        __threadfence_block();
+                        counters[s * R + r_in] = 0;
+#pragma unroll
+                        for (int b = 0; b < B; ++b) {
+                            float v = 0.0f;
+                            for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w * B + b];
+                            dst[(size_t)b * p.stride_dst + rbase + r_in] = from_float<dst_t>(v);
+                        }
+                    }
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
-        if (WPR > 1) {
-            named_bar_sync(1, GEMV_CONSUMER_WARPS * 32);
-            for (int o = tid; o < rows_here * B; o += GEMV_CONSUMER_WARPS * 32) {
-                const int r_in = o / B, b = o - r_in * B;
-                float v = 0.0f;
-                for (int w = 0; w < WPR; ++w) v += part[((size_t)r_in * WPR + w) * B + b];
-                dst[(size_t)b * p.stride_dst + rbase + r_in] = from_float<dst_t>(v);
-            }
-        }
     }
+    GEMV_TRACE(4);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -559,13 +677,13 @@ __global__ void __launch_bounds__(256) gemv_simple_kernel(const uint8_t* __restr
                 const float s0 = (float)ld_i8(sb + 192 + 8 * n + 2 * qd), s1 = (float)ld_i8(sb + 192 + 8 * n + 2 * qd + 1);
                 acc[b] += scale * d8 * (s0 * (float)d0 + s1 * (float)d1);
             } else {
-                int dot = 0, s8 = 0;
+                int dotv = 0, s8 = 0;
                 for (int l = 0; l < 32; ++l) {
                     const int a = ld_i8(ab + 4 + l);
-                    dot += wq[l] * a;
+                    dotv += wq[l] * a;
                     s8 += a;
                 }
-                acc[b] += scale * d8 * (float)dot - minv * d8 * (float)s8;
+                acc[b] += scale * d8 * (float)dotv - minv * d8 * (float)s8;
             }
         }
     }
@@ -585,11 +703,12 @@ struct GemvPlan {
     bool staged;
     GemvParams p;
     int grid;
+    int nreg;  // register-resident item slots per lane (0 = activations read from shared memory)
     size_t smem;
 };
 
-// Chooses rows per stage, warps per row, ring depth and grid for a shape. `w` is only inspected for alignment
-// (nullptr = assume aligned).
+// Chooses the lane-to-item mapping, rows per stage, ring depth and grid for a shape. `w` is only inspected for
+// alignment (nullptr = assume aligned).
 static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     const RuntimeInfo& rt = runtime_info();
     GemvPlan plan{};
@@ -602,48 +721,66 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     p.act_bytes = ((B * (K / 64) * ACT_REC_BYTES) + 127) & ~127;
     p.use_pdl = rt.use_pdl;
     plan.staged = false;
-    if (rt.force_simple || K % 64 != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return plan;
+    if (rt.force_simple || K % 128 != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return plan;
 
-    // rows per stage: ~stage_target bytes, at least one aligned unit; fewer rows than consumer warps means each
-    // row is split over several warps
-    int rmax = rt.gemv_stage_target / p.row_bytes;
-    if (rmax < 1) rmax = 1;
-    int R, wpr;
-    if (rmax >= GEMV_CONSUMER_WARPS) {
-        wpr = 1;
-        R = rmax / GEMV_CONSUMER_WARPS * GEMV_CONSUMER_WARPS;
-    } else {
-        R = 1;
-        while (R * 2 <= rmax) R *= 2;
-        if (R < p.row_align) R = p.row_align;  // both powers of two <= 8
-        wpr = GEMV_CONSUMER_WARPS / R;
+    const int items = K / 128;
+    int islots = 32;
+    while (islots > 1 && (islots >> 1) >= items) islots >>= 1;
+    const int rpw = 32 / islots;
+    // a row of more than 32 items: up to 2 item slots per lane (their activations stay in registers for one
+    // activation row), then more warps per row
+    int ipl = 1, wpr = 1;
+    if (items > 32) {
+        const int regs_ipl = (B == 1) ? 2 : 1;
+        while (wpr * 32 * ipl < items) {
+            if (ipl < regs_ipl) ipl *= 2;
+            else if (wpr < GEMV_CONSUMER_WARPS) wpr *= 2;
+            else ipl *= 2;
+        }
+        // prefer one slot per lane when that does not need more warps than two slots would
+        if (ipl == 2 && wpr * 32 >= items) ipl = 1;
     }
+    // keep a stage (one pass of all warps) under ~48 KB: trade the second slot for more warps per row
+    while (ipl > 1 && wpr < GEMV_CONSUMER_WARPS &&
+           (long long)(GEMV_CONSUMER_WARPS / wpr) * rpw * p.row_bytes > 48 * 1024) {
+        ipl /= 2;
+        wpr *= 2;
+    }
+    if (ipl > 16) return plan;
+    const int nrg = GEMV_CONSUMER_WARPS / wpr;
+    const int rows_per_pass = nrg * rpw;
+    const int unit = rows_per_pass * p.row_align / gcd_int(rows_per_pass, p.row_align);
+    int R = rt.gemv_stage_target / (unit * p.row_bytes) * unit;
+    if (R < unit) R = unit;
     p.rows_per_stage = R;
     p.warps_per_row = wpr;
+    p.items_per_lane = ipl;
     p.stage_bytes = (R * p.row_bytes + 16 + 127) & ~127;
-    const int partial_bytes = wpr > 1 ? ((2 * R * wpr * B * 4 + 127) & ~127) : 0;
-    const int fixed = 128 + p.act_bytes + partial_bytes;
     const int budget = rt.smem_optin - 1024;  // 1 KB per CTA is reserved by the system
-    if (budget - fixed < 2 * p.stage_bytes) return plan;  // does not fit: simple kernel
-    // two CTAs per SM when each still gets >= 3 stages and >= 48 KB of ring: more warps to hide unpack latency
-    int per_cta = budget, ctas_per_sm = 1;
-    {
-        const int half = rt.smem_per_sm / 2 - 1024;
-        const int avail2 = half - fixed;
-        if (avail2 >= 3 * p.stage_bytes && avail2 >= 48 * 1024) {
-            ctas_per_sm = 2;
-            per_cta = half;
+    int S = 0;
+    for (;;) {
+        p.rows_per_stage = R;
+        p.stage_bytes = (R * p.row_bytes + 16 + 127) & ~127;
+        for (S = GEMV_MAX_STAGES; S >= 2; --S) {
+            const int combine = wpr > 1 ? (((S * R * wpr * B + S * R) * 4 + 127) & ~127) : 0;
+            if (128 + p.act_bytes + combine + S * p.stage_bytes <= budget) {
+                plan.smem = (size_t)128 + p.act_bytes + combine + (size_t)S * p.stage_bytes;
+                break;
+            }
         }
+        // large batches leave little room beside their activations: hold fewer rows than one pass of all warps
+        if (S >= 2 || R <= p.row_align || (R / 2) % p.row_align != 0) break;
+        R /= 2;
     }
-    int S = (per_cta - fixed) / p.stage_bytes;
-    if (S > GEMV_MAX_STAGES) S = GEMV_MAX_STAGES;
+    if (S < 2) return plan;  // does not fit: simple kernel
     p.nstages = S;
-    plan.smem = (size_t)fixed + (size_t)S * p.stage_bytes;
     const long long units = (N + p.row_align - 1) / p.row_align;
-    long long grid = (long long)rt.sm_count * ctas_per_sm;
+    long long grid = rt.sm_count;
     if (grid > units) grid = units;
     if (grid < 1) grid = 1;
     plan.grid = (int)grid;
+    // register-resident activations: 40 registers per slot and activation row
+    plan.nreg = (B == 1 && ipl <= 2) ? ipl : ((B == 2 && ipl == 1) ? 1 : 0);
     plan.staged = true;
     return plan;
 }
@@ -664,9 +801,9 @@ static inline cudaError_t launch_gemv_kernel(Kern kernel, int grid, int block, s
     return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
-template <int TYPE, int B, typename dst_t, int ACT, typename act_t>
-static inline int launch_staged(const GemvPlan& plan, cudaStream_t s) {
-    auto kernel = gemv_staged_kernel<TYPE, B, dst_t, ACT, act_t>;
+template <int TYPE, int B, typename dst_t, int ACT, typename act_t, int NREG>
+static inline int launch_staged_n(const GemvPlan& plan, cudaStream_t s) {
+    auto kernel = gemv_staged_kernel<TYPE, B, dst_t, ACT, act_t, NREG>;
     static bool configured = false;  // per instantiation; the attribute is set on the first launch
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -675,6 +812,13 @@ static inline int launch_staged(const GemvPlan& plan, cudaStream_t s) {
         configured = true;
     }
     return (int)launch_gemv_kernel(kernel, plan.grid, GEMV_THREADS, plan.smem, s, plan.p.use_pdl != 0, plan.p);
+}
+
+template <int TYPE, int B, typename dst_t, int ACT, typename act_t>
+static inline int launch_staged(const GemvPlan& plan, cudaStream_t s) {
+    if (B == 1 && plan.nreg == 2) return launch_staged_n<TYPE, B, dst_t, ACT, act_t, (B == 1 ? 2 : 0)>(plan, s);
+    if (B <= 2 && plan.nreg == 1) return launch_staged_n<TYPE, B, dst_t, ACT, act_t, (B <= 2 ? 1 : 0)>(plan, s);
+    return launch_staged_n<TYPE, B, dst_t, ACT, act_t, 0>(plan, s);
 }
 
 template <int TYPE, int B, typename dst_t>
@@ -687,6 +831,7 @@ static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int 
     plan.p.stride_act = stride_act;
     plan.p.stride_dst = stride_dst;
     plan.p.status = status_ptr();
+    plan.p.trace = trace_slot();
     if (plan.staged) {
         if (act_mode == ACT_Q8_1) return launch_staged<TYPE, B, dst_t, ACT_Q8_1, float>(plan, s);
         // raw activations have the output's type
@@ -732,7 +877,7 @@ static inline int gemv_type_dispatch(int dst_elem, const void* vx, const void* a
 
 // The reference's launcher symbols for one type (crates/inference-quant/src/gguf/ffi.rs:846-878); stride_col_y is in
 // Q8_1 blocks. Launchers return nothing, as the reference's: a failed launch surfaces at the caller's next checked
-// CUDA call, and is also kept for b200q_last_launch_status().
+// CUDA call, and is also kept for b200q_take_launch_status().
 #define B200Q_DEFINE_GEMV_TYPE(tag, TYPE)                                                                              \
     namespace b200q {                                                                                                  \
     int gemv_##tag(int dst_elem, const void* vx, const void* act, void* dst, int K, int N, int stride_act,             \

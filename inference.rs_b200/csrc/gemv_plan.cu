@@ -12,5 +12,7 @@ void gemv_describe(int type, int K, int N, int b, int* out) {
     out[5] = plan.p.warps_per_row;
     out[6] = plan.p.stage_bytes;
     out[7] = plan.p.row_align;
+    out[8] = plan.p.items_per_lane;
+    out[9] = plan.nreg;
 }
 }  // namespace b200q

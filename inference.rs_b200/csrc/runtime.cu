@@ -8,7 +8,7 @@ namespace b200q {
 
 __device__ unsigned int g_status_word[4] = {0, 0, 0, 0};
 
-static RuntimeInfo g_rt = {0, 0, 0, 0, 0, 24 * 1024};
+static RuntimeInfo g_rt = {0, 0, 0, 0, 0, 36 * 1024};
 static std::atomic<int> g_launch_status{0};
 
 static void query_device() {
@@ -51,6 +51,20 @@ unsigned int* status_ptr() {
         cached[dev] = static_cast<unsigned int*>(p);
     }
     return cached[dev];
+}
+
+static unsigned long long* g_trace = nullptr;
+static int g_trace_records = 0;
+static std::atomic<int> g_trace_next{0};
+void set_trace_buffer(unsigned long long* dev, int records) {
+    g_trace = dev;
+    g_trace_records = records;
+    g_trace_next = 0;
+}
+unsigned long long* trace_slot() {
+    if (g_trace == nullptr || g_trace_records <= 0) return nullptr;
+    const int i = g_trace_next.fetch_add(1) % g_trace_records;
+    return g_trace + (size_t)i * 16;
 }
 
 int note_launch_status(int status) {

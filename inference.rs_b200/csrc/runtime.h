@@ -25,6 +25,9 @@ struct RuntimeInfo {
 const RuntimeInfo& runtime_info();
 RuntimeInfo& runtime_info_mut();
 unsigned int* status_ptr();          // device address of the status word of the current device (cached)
+// diagnostics: when a trace buffer is set, every GEMV launch gets the next 16-slot record of it (wrapping)
+void set_trace_buffer(unsigned long long* dev, int records);
+unsigned long long* trace_slot();
 int note_launch_status(int status);  // remembers the first non-zero status; returns its argument
 int take_launch_status();            // returns and clears it
 

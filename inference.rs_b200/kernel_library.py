@@ -40,8 +40,9 @@ SYMBOLS.update({
     "b200q_device_status": ([C.POINTER(C.c_uint * 4)], _i32),
     "b200q_reset_device_status": ([], _i32),
     "b200q_take_launch_status": ([], _i32),
+    "b200q_set_trace_buffer": ([_vp, _i32], _i32),
     "b200q_gemv": ([_i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp], _i32),
-    "b200q_gemv_plan": ([_i32, _i32, _i32, _i32, C.POINTER(_i32 * 8)], _i32),
+    "b200q_gemv_plan": ([_i32, _i32, _i32, _i32, C.POINTER(_i32 * 10)], _i32),
 })
 DATA_SYMBOLS = ["inference_kernel_build_id"]
 

@@ -98,9 +98,10 @@ def gemv(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.
 
 
 def gemv_plan(dtype: GgmlDType, k: int, n: int, b: int) -> dict:
-    out = (C.c_int * 8)()
+    out = (C.c_int * 10)()
     kl.check(kl.library().b200q_gemv_plan(int(dtype), k, n, b, C.byref(out)), "b200q_gemv_plan")
-    keys = ("staged", "grid", "smem", "stages", "rows_per_stage", "warps_per_row", "stage_bytes", "row_align")
+    keys = ("staged", "grid", "smem", "stages", "rows_per_stage", "warps_per_row", "stage_bytes", "row_align",
+            "items_per_lane", "reg_slots")
     return dict(zip(keys, (int(v) for v in out)))
 
 

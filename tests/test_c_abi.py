@@ -68,7 +68,9 @@ def test_gemv_plans_respect_hardware_limits(tag, k, n, b):
     assert plan["smem"] <= 227 * 1024
     assert 2 <= plan["stages"] <= 8
     assert plan["rows_per_stage"] % plan["row_align"] == 0
-    assert (plan["rows_per_stage"] * plan["warps_per_row"]) % 8 == 0 or plan["warps_per_row"] == 1
+    assert (plan["rows_per_stage"] * plan["warps_per_row"]) % 16 == 0
+    items = k // 128
+    assert plan["warps_per_row"] * 32 * plan["items_per_lane"] >= items
     assert plan["stage_bytes"] >= plan["rows_per_stage"] * dt.row_bytes(k) + 16
     assert (plan["row_align"] * dt.row_bytes(k)) % 16 == 0
-    assert 1 <= plan["grid"] <= 148 * 2
+    assert 1 <= plan["grid"] <= 148
