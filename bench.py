@@ -280,6 +280,7 @@ def main():
     ap.add_argument("--two-launch", action="store_true", help="--single: quantize launcher + GEMV launcher instead of one launch")
     ap.add_argument("--pdl", type=int, default=None, help="programmatic dependent launch on/off")
     ap.add_argument("--stage-bytes", type=int, default=None, help="GEMV planner: target bytes per shared-memory stage")
+    ap.add_argument("--ctas-per-sm", type=int, default=None, help="GEMV planner: CTAs of one grid per SM (1 or 2)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -293,6 +294,9 @@ def main():
     if args.pdl is not None:
         from inference_rs_b200 import ops as _ops
         _ops.set_option("pdl", args.pdl)
+    if args.ctas_per_sm is not None:
+        from inference_rs_b200 import ops as _ops
+        _ops.set_option("gemv_ctas_per_sm", args.ctas_per_sm)
     if args.stage_bytes is not None:
         from inference_rs_b200 import ops as _ops
         _ops.set_option("gemv_stage_bytes", args.stage_bytes)

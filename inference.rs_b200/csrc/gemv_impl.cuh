@@ -28,7 +28,8 @@ namespace b200q {
 constexpr int GEMV_CONSUMER_WARPS = 16;
 constexpr int GEMV_CONSUMER_THREADS = GEMV_CONSUMER_WARPS * 32;
 constexpr int GEMV_THREADS = GEMV_CONSUMER_THREADS + 32;
-constexpr int GEMV_MAX_STAGES = 8;
+constexpr int GEMV_MAX_STAGES = 16;
+constexpr int GEMV_BARRIER_BYTES = 2 * GEMV_MAX_STAGES * 8;  // full[] and empty[]
 constexpr int ACT_REC_BYTES = 80;  // i8 q[64]; f32 d[2]; f32 ds[2]
 
 enum ActMode : int { ACT_Q8_1 = 0, ACT_RAW_Q8_1 = 1, ACT_RAW_CPU = 2 };
@@ -45,6 +46,8 @@ struct GemvParams {
     int warps_per_row;   // WPR: power of two <= 16; 16 / WPR row groups work on different rows at once
     int items_per_lane;  // IPL: item slots of one lane: item = (warp % WPR) * 32 + lane + j * 32 * WPR, j < IPL
     int row_align;       // rows per 16-byte-aligned unit of the byte stream
+    int units_per_cta;   // CTA c owns units [c * q + min(c, r), ...) with q = units_per_cta, r = units_extra
+    int units_extra;
     int nstages;
     int stage_bytes;     // multiple of 128
     int act_bytes;       // bytes of activation records
@@ -69,10 +72,27 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // Activation staging (generic stores into shared memory; read back with explicit shared loads)
 // ---------------------------------------------------------------------------------------------
 
+// The first unit of activation data of each thread, loaded at the very top of the kernel: a Q8_1 block (9 words) or
+// 8 raw values.
+template <int ACT, typename act_t> struct ActPrefetch;
+template <typename act_t> struct ActPrefetch<ACT_Q8_1, act_t> {
+    uint32_t v[9];
+    __device__ __forceinline__ void issue(const void* act, int B, int K, int stride_blocks, bool, int tid) {
+        const int nblk = K / 32;
+        if (tid < B * nblk) {
+            const int b = tid / nblk, kb = tid - b * nblk;
+            const uint32_t* src =
+                reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(act) + ((size_t)b * stride_blocks + kb) * Q8_1_BYTES);
+#pragma unroll
+            for (int j = 0; j < 9; ++j) v[j] = src[j];
+        }
+    }
+};
+
 // From Q8_1 blocks: one thread per 32-value block.
-template <int B>
+template <int B, typename Pre>
 __device__ __forceinline__ void stage_acts_q8_1(uint8_t* acts, const uint8_t* vy, int K, int stride_blocks, int tid,
-                                                int nthreads) {
+                                                int nthreads, const Pre& pre) {
     const int nblk = K / 32;
     const int nrec = K / 64;
     for (int i = tid; i < B * nblk; i += nthreads) {
@@ -81,8 +101,13 @@ __device__ __forceinline__ void stage_acts_q8_1(uint8_t* acts, const uint8_t* vy
         uint8_t* rec = acts + ((size_t)b * nrec + (kb >> 1)) * ACT_REC_BYTES;
         const int h = kb & 1;
         uint32_t v[9];
+        if (i == tid) {
 #pragma unroll
-        for (int j = 0; j < 9; ++j) v[j] = src[j];
+            for (int j = 0; j < 9; ++j) v[j] = pre.v[j];
+        } else {
+#pragma unroll
+            for (int j = 0; j < 9; ++j) v[j] = src[j];
+        }
         int sum = 0;
         uint32_t* qdst = reinterpret_cast<uint32_t*>(rec + 32 * h);
 #pragma unroll
@@ -142,6 +167,63 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, boo
     }
 }
 
+// Raw activations: up to PRE_UNITS chunks of 8 values per thread, kept as raw bits so that nothing waits for the
+// loads until the values are used.
+constexpr int PRE_UNITS = 4;
+template <int ACT, typename act_t> struct ActPrefetch {
+    static constexpr int WORDS = sizeof(act_t) * 2;  // 32-bit words per chunk of 8 values
+    uint32_t raw[PRE_UNITS][WORDS];
+    __device__ __forceinline__ void issue(const void* act, int B, int K, int stride_elems, bool vec, int tid) {
+        const int chunks = K / 8;
+#pragma unroll
+        for (int u = 0; u < PRE_UNITS; ++u) {
+            const int i = tid + u * GEMV_CONSUMER_THREADS;
+            if (i < B * chunks) {
+                const int b = i / chunks, c = i - b * chunks;
+                const act_t* src = reinterpret_cast<const act_t*>(act) + (size_t)b * stride_elems + 8 * c;
+                if (vec) {
+#pragma unroll
+                    for (int q = 0; q < WORDS / 4; ++q) {
+                        const uint4 t = reinterpret_cast<const uint4*>(src)[q];
+                        raw[u][4 * q] = t.x; raw[u][4 * q + 1] = t.y; raw[u][4 * q + 2] = t.z; raw[u][4 * q + 3] = t.w;
+                    }
+                } else if (sizeof(act_t) == 4) {
+#pragma unroll
+                    for (int q = 0; q < WORDS; ++q) raw[u][q] = reinterpret_cast<const uint32_t*>(src)[q];
+                } else {
+#pragma unroll
+                    for (int q = 0; q < WORDS; ++q) {
+                        const unsigned short lo = reinterpret_cast<const unsigned short*>(src)[2 * q];
+                        const unsigned short hi = reinterpret_cast<const unsigned short*>(src)[2 * q + 1];
+                        raw[u][q] = (uint32_t)lo | ((uint32_t)hi << 16);
+                    }
+                }
+            }
+        }
+    }
+    __device__ __forceinline__ void get(int u, float (&v)[8]) const;
+};
+template <> __device__ __forceinline__ void ActPrefetch<ACT_RAW_Q8_1, float>::get(int u, float (&v)[8]) const {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(raw[u][j]);
+}
+template <> __device__ __forceinline__ void ActPrefetch<ACT_RAW_CPU, float>::get(int u, float (&v)[8]) const {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(raw[u][j]);
+}
+#define B200Q_PREFETCH_GET16(MODE, T, CONV2, T2)                                                        \
+    template <> __device__ __forceinline__ void ActPrefetch<MODE, T>::get(int u, float (&v)[8]) const { \
+        _Pragma("unroll") for (int j = 0; j < 4; ++j) {                                                 \
+            const float2 f = CONV2(*reinterpret_cast<const T2*>(&raw[u][j]));                           \
+            v[2 * j] = f.x;                                                                             \
+            v[2 * j + 1] = f.y;                                                                         \
+        }                                                                                               \
+    }
+B200Q_PREFETCH_GET16(ACT_RAW_Q8_1, __half, __half22float2, __half2)
+B200Q_PREFETCH_GET16(ACT_RAW_CPU, __half, __half22float2, __half2)
+B200Q_PREFETCH_GET16(ACT_RAW_Q8_1, __nv_bfloat16, __bfloat1622float2, __nv_bfloat162)
+B200Q_PREFETCH_GET16(ACT_RAW_CPU, __nv_bfloat16, __bfloat1622float2, __nv_bfloat162)
+
 // From raw rows, quantized here. Each thread takes 8 consecutive values, so 4 lanes share a 32-value block and a warp
 // covers 256 values.
 //   ACT_RAW_Q8_1: the decode quantizer's arithmetic (d = amax / 127 rounded to f16, q = roundf(x / d)): identical to
@@ -150,9 +232,9 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, boo
 //                 per 256 values, iscale = -127 / max, crates/inference-tensor/src/quantized/k_quants.rs:2721-2760) and
 //                 Q8_0 for Q8_0 (per 32, f16 scale, q = round(x * (1 / d)), quantized/mod.rs:43-56). The integer dot
 //                 products then equal the CPU path's exactly.
-template <int B, typename src_t, int TYPE, int MODE>
+template <int B, typename src_t, int TYPE, int MODE, typename Pre>
 __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, int K, int stride_elems, bool vec, int tid,
-                                               int nthreads) {
+                                               int nthreads, const Pre& pre) {
     const int chunks = K / 8;
     const int nrec = K / 64;
     const int lane = tid & 31;
@@ -161,7 +243,12 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
     for (int i = tid; i < B * chunks; i += nthreads) {
         const int b = i / chunks, c = i - b * chunks;
         float v[8];
-        load8<src_t>(x + (size_t)b * stride_elems + 8 * c, vec, v);
+        const int u = (i - tid) / nthreads;
+        if (u == 0) pre.get(0, v);
+        else if (u == 1) pre.get(1, v);
+        else if (u == 2) pre.get(2, v);
+        else if (u == 3) pre.get(3, v);
+        else load8<src_t>(x + (size_t)b * stride_elems + 8 * c, vec, v);
         int q[8];
         float d_used;
         if (PER_256) {
@@ -199,8 +286,19 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
 #pragma unroll
                 for (int j = 0; j < 8; ++j) q[j] = (int)roundf(v[j] * id);
             } else {
+                // roundf(x / d) without eight IEEE divisions: one exact reciprocal, a residual-corrected quotient
+                // (accurate to a couple of ulp), and the exact division only where that quotient lies within 1e-3
+                // of a rounding boundary, so the result is always the one the quantize launcher computes
+                const float rcp = amax == 0.0f ? 0.0f : 1.0f / d;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) q[j] = amax == 0.0f ? 0 : (int)roundf(v[j] / d);
+                for (int j = 0; j < 8; ++j) {
+                    const float q0 = v[j] * rcp;
+                    const float q1 = fmaf(fmaf(-d, q0, v[j]), rcp, q0);
+                    const float qr = rintf(q1);
+                    int qi = (int)qr;
+                    if (fabsf(q1 - qr) > 0.499f) qi = (int)roundf(v[j] / d);
+                    q[j] = amax == 0.0f ? 0 : qi;
+                }
             }
             d_used = __half2float(__float2half_rn(d));
         }
@@ -430,7 +528,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + GEMV_MAX_STAGES;
-    uint8_t* acts = smem + 128;
+    uint8_t* acts = smem + GEMV_BARRIER_BYTES;
     const int S = p.nstages, R = p.rows_per_stage, WPR = p.warps_per_row, IPL = p.items_per_lane;
     // cross-warp combine (WPR > 1): per stage and row, WPR partial sums per activation row and an arrival counter
     float* partial = reinterpret_cast<float*>(acts + p.act_bytes);  // [S][R][WPR][B]
@@ -441,37 +539,56 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     GEMV_TRACE(0);
+    if (p.use_pdl) {
+        grid_launch_dependents();  // the next grid may start its own set-up now
+        if (warp != GEMV_CONSUMER_WARPS) grid_dependency_wait();  // activations come from the previous grid
+    }
+    // the first activation loads go out before anything else: issued after the weight stream has started they
+    // would queue behind megabytes of bulk copies
+    ActPrefetch<ACT, act_t> pre;
+    if (warp != GEMV_CONSUMER_WARPS) pre.issue(p.act, B, p.K, p.stride_act, p.act_vec != 0, tid);
 
-    if (tid == 0) {
+    // this CTA's rows: a contiguous run of 16-byte-aligned units, sizes differing by at most one unit
+    const int cta = blockIdx.x;
+    const int unit0 = cta * p.units_per_cta + min(cta, p.units_extra);
+    const int row0 = unit0 * p.row_align;
+    int row1 = (unit0 + p.units_per_cta + (cta < p.units_extra ? 1 : 0)) * p.row_align;
+    if (row1 > p.N) row1 = p.N;
+    const int nrows = row1 > row0 ? row1 - row0 : 0;
+    const int niter = (nrows + R - 1) / R;
+
+    // The producer thread sets the barriers up and starts the weight stream at once; weights never depend on the
+    // previous grid, so under programmatic dependent launch this runs while that grid is still computing.
+    const bool is_producer = (warp == GEMV_CONSUMER_WARPS);
+    int issued = 0;
+    if (is_producer && lane == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], GEMV_CONSUMER_WARPS);
         }
         mbar_init_fence();
+        if (p.trace != nullptr && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
+            p.trace[(blockIdx.x == 0 ? 0 : 8) + 5] = global_timer_ns();
+        for (; issued < niter && issued < S; ++issued) {
+            const int r = row0 + issued * R;
+            const int rows = min(R, row1 - r);
+            const uint32_t bytes = ((uint32_t)rows * (uint32_t)p.row_bytes + 15u) & ~15u;
+            mbar_arrive_expect_tx(&full[issued], bytes);
+            bulk_copy_g2s(ring + (size_t)issued * p.stage_bytes, p.w + (size_t)r * p.row_bytes, bytes, &full[issued]);
+        }
     }
     for (int i = tid; i < counter_ints; i += GEMV_THREADS) counters[i] = 0;
     __syncthreads();
     GEMV_TRACE(1);
 
-    // this CTA's rows: a contiguous run of 16-byte-aligned units
-    const long long units = (p.N + p.row_align - 1) / p.row_align;
-    const int row0 = (int)(units * blockIdx.x / gridDim.x) * p.row_align;
-    int row1 = (int)(units * (blockIdx.x + 1) / gridDim.x) * p.row_align;
-    if (row1 > p.N) row1 = p.N;
-    const int nrows = row1 > row0 ? row1 - row0 : 0;
-    const int niter = (nrows + R - 1) / R;
-
-    if (warp == GEMV_CONSUMER_WARPS) {
-        // ---------------- producer: one thread streams this CTA's byte range ----------------
+    if (is_producer) {
+        // ---------------- producer: refills stages as the consumers release them ----------------
         if (lane == 0) {
             bool ok = true;
-            int issued = 0;
-            for (int it = 0; it < niter && ok; ++it) {
+            for (int it = issued; it < niter && ok; ++it) {
                 const int s = it % S;
-                if (it >= S) {
-                    ok = mbar_wait_bounded(&empty[s], ((it / S) - 1) & 1);
-                    if (!ok) { record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, it); break; }
-                }
+                ok = mbar_wait_bounded(&empty[s], ((it / S) - 1) & 1);
+                if (!ok) { record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, it); break; }
                 const int r = row0 + it * R;
                 const int rows = min(R, row1 - r);
                 const uint32_t bytes = ((uint32_t)rows * (uint32_t)p.row_bytes + 15u) & ~15u;
@@ -494,14 +611,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
     }
 
     // ---------------- consumers ----------------
-    if (p.use_pdl) grid_dependency_wait();
-    if (ACT == ACT_Q8_1)
-        stage_acts_q8_1<B>(acts, reinterpret_cast<const uint8_t*>(p.act), p.K, p.stride_act, tid, GEMV_CONSUMER_THREADS);
+    if constexpr (ACT == ACT_Q8_1)
+        stage_acts_q8_1<B>(acts, reinterpret_cast<const uint8_t*>(p.act), p.K, p.stride_act, tid, GEMV_CONSUMER_THREADS, pre);
     else
         stage_acts_raw<B, act_t, TYPE, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.stride_act, p.act_vec != 0, tid,
-                                            GEMV_CONSUMER_THREADS);
+                                            GEMV_CONSUMER_THREADS, pre);
+    GEMV_TRACE(6);
     named_bar_sync(1, GEMV_CONSUMER_THREADS);
-    if (p.use_pdl) grid_launch_dependents();
     GEMV_TRACE(2);
 
     const int nrec = p.K / 64;
@@ -530,6 +646,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                 if (item0 + j * item_step < items) areg[b][j].load(acts_addr + b * act_row_bytes, item0 + j * item_step);
     }
 
+    GEMV_TRACE(7);
     bool alive = true;
     for (int it = 0; it < niter; ++it) {
         const int s = it % S;
@@ -541,8 +658,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         const uint32_t st = ring_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
         const int rbase = row0 + it * R;
         const int rows_here = min(R, row1 - rbase);
+        // rows of consecutive stages go to consecutive warp groups, so a stage may hold fewer rows than one pass of
+        // all warps without leaving the same warps idle every time
+        const int rot = (it * R) % rows_per_pass;
+        const int my_slot = row_slot >= rot ? row_slot - rot : row_slot - rot + rows_per_pass;
         for (int pass0 = 0; pass0 < rows_here; pass0 += rows_per_pass) {  // warp-uniform trip count
-            const int r_in = pass0 + row_slot;
+            const int r_in = pass0 + my_slot;
             const bool has_row = r_in < rows_here;
             float acc[B];
 #pragma unroll
@@ -749,6 +870,8 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     if (ipl > 16) return plan;
     const int nrg = GEMV_CONSUMER_WARPS / wpr;
     const int rows_per_pass = nrg * rpw;
+    // rows per stage: whole passes of all warps (every warp visits every stage in order, so a stage that feeds only
+    // some warps would stall the others), about gemv_stage_target bytes, at least one pass
     const int unit = rows_per_pass * p.row_align / gcd_int(rows_per_pass, p.row_align);
     int R = rt.gemv_stage_target / (unit * p.row_bytes) * unit;
     if (R < unit) R = unit;
@@ -756,15 +879,15 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     p.warps_per_row = wpr;
     p.items_per_lane = ipl;
     p.stage_bytes = (R * p.row_bytes + 16 + 127) & ~127;
-    const int budget = rt.smem_optin - 1024;  // 1 KB per CTA is reserved by the system
+    const int budget = rt.smem_optin - 1024;  // one CTA per SM; 1 KB per CTA is reserved by the system
     int S = 0;
     for (;;) {
         p.rows_per_stage = R;
         p.stage_bytes = (R * p.row_bytes + 16 + 127) & ~127;
         for (S = GEMV_MAX_STAGES; S >= 2; --S) {
             const int combine = wpr > 1 ? (((S * R * wpr * B + S * R) * 4 + 127) & ~127) : 0;
-            if (128 + p.act_bytes + combine + S * p.stage_bytes <= budget) {
-                plan.smem = (size_t)128 + p.act_bytes + combine + (size_t)S * p.stage_bytes;
+            if (GEMV_BARRIER_BYTES + p.act_bytes + combine + S * p.stage_bytes <= budget) {
+                plan.smem = (size_t)GEMV_BARRIER_BYTES + p.act_bytes + combine + (size_t)S * p.stage_bytes;
                 break;
             }
         }
@@ -779,6 +902,8 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     if (grid > units) grid = units;
     if (grid < 1) grid = 1;
     plan.grid = (int)grid;
+    p.units_per_cta = (int)(units / grid);
+    p.units_extra = (int)(units % grid);
     // register-resident activations: 40 registers per slot and activation row
     plan.nreg = (B == 1 && ipl <= 2) ? ipl : ((B == 2 && ipl == 1) ? 1 : 0);
     plan.staged = true;

@@ -66,9 +66,8 @@ def test_gemv_plans_respect_hardware_limits(tag, k, n, b):
     if not plan["staged"]:
         return
     assert plan["smem"] <= 227 * 1024
-    assert 2 <= plan["stages"] <= 8
+    assert 2 <= plan["stages"] <= 16
     assert plan["rows_per_stage"] % plan["row_align"] == 0
-    assert (plan["rows_per_stage"] * plan["warps_per_row"]) % 16 == 0
     items = k // 128
     assert plan["warps_per_row"] * 32 * plan["items_per_lane"] >= items
     assert plan["stage_bytes"] >= plan["rows_per_stage"] * dt.row_bytes(k) + 16

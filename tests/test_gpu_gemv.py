@@ -148,7 +148,7 @@ def test_batch_rows_are_independent(type_id):
     try:
         other = ops.gemv(DT[type_id], w_dev, x, n)
     finally:
-        ops.set_option("gemv_stage_bytes", 24 * 1024)
+        ops.set_option("gemv_stage_bytes", 40 * 1024)
     torch.cuda.synchronize()
     np.testing.assert_allclose(as_f32_numpy(other), as_f32_numpy(full), rtol=2 ** -7, atol=1e-3)
     assert_device_ok()
