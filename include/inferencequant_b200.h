@@ -123,6 +123,13 @@ int b200q_set_trace_buffer(void* dev, int records);
 int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
                int b_size, int act_quant, void* stream);
 
+/* Prefill GEMM on the tcgen05 tensor cores: y[M][ldy] = x[M][ldx] . W[N][K]^T with x, y of element type `elem`
+ * (B200Q_BF16 or B200Q_F16), f32 accumulation in tensor memory. Weights are dequantized tile by tile inside the
+ * kernel; activations are not quantized. Needs K a multiple of 64, x 16-byte aligned with ldx * 2 a multiple of 16.
+ * Host-side counterpart in the reference: fast_mmq::plain (crates/inference-quant/src/gguf/fast_mmq.rs:604-715,842-845),
+ * which quantizes activations to Q8_1 blocks and runs launch_mmq_gguf_<type> (ffi.rs:911-927). */
+int b200q_gemm(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* stream);
+
 /* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,
  *        item slots per lane, register-resident slots} */
 int b200q_gemv_plan(int type, int K, int N, int b_size, int out[10]);

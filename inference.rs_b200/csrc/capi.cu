@@ -11,6 +11,7 @@ int gemv_q4_k(int, const void*, const void*, void*, int, int, int, int, int, int
 int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
 int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
 void gemv_describe(int type, int K, int N, int b, int* out);
+int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s);
 
 static thread_local char t_error[256] = "";
 int set_error(int code, const char* msg) {
@@ -103,6 +104,18 @@ int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int 
     if (rc == B200Q_ERR_UNSUPPORTED)
         return set_error(rc, "no one-launch GEMV for this shape or alignment: quantize to Q8_1 and use launch_mmvq_gguf_*_plain");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemv failed");
+    return B200Q_OK;
+}
+
+// Prefill GEMM on the tensor cores: y[M][ldy] = x[M][ldx] . W[N][K]^T, x and y of element type `elem` (bf16 or f16).
+int b200q_gemm(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* stream) {
+    if (!w || !x || !y) return set_error(B200Q_ERR_INVALID, "null pointer");
+    if (type_block_bytes(type) == 0) return set_error(B200Q_ERR_UNSUPPORTED, "weight type is not Q8_0, Q4_K or Q6_K");
+    if (elem != ELEM_BF16 && elem != ELEM_F16) return set_error(B200Q_ERR_UNSUPPORTED, "b200q_gemm takes bf16 or f16 activations");
+    const int rc = gemm_dispatch(type, elem, w, x, y, M, N, K, ldx, ldy, (cudaStream_t)stream);
+    if (rc == B200Q_ERR_UNSUPPORTED)
+        return set_error(rc, "b200q_gemm needs K a multiple of 64 and of the block size, 16-byte aligned activation rows and Q4_K weights");
+    if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemm failed");
     return B200Q_OK;
 }
 

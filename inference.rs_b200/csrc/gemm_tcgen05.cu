@@ -1,0 +1,492 @@
+// Prefill GEMM: Y[m][n] = sum_k X[m][k] * W[n][k] for packed Q8_0 / Q4_K / Q6_K weights (GGUF layout) and M >= 17
+// bf16 / f16 activation rows, f32 accumulation, output in the activation type. Takes the place of the reference's
+// tiled int8 path `mul_mat_q` (crates/inference-quant/kernels/cuda/mmq_gguf/mmq_gguf.cuh:3632-3875, host side
+// crates/inference-quant/src/gguf/fast_mmq.rs:604-715) with a tile GEMM on the 5th-generation tensor cores:
+//
+//   * A operand = activations, 128 tokens x 64 k per stage, brought in by TMA (cp.async.bulk.tensor, 128-byte swizzle);
+//   * B operand = weights, dequantized by eight warps from the packed blocks straight into the same K-major
+//     128-byte-swizzled shared-memory layout as bf16 / f16 (scale and min folded in f32, one rounding), made visible
+//     to the tensor core with a proxy fence; activations are NOT quantized, so the only error is the weights' own;
+//   * tcgen05.mma (kind::f16, M = 128, N = 128, K = 16) issued by one thread, accumulators in TMEM (one 128-column
+//     block per 128-token sub-tile, 1 or 2 sub-tiles per CTA), completion signalled with tcgen05.commit on mbarriers;
+//   * epilogue: tcgen05.ld 32 lanes x 32 columns per warp, convert, 64-byte stores per token row.
+//
+// Every wait is bounded; a wait that gives up records a code in the device status word, work is skipped, and the
+// kernel still frees its TMEM columns before it returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "runtime.h"
+
+namespace b200q {
+
+constexpr int GEMM_BM = 128;       // tokens per sub-tile = TMEM lanes
+constexpr int GEMM_BN = 128;       // weight rows per tile = TMEM columns per sub-tile
+constexpr int GEMM_BK = 64;        // k per stage: one 128-byte swizzled row of 16-bit elements
+constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_DEQ_WARPS = 8;  // warps 4..11
+constexpr int GEMM_THREADS = 32 * (4 + GEMM_DEQ_WARPS);
+constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;  // 16 KB per sub-tile and stage
+constexpr int GEMM_B_BYTES = GEMM_BN * GEMM_BK * 2;  // 16 KB per stage
+
+struct GemmParams {
+    const uint8_t* w;  // packed weights [N][K / block]
+    void* y;           // [M][ldy]
+    int M, N, K;
+    int ldy;
+    int row_bytes;
+    unsigned int* status;
+};
+
+// ---- tcgen05 / TMA wrappers ------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], 16-bit inputs, f32 accumulate
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread = lane of this warp's TMEM quarter)
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+        "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+// Descriptor fields: start address >> 4 (14 bits), leading byte offset (unused for swizzled K-major, 1),
+// stride byte offset 1024 >> 4 at bit 32, descriptor version 1 at bit 46, layout type SWIZZLE_128B (2) at bit 61.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: f32 accumulator (1 at bit 4), A / B format at bits 7 / 10 (0 = f16, 1 = bf16),
+// both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int fmt, int m, int n) {
+    return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <typename T> struct ElemFormat;  // tcgen05 kind::f16 operand format code
+template <> struct ElemFormat<__half> { static constexpr int value = 0; };
+template <> struct ElemFormat<__nv_bfloat16> { static constexpr int value = 1; };
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One 16-byte chunk (8 elements) of B row r, logical chunk j (k = 8j .. 8j+7) of a stage: swizzled position.
+__device__ __forceinline__ uint32_t b_chunk_addr(uint32_t stage_addr, int r, int j) {
+    return stage_addr + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u + (uint32_t)((j ^ (r & 7)) << 4);
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Dequantization of one unit = 32 consecutive k of one weight row (half h of a 64-wide k block) into 64 bytes of the
+// B stage. The packed blocks are read straight from global memory (L2 serves the re-reads of other token tiles).
+// ---------------------------------------------------------------------------------------------
+template <int N>
+__device__ __forceinline__ void ldg_words_u16aligned(const uint8_t* p, uint32_t (&out)[N]) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t shift = (uint32_t)(a & 2u) * 8u;
+    const uint32_t* base = reinterpret_cast<const uint32_t*>(a & ~(uintptr_t)3);
+    uint32_t w[N + 1];
+#pragma unroll
+    for (int i = 0; i <= N; ++i) w[i] = __ldg(base + i);
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = __funnelshift_r(w[i], w[i + 1], shift);
+}
+__device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p)); }
+
+// byte b (0..255) -> float, exactly, without the conversion unit
+__device__ __forceinline__ float byte_to_float(uint32_t b) { return __uint_as_float(0x4B000000u | b) - 8388608.0f; }
+
+template <typename T>
+__device__ __forceinline__ void store_unit(uint32_t stage_addr, int r, int h, const float (&v)[32]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        sts128(b_chunk_addr(stage_addr, r, 4 * h + i), pack2<T>(v[8 * i], v[8 * i + 1]), pack2<T>(v[8 * i + 2], v[8 * i + 3]),
+               pack2<T>(v[8 * i + 4], v[8 * i + 5]), pack2<T>(v[8 * i + 6], v[8 * i + 7]));
+    }
+}
+
+template <int TYPE> struct Dequant;
+
+// Q4_K: k block kb = chunk c = kb & 3 of superblock kb >> 2; half h is sub-block 2c + h (low / high nibbles of the
+// same 32 bytes). value = d * sc * q - dmin * m (crates/inference-tensor/src/quantized/k_quants.rs:2096-2123).
+template <> struct Dequant<TYPE_Q4_K> {
+    uint4 hdr, q0, q1;
+    __device__ __forceinline__ void load(const uint8_t* row, int kb, int) {
+        const uint8_t* sb = row + (size_t)(kb >> 2) * Q4_K_BYTES;
+        hdr = __ldg(reinterpret_cast<const uint4*>(sb));
+        q0 = __ldg(reinterpret_cast<const uint4*>(sb + 16 + 32 * (kb & 3)));
+        q1 = __ldg(reinterpret_cast<const uint4*>(sb + 32 + 32 * (kb & 3)));
+    }
+    __device__ __forceinline__ void values(int kb, int h, float (&v)[32]) const {
+        const int j = 2 * (kb & 3) + h;
+        uint32_t sc, m;
+        if (j < 4) {
+            sc = ((hdr.y >> (8 * j)) & 0x3fu);
+            m = ((hdr.z >> (8 * j)) & 0x3fu);
+        } else {
+            const int jj = j - 4;
+            const uint32_t lo = (hdr.w >> (8 * jj)) & 0xffu;
+            sc = (lo & 0xfu) | ((((hdr.y >> (8 * jj)) & 0xffu) >> 6) << 4);
+            m = (lo >> 4) | ((((hdr.z >> (8 * jj)) & 0xffu) >> 6) << 4);
+        }
+        const float dl = half_bits_to_float(hdr.x) * byte_to_float(sc);
+        const float ml = half_bits_to_float(hdr.x >> 16) * byte_to_float(m);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const int sh = 4 * h;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) v[4 * i + b] = fmaf(dl, byte_to_float((w[i] >> (8 * b + sh)) & 0xfu), -ml);
+        }
+    }
+};
+
+// Q6_K: k block kb: superblock kb >> 2, half n = (kb & 3) >> 1, pair p = kb & 1; unit h is quarter qd = 2p + h:
+// ql[64n + 32h + l] nibble p, qh[32n + l] bits 2qd, scale[8n + 2qd + l/16]; value = d * sc * (q - 32)
+// (crates/inference-tensor/src/quantized/k_quants.rs:2649-2680).
+template <> struct Dequant<TYPE_Q6_K> {
+    uint32_t ql[8], qh[8];
+    uint32_t sc2, dbits;
+    __device__ __forceinline__ void load(const uint8_t* row, int kb, int h) {
+        const uint8_t* sb = row + (size_t)(kb >> 2) * Q6_K_BYTES;
+        const int n = (kb & 3) >> 1, qd = 2 * (kb & 1) + h;
+        ldg_words_u16aligned<8>(sb + 64 * n + 32 * h, ql);
+        ldg_words_u16aligned<8>(sb + 128 + 32 * n, qh);
+        sc2 = ldg_u16(sb + 192 + 8 * n + 2 * qd);
+        dbits = ldg_u16(sb + 208);
+    }
+    __device__ __forceinline__ void values(int kb, int h, float (&v)[32]) const {
+        const int p = kb & 1, qd = 2 * p + h;
+        const float d = half_bits_to_float(dbits);
+        const float s0 = d * (float)(int)(int8_t)(sc2 & 0xffu), s1 = d * (float)(int)(int8_t)(sc2 >> 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const uint32_t lo = (ql[i] >> (8 * b + 4 * p)) & 0xfu;
+                const uint32_t hi = (qh[i] >> (8 * b + 2 * qd)) & 0x3u;
+                const float q = byte_to_float(lo | (hi << 4)) - 32.0f;
+                v[4 * i + b] = (i < 4 ? s0 : s1) * q;
+            }
+        }
+    }
+};
+
+// Q8_0: unit h of k block kb is block 2 kb + h: f16 d, 32 int8; value = d * q.
+template <> struct Dequant<TYPE_Q8_0> {
+    uint32_t w[9];
+    __device__ __forceinline__ void load(const uint8_t* row, int kb, int h) {
+        ldg_words_u16aligned<9>(row + (size_t)(2 * kb + h) * Q8_0_BYTES, w);  // bytes 0..35 (34 used)
+    }
+    __device__ __forceinline__ void values(int, int, float (&v)[32]) const {
+        const float d = half_bits_to_float(w[0]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t q = __funnelshift_r(w[i], w[i + 1], 16);  // bytes 2 + 4i .. 5 + 4i
+#pragma unroll
+            for (int b = 0; b < 4; ++b) v[4 * i + b] = d * (float)(int)(int8_t)((q >> (8 * b)) & 0xffu);
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// The kernel: one CTA computes a (MT * 128 tokens) x (128 weight rows) tile over the whole K.
+//   warp 0    TMA producer of the activation sub-tiles
+//   warp 1    tcgen05.mma issuer
+//   warp 2    TMEM allocation / release
+//   warps 4+  weight dequantization into the B stages, then the epilogue
+// ---------------------------------------------------------------------------------------------
+struct GemmBarriers {
+    uint64_t full_a[GEMM_STAGES];
+    uint64_t full_b[GEMM_STAGES];
+    uint64_t empty[GEMM_STAGES];
+    uint64_t tmem_full;
+    uint32_t tmem_base;
+    uint32_t failed;
+};
+
+template <int TYPE, typename T, int MT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+    extern __shared__ uint8_t gemm_smem_raw[];
+    // operand stages need 1024-byte alignment for the 128-byte swizzle
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* a_stages = smem;                                        // [S][MT][16 KB]
+    uint8_t* b_stages = smem + GEMM_STAGES * MT * GEMM_A_BYTES;      // [S][16 KB]
+    GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(b_stages + GEMM_STAGES * GEMM_B_BYTES);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * GEMM_BN;
+    const int m0 = blockIdx.y * (MT * GEMM_BM);
+    const int nkb = p.K / GEMM_BK;
+    constexpr uint32_t TMEM_COLS = MT * GEMM_BN;  // 128 or 256: a power of two >= 32
+
+    if (tid == 0) {
+        for (int s = 0; s < GEMM_STAGES; ++s) {
+            mbar_init(&bars->full_a[s], 1);
+            mbar_init(&bars->full_b[s], GEMM_DEQ_WARPS);
+            mbar_init(&bars->empty[s], 1);
+        }
+        mbar_init(&bars->tmem_full, 1);
+        bars->failed = 0;
+        mbar_init_fence();
+    }
+    if (warp == 2) tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % GEMM_STAGES;
+                if (!mbar_wait_bounded(&bars->empty[s], ((kb / GEMM_STAGES) & 1) ^ 1)) {
+                    record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, kb);
+                    ok = false;
+                    break;
+                }
+                mbar_arrive_expect_tx(&bars->full_a[s], MT * GEMM_A_BYTES);
+#pragma unroll
+                for (int t = 0; t < MT; ++t)
+                    tma_load_2d(a_stages + (size_t)(s * MT + t) * GEMM_A_BYTES, &tmap_x, kb * GEMM_BK, m0 + t * GEMM_BM, &bars->full_a[s]);
+                issued = kb + 1;
+            }
+            if (!ok) {  // let every copy already issued land before the CTA may exit
+                for (int kb = max(0, issued - GEMM_STAGES); kb < issued; ++kb)
+                    if (!mbar_wait_bounded(&bars->full_a[kb % GEMM_STAGES], (kb / GEMM_STAGES) & 1)) {
+                        record_failure(p.status, STATUS_WAIT_DRAIN_TIMEOUT, kb);
+                        break;
+                    }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_f16(ElemFormat<T>::value, GEMM_BM, GEMM_BN);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % GEMM_STAGES;
+                const uint32_t ph = (kb / GEMM_STAGES) & 1;
+                if (!mbar_wait_bounded(&bars->full_a[s], ph) || !mbar_wait_bounded(&bars->full_b[s], ph)) {
+                    record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, kb);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint64_t db = make_smem_desc_sw128(smem_u32(b_stages + (size_t)s * GEMM_B_BYTES));
+#pragma unroll
+                for (int t = 0; t < MT; ++t) {
+                    const uint64_t da = make_smem_desc_sw128(smem_u32(a_stages + (size_t)(s * MT + t) * GEMM_A_BYTES));
+#pragma unroll
+                    for (int k = 0; k < GEMM_BK / 16; ++k)  // 16 k = 32 bytes along the swizzled row: +2 in the address field
+                        tc_mma_f16(tmem_base + t * GEMM_BN, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                tc_commit(&bars->empty[s]);  // frees the stage when these MMAs have read it
+            }
+            if (ok) tc_commit(&bars->tmem_full);
+            else bars->failed = 1;
+        }
+    } else if (warp >= 4) {
+        // ---------------- dequantization ----------------
+        const int dt = tid - 128;            // 0..255
+        const int r = dt & (GEMM_BN - 1);    // weight row of the tile
+        const int h = dt >> 7;               // which 32 of the 64 k (warp-uniform)
+        const int wrow = n0 + r;
+        const bool row_ok = wrow < p.N;
+        const uint8_t* rowp = p.w + (size_t)(row_ok ? wrow : 0) * p.row_bytes;
+        Dequant<TYPE> cur, nxt;
+        bool ok = true;
+        if (nkb > 0) cur.load(rowp, 0, h);
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % GEMM_STAGES;
+            if (kb + 1 < nkb) nxt.load(rowp, kb + 1, h);  // software prefetch of the next packed unit
+            float v[32];
+            cur.values(kb, h, v);
+            if (!row_ok) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+            }
+            if (ok && !mbar_wait_bounded(&bars->empty[s], ((kb / GEMM_STAGES) & 1) ^ 1)) {
+                record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, kb);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);  // keep the warp together
+            if (ok) {
+                store_unit<T>(smem_u32(b_stages + (size_t)s * GEMM_B_BYTES), r, h, v);
+                fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->full_b[s]);
+            }
+            cur = nxt;
+        }
+        // ---------------- epilogue ----------------
+        const int t = (warp - 4) >> 2;       // sub-tile of this warp
+        const int quarter = warp & 3;        // TMEM lanes 32 * quarter .. + 31
+        if (t < MT) {
+            if (ok && !mbar_wait_bounded(&bars->tmem_full, 0)) {
+                record_failure(p.status, STATUS_WAIT_MMA_TIMEOUT, 0);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            const int row = m0 + t * GEMM_BM + quarter * 32 + lane;
+            T* yrow = reinterpret_cast<T*>(p.y) + (size_t)row * p.ldy;
+            const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && ((size_t)p.ldy * sizeof(T) % 16 == 0);
+            if (ok) {
+#pragma unroll 1
+                for (int c = 0; c < GEMM_BN / 32; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + t * GEMM_BN + c * 32, acc);
+                    const int col0 = n0 + c * 32;
+                    if (row < p.M) {
+                        if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint4 o;
+                                o.x = pack2<T>(__uint_as_float(acc[8 * q]), __uint_as_float(acc[8 * q + 1]));
+                                o.y = pack2<T>(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3]));
+                                o.z = pack2<T>(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5]));
+                                o.w = pack2<T>(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7]));
+                                *reinterpret_cast<uint4*>(yrow + col0 + 8 * q) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) yrow[col0 + j] = from_float<T>(__uint_as_float(acc[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+template <int TYPE, typename T, int MT>
+static int launch_gemm_mt(const CUtensorMap& map, const GemmParams& p, cudaStream_t s) {
+    auto kernel = gemm_tcgen05_kernel<TYPE, T, MT>;
+    const size_t smem = 1024 + (size_t)GEMM_STAGES * (MT * GEMM_A_BYTES + GEMM_B_BYTES) + sizeof(GemmBarriers);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((unsigned)((p.N + GEMM_BN - 1) / GEMM_BN), (unsigned)((p.M + MT * GEMM_BM - 1) / (MT * GEMM_BM)), 1);
+    kernel<<<grid, GEMM_THREADS, smem, s>>>(map, p);
+    return (int)cudaGetLastError();
+}
+
+template <int TYPE, typename T>
+static int launch_gemm_t(const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (encode == nullptr) return B200Q_ERR_UNSUPPORTED;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldx * sizeof(T)};
+    const cuuint32_t box[2] = {GEMM_BK, GEMM_BM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = ElemFormat<T>::value == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = encode(&map, dt, 2, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return B200Q_ERR_INVALID;
+    GemmParams p{};
+    p.w = static_cast<const uint8_t*>(w);
+    p.y = y;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.ldy = ldy;
+    p.row_bytes = K / type_block_elems(TYPE) * type_block_bytes(TYPE);
+    p.status = status_ptr();
+    // two 128-token sub-tiles per CTA halve the dequantization work per flop; one keeps more CTAs busy on small problems
+    const long long tiles2 = (long long)((N + GEMM_BN - 1) / GEMM_BN) * ((M + 2 * GEMM_BM - 1) / (2 * GEMM_BM));
+    if (M > GEMM_BM && tiles2 >= runtime_info().sm_count) return launch_gemm_mt<TYPE, T, 2>(map, p, s);
+    return launch_gemm_mt<TYPE, T, 1>(map, p, s);
+}
+
+int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % GEMM_BK != 0 || K % type_block_elems(type) != 0) return B200Q_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || ((size_t)ldx * 2) % 16 != 0) return B200Q_ERR_UNSUPPORTED;
+    if (type == TYPE_Q4_K && reinterpret_cast<uintptr_t>(w) % 16 != 0) return B200Q_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(w) % 2 != 0) return B200Q_ERR_UNSUPPORTED;
+#define B200Q_GEMM_CASE(TYPE)                                                                                     \
+    if (type == TYPE) {                                                                                           \
+        if (elem == ELEM_BF16) return launch_gemm_t<TYPE, __nv_bfloat16>(w, x, y, M, N, K, ldx, ldy, s);          \
+        if (elem == ELEM_F16) return launch_gemm_t<TYPE, __half>(w, x, y, M, N, K, ldx, ldy, s);                  \
+        return B200Q_ERR_UNSUPPORTED;                                                                             \
+    }
+    B200Q_GEMM_CASE(TYPE_Q4_K)
+    B200Q_GEMM_CASE(TYPE_Q6_K)
+    B200Q_GEMM_CASE(TYPE_Q8_0)
+#undef B200Q_GEMM_CASE
+    return B200Q_ERR_UNSUPPORTED;
+}
+
+}  // namespace b200q

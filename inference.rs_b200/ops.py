@@ -97,6 +97,16 @@ def gemv(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.
     return dst
 
 
+def gemm(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """`b200q_gemm`: prefill tile GEMM on the tensor cores. x [m, k] bf16/f16 -> [m, n] of x's dtype."""
+    _require_cuda(w, x)
+    m, k = x.shape
+    y = torch.empty((m, n), dtype=x.dtype, device=x.device) if out is None else out
+    kl.check(kl.library().b200q_gemm(int(dtype), elem_of(x.dtype), w.data_ptr(), x.data_ptr(), y.data_ptr(), m, n, k,
+                                     x.stride(0), y.stride(0), _stream()), "b200q_gemm")
+    return y
+
+
 def gemv_plan(dtype: GgmlDType, k: int, n: int, b: int) -> dict:
     out = (C.c_int * 10)()
     kl.check(kl.library().b200q_gemv_plan(int(dtype), k, n, b, C.byref(out)), "b200q_gemv_plan")
