@@ -184,6 +184,41 @@ def run_single(args):
           flush=True)
 
 
+def run_gemm_single(args):
+    """--gemm TYPE K N M: one prefill GEMM shape; prints one JSON line with TFLOP/s against the measured bf16 peak."""
+    import torch
+
+    import inference_rs_b200 as pkg
+    from inference_rs_b200 import ops
+
+    tname, k, n, m = args.gemm[0], int(args.gemm[1]), int(args.gemm[2]), int(args.gemm[3])
+    dt = {"q4_k": pkg.GgmlDType.Q4K, "q6_k": pkg.GgmlDType.Q6K, "q8_0": pkg.GgmlDType.Q8_0}[tname]
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    w = random_blocks_device(torch, dt, n, k, gen)
+    x = torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            ops.gemm(dt, w, x, n, out=y)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            ops.gemm(dt, w, x, n, out=y)
+        e1.record(stream)
+        stream.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / args.steps
+    tflops = 2.0 * m * n * k / us / 1e6
+    peak = 1647.9
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        peak = float(json.load(open(p))["bf16_tflops"])
+    print(json.dumps({"gemm": tname, "k": k, "n": n, "m": m, "us": us, "TFLOPs": tflops, "frac_of_measured_bf16": tflops / peak,
+                      "device_status": list(pkg.kernel_library.device_status())}), flush=True)
+
+
 def cpu_chain_sample(model, threads, seconds_budget=12.0):
     """Times the CPU oracle on one layer's projections plus the output head at batch 1 and scales to a token.
     Returns (tok/s, description)."""
@@ -276,6 +311,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time every shape of the decode sweep")
     ap.add_argument("--single", nargs=4, metavar=("TYPE", "K", "N", "B"), help="time one GEMV shape only (q4_k|q6_k|q8_0)")
+    ap.add_argument("--gemm", nargs=4, metavar=("TYPE", "K", "N", "M"), help="time one prefill GEMM shape only")
     ap.add_argument("--copies", type=int, default=0, help="--single: number of rotating weight copies")
     ap.add_argument("--two-launch", action="store_true", help="--single: quantize launcher + GEMV launcher instead of one launch")
     ap.add_argument("--pdl", type=int, default=None, help="programmatic dependent launch on/off")
@@ -302,6 +338,9 @@ def main():
         _ops.set_option("gemv_stage_bytes", args.stage_bytes)
     if args.single:
         run_single(args)
+        return
+    if args.gemm:
+        run_gemm_single(args)
         return
 
     import torch

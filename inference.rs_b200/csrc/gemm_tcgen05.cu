@@ -134,6 +134,10 @@ __device__ __forceinline__ uint32_t ldg_u16(const uint8_t* p) { return (uint32_t
 
 // byte b (0..255) -> float, exactly, without the conversion unit
 __device__ __forceinline__ float byte_to_float(uint32_t b) { return __uint_as_float(0x4B000000u | b) - 8388608.0f; }
+// byte `idx` of w as the float 2^23 + byte (one byte-permute); subtract 2^23 (+ an offset) to get the value
+template <int idx> __device__ __forceinline__ float byte_as_magic(uint32_t w) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650 | idx));
+}
 
 template <typename T>
 __device__ __forceinline__ void store_unit(uint32_t stage_addr, int r, int h, const float (&v)[32]) {
@@ -174,8 +178,11 @@ template <> struct Dequant<TYPE_Q4_K> {
         const int sh = 4 * h;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-#pragma unroll
-            for (int b = 0; b < 4; ++b) v[4 * i + b] = fmaf(dl, byte_to_float((w[i] >> (8 * b + sh)) & 0xfu), -ml);
+            const uint32_t nib = (w[i] >> sh) & 0x0f0f0f0fu;  // four quants, one per byte
+            v[4 * i + 0] = fmaf(dl, byte_as_magic<0>(nib) - 8388608.0f, -ml);
+            v[4 * i + 1] = fmaf(dl, byte_as_magic<1>(nib) - 8388608.0f, -ml);
+            v[4 * i + 2] = fmaf(dl, byte_as_magic<2>(nib) - 8388608.0f, -ml);
+            v[4 * i + 3] = fmaf(dl, byte_as_magic<3>(nib) - 8388608.0f, -ml);
         }
     }
 };
@@ -200,13 +207,13 @@ template <> struct Dequant<TYPE_Q6_K> {
         const float s0 = d * (float)(int)(int8_t)(sc2 & 0xffu), s1 = d * (float)(int)(int8_t)(sc2 >> 8);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const uint32_t lo = (ql[i] >> (8 * b + 4 * p)) & 0xfu;
-                const uint32_t hi = (qh[i] >> (8 * b + 2 * qd)) & 0x3u;
-                const float q = byte_to_float(lo | (hi << 4)) - 32.0f;
-                v[4 * i + b] = (i < 4 ? s0 : s1) * q;
-            }
+            // four 6-bit quants, one per byte: low nibble | two high bits << 4
+            const uint32_t q4 = ((ql[i] >> (4 * p)) & 0x0f0f0f0fu) | (((qh[i] >> (2 * qd)) & 0x03030303u) << 4);
+            const float sc = i < 4 ? s0 : s1;
+            v[4 * i + 0] = sc * (byte_as_magic<0>(q4) - 8388640.0f);  // 2^23 + 32
+            v[4 * i + 1] = sc * (byte_as_magic<1>(q4) - 8388640.0f);
+            v[4 * i + 2] = sc * (byte_as_magic<2>(q4) - 8388640.0f);
+            v[4 * i + 3] = sc * (byte_as_magic<3>(q4) - 8388640.0f);
         }
     }
 };
@@ -221,9 +228,12 @@ template <> struct Dequant<TYPE_Q8_0> {
         const float d = half_bits_to_float(w[0]);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const uint32_t q = __funnelshift_r(w[i], w[i + 1], 16);  // bytes 2 + 4i .. 5 + 4i
-#pragma unroll
-            for (int b = 0; b < 4; ++b) v[4 * i + b] = d * (float)(int)(int8_t)((q >> (8 * b)) & 0xffu);
+            // bytes 2 + 4i .. 5 + 4i, flipped to unsigned (q + 128)
+            const uint32_t q = __funnelshift_r(w[i], w[i + 1], 16) ^ 0x80808080u;
+            v[4 * i + 0] = d * (byte_as_magic<0>(q) - 8388736.0f);  // 2^23 + 128
+            v[4 * i + 1] = d * (byte_as_magic<1>(q) - 8388736.0f);
+            v[4 * i + 2] = d * (byte_as_magic<2>(q) - 8388736.0f);
+            v[4 * i + 3] = d * (byte_as_magic<3>(q) - 8388736.0f);
         }
     }
 };
