@@ -7,3 +7,4 @@ every operation raises if the library is missing.
 from . import kernel_library  # noqa: F401
 from .kernel_library import KernelLibraryError, library  # noqa: F401
 from .dtypes import GgmlDType  # noqa: F401
+from .qmatmul import GgufMatMul, QMatMul, QTensor  # noqa: F401

@@ -1,0 +1,141 @@
+"""Host-side mirror of the reference's quantized-matmul operator for this path: `QTensor`, `QMatMul` and
+`GgufMatMul` with the same names, argument meaning and error behaviour, on torch device memory.
+
+Reference: `QTensor` / `QMatMul` (crates/inference-tensor/src/quantized/mod.rs:85-120,1117-1187,1625-1647),
+`GgufMatMul::forward` and its dispatch (crates/inference-quant/src/gguf/mod.rs:435-571), the row-count policy of
+`fast_mmvq::plain` / `fast_mmq::plain` (crates/inference-quant/src/gguf/fast_mmvq.rs:84-134,477-665,
+fast_mmq.rs:604-715). Every forward runs the CUDA kernels of the C-ABI library; there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import ops
+from .dtypes import MATRIX_ROW_PADDING, GgmlDType, pad
+
+MMVQ_MAX_BATCH = 8  # rows the decode GEMV launchers take (fast_mmvq.rs:84)
+
+
+class QTensor:
+    """Packed GGUF blocks of a `[n, k]` weight on a CUDA device (rows contiguous, then the reference's padding)."""
+
+    def __init__(self, data: torch.Tensor, dtype: GgmlDType, shape: tuple[int, int]):
+        n, k = shape
+        if k % dtype.block_size:
+            # mod.rs:872-884: the last dimension must hold whole blocks
+            raise ValueError(f"quantized tensor last dim {k} is not a multiple of the {dtype.name} block size {dtype.block_size}")
+        need = n * dtype.row_bytes(k)
+        if data.dtype != torch.uint8 or data.numel() < need:
+            raise ValueError(f"{dtype.name} tensor of shape {shape} needs {need} bytes, got {data.numel()} of {data.dtype}")
+        self.data, self.dtype, self.shape = data, dtype, (n, k)
+
+    @classmethod
+    def from_packed(cls, packed, dtype: GgmlDType, shape: tuple[int, int], device="cuda") -> "QTensor":
+        """From host bytes (numpy uint8 or torch CPU tensor), uploaded with the trailing padding."""
+        return cls(ops.upload_weights(packed, dtype, device), dtype, shape)
+
+    @property
+    def storage_size_in_bytes(self) -> int:
+        return self.shape[0] * self.dtype.row_bytes(self.shape[1])
+
+    def packed_bytes(self) -> torch.Tensor:
+        """The blocks without the padding."""
+        return self.data[: self.storage_size_in_bytes]
+
+    @property
+    def device(self) -> torch.device:
+        return self.data.device
+
+
+class QMatMul:
+    """`y = x @ W^T` for a quantized `W`; x `[..., k]` contiguous -> y `[..., n]` in x's dtype (mod.rs:1625-1647)."""
+
+    def __init__(self, qtensor: QTensor):
+        self.qtensor = qtensor
+
+    @classmethod
+    def from_qtensor(cls, qtensor: QTensor) -> "QMatMul":
+        return cls(qtensor)
+
+    def forward(self, xs: torch.Tensor, act_quant: int = ops.ACT_QUANT_Q8_1) -> torch.Tensor:
+        n, k = self.qtensor.shape
+        if xs.dim() < 2:
+            raise ValueError(f"input tensor has only one dimension {tuple(xs.shape)}")
+        if not xs.is_contiguous():
+            raise ValueError(f"input tensor is not contiguous {tuple(xs.shape)}")
+        if xs.shape[-1] != k:
+            raise ValueError(f"input tensor {tuple(xs.shape)} incompatible with {(n, k)}")
+        if xs.device != self.qtensor.device:
+            raise ValueError(f"input on {xs.device}, weights on {self.qtensor.device}")
+        x2 = xs.reshape(-1, k)
+        y = _forward_rows(self.qtensor, x2, act_quant)
+        return y.reshape(*xs.shape[:-1], n)
+
+    __call__ = forward
+
+
+def prefers_mmvq(rows: int) -> bool:
+    """Decode GEMV for up to MMVQ_MAX_BATCH rows, the prefill GEMM above (fast_mmvq.rs:96-134 collapses to this once the
+    small-batch tensor-core matvec is not in play)."""
+    return rows <= MMVQ_MAX_BATCH
+
+
+def _forward_rows(w: QTensor, x: torch.Tensor, act_quant: int) -> torch.Tensor:
+    n, k = w.shape
+    rows = x.shape[0]
+    if rows == 0:
+        return torch.empty((0, n), dtype=x.dtype, device=x.device)
+    if prefers_mmvq(rows):
+        if k % 128 == 0:
+            return ops.gemv(w.dtype, w.data, x, n, act_quant=act_quant)
+        # shapes the one-launch kernel declines: the reference's own two-launch protocol
+        vy = ops.quantize_q8_1(x, pad(k, MATRIX_ROW_PADDING))
+        return ops.mmvq_plain(w.dtype, w.data, vy, n, k, rows, x.dtype)
+    if x.dtype in (torch.bfloat16, torch.float16) and k % 64 == 0:
+        return ops.gemm(w.dtype, w.data, x, n)
+    if x.dtype == torch.float32 and k % 64 == 0:
+        # the tensor-core path takes 16-bit activations; f32 inputs are narrowed as the reference narrows them for
+        # its own CUDA path (crates/inference-quant/src/gguf/mod.rs:667-691 keeps bf16 when given bf16)
+        return ops.gemm(w.dtype, w.data, x.to(torch.bfloat16), n).to(torch.float32)
+    # K not a multiple of 64 (Q8_0 only): batches of the GEMV launcher
+    outs = []
+    for i in range(0, rows, MMVQ_MAX_BATCH):
+        xb = x[i:i + MMVQ_MAX_BATCH].contiguous()
+        vy = ops.quantize_q8_1(xb, pad(k, MATRIX_ROW_PADDING))
+        outs.append(ops.mmvq_plain(w.dtype, w.data, vy, n, k, xb.shape[0], x.dtype))
+    return torch.cat(outs, 0)
+
+
+class GgufMatMul:
+    """The `QuantMethod` of GGUF weights: forward = quantized matmul plus optional bias
+    (crates/inference-quant/src/gguf/mod.rs:92-100,513-571; trait crates/inference-quant/src/lib.rs:2014-2291)."""
+
+    def __init__(self, w: QMatMul, b: torch.Tensor | None = None):
+        self.w, self.b = w, b
+
+    @classmethod
+    def from_qtensor(cls, q: QTensor, bias: torch.Tensor | None = None) -> "GgufMatMul":
+        return cls(QMatMul.from_qtensor(q), bias)
+
+    def quantized_act_type(self):
+        return None  # CUDA GGUF takes activations as they are (gguf/mod.rs:667-691)
+
+    def dtype_and_device(self):
+        return self.w.qtensor.dtype, self.w.qtensor.device
+
+    def is_distributed(self) -> bool:
+        return False
+
+    def get_qtensor(self) -> QTensor:
+        return self.w.qtensor
+
+    def forward_raw(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.w.forward(x)
+        return y if self.b is None else y + self.b.to(y.dtype)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.forward_raw(x)
+
+    __call__ = forward
+

@@ -1,0 +1,122 @@
+"""GPU tests of the host-side operator mirror (`QMatMul`, `GgufMatMul`) and of the tensor-parallel layers."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import kquants as kq
+
+import inference_rs_b200 as pkg
+from inference_rs_b200 import QMatMul, QTensor, GgufMatMul
+from inference_rs_b200.tensor_parallel import ColumnParallelLayer, RowParallelLayer, Shard, load_linear_shard
+from gpu_util import DT, TYPES, as_f32_numpy, assert_device_ok, seeded_acts, seeded_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("type_id", TYPES)
+@pytest.mark.parametrize("rows", [1, 3, 9, 33, 40])
+def test_qmatmul_forward_matches_the_cpu_path(type_id, rows):
+    """The reference's own check (crates/inference-quant/src/gguf/mod.rs:998-1037: 64x512 weights, batch 3 -> GEMV and
+    40 -> GEMM, f32 and bf16 inputs, max|err| <= 0.02 max|ref|), here against the CPU oracle and at 1e-2."""
+    n, k = 64, 512
+    packed = kq.quantize(type_id, seeded_weights(n, k, 50))
+    q = QTensor.from_packed(packed, DT[type_id], (n, k))
+    qmm = QMatMul.from_qtensor(q)
+    for dtype in (torch.float32, torch.bfloat16):
+        x = seeded_acts(rows, k, 60 + rows, dtype)
+        y = qmm.forward(x.cuda())
+        assert y.shape == (rows, n) and y.dtype == dtype
+        cpu = kq.matmul(type_id, as_f32_numpy(x), packed, n)
+        err = np.abs(as_f32_numpy(y) - cpu).max()
+        assert err <= 1e-3 + (1e-2 if dtype == torch.float32 else 2e-2) * np.abs(cpu).max(), (rows, dtype, err)
+    # leading dimensions are kept
+    x3 = seeded_acts(6, k, 5, torch.bfloat16).reshape(2, 3, k).cuda()
+    assert qmm.forward(x3).shape == (2, 3, n)
+    assert_device_ok()
+
+
+def test_qmatmul_errors_mirror_the_reference():
+    q = QTensor.from_packed(kq.quantize(kq.Q4_K, seeded_weights(8, 256, 1)), DT[kq.Q4_K], (8, 256))
+    qmm = QMatMul.from_qtensor(q)
+    with pytest.raises(ValueError, match="incompatible"):
+        qmm.forward(torch.zeros(2, 512, device="cuda"))
+    with pytest.raises(ValueError, match="only one dimension"):
+        qmm.forward(torch.zeros(256, device="cuda"))
+    with pytest.raises(ValueError, match="not contiguous"):
+        qmm.forward(torch.zeros(256, 4, device="cuda").t())
+    with pytest.raises(ValueError, match="not a multiple"):
+        QTensor(torch.zeros(100, dtype=torch.uint8, device="cuda"), DT[kq.Q4_K], (1, 100))
+
+
+def test_bias_is_added_after_the_matmul():
+    n, k = 32, 256
+    packed = kq.quantize(kq.Q8_0, seeded_weights(n, k, 2))
+    bias = torch.arange(n, dtype=torch.float32)
+    layer = GgufMatMul.from_qtensor(QTensor.from_packed(packed, DT[kq.Q8_0], (n, k)), bias.cuda())
+    x = seeded_acts(2, k, 3, torch.float32)
+    y = layer.forward(x.cuda())
+    cpu = kq.matmul(kq.Q8_0, as_f32_numpy(x), packed, n) + bias.numpy()
+    assert np.abs(as_f32_numpy(y) - cpu).max() <= 1e-3 + 1e-2 * np.abs(cpu).max()
+
+
+@pytest.mark.parametrize("type_id", [kq.Q4_K, kq.Q6_K])
+def test_shards_on_one_gpu_add_up(type_id):
+    """Both ranks' shards evaluated on one device: column shards concatenate, row shards sum to the unsharded output."""
+    n, k, world = 256, 2048, 2
+    packed = kq.quantize(type_id, seeded_weights(n, k, 9))
+    x = seeded_acts(2, k, 10, torch.bfloat16).cuda()
+    full = QMatMul(QTensor.from_packed(packed, DT[type_id], (n, k))).forward(x).float()
+    cols = [QMatMul(load_linear_shard(packed, DT[type_id], (n, k), Shard.simple(0, r, world))).forward(x) for r in range(world)]
+    assert torch.equal(torch.cat(cols, 1).float(), full)
+    parts = [QMatMul(load_linear_shard(packed, DT[type_id], (n, k), Shard.simple(1, r, world))).forward(
+        x[:, r * k // world:(r + 1) * k // world].contiguous()).float() for r in range(world)]
+    total = parts[0] + parts[1]
+    assert (total - full).abs().max() <= 2e-2 * full.abs().max()
+    assert_device_ok()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _tp_rank(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        n, k = 512, 2048
+        packed_up = kq.quantize(kq.Q4_K, seeded_weights(k, n, 21))      # column parallel: [k out, n in]
+        packed_down = kq.quantize(kq.Q6_K, seeded_weights(n, k, 22))    # row parallel: [n out, k in]
+        x = seeded_acts(2, n, 23, torch.bfloat16)
+        up = ColumnParallelLayer(packed_up, DT[kq.Q4_K], (k, n), rank, world, device=f"cuda:{rank}")
+        down = RowParallelLayer(packed_down, DT[kq.Q6_K], (n, k), rank, world, device=f"cuda:{rank}")
+        h = up(x.cuda(rank))                      # [2, k / world]: this rank's slice of the hidden features
+        y = down(h)                               # all-reduced: the same on every rank
+        torch.cuda.synchronize()
+        h_full = kq.matmul(kq.Q4_K, as_f32_numpy(x), packed_up, k)
+        h_bf16 = torch.from_numpy(h_full).to(torch.bfloat16).float().numpy()
+        ref = kq.matmul(kq.Q6_K, h_bf16, packed_down, n)
+        ret[rank] = float(np.abs(as_f32_numpy(y) - ref).max() / np.abs(ref).max())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_then_row_parallel_over_nccl():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_tp_rank, args=(world, port, ret), nprocs=world, join=True)
+        assert all(ret[r] < 3e-2 for r in range(world)), dict(ret)
+        assert abs(ret[0] - ret[1]) < 1e-6
