@@ -123,6 +123,19 @@ int b200q_set_trace_buffer(void* dev, int records);
 int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
                int b_size, int act_quant, void* stream);
 
+/* No counterpart in the reference. The decode GEMV for callers that cannot allocate device memory (their memory
+ * belongs to a pool of their own, or they may not call cudaMalloc because it synchronizes the device and stalls
+ * every other stream): quantizes x [b_size][K] (contiguous rows, element type `elem`) to Q8_1 blocks in a fixed
+ * 294,912-byte array inside the library image, then runs the same GEMV as launch_mmvq_gguf_<type>_<elem>_plain on
+ * them; dst [b_size][stride_dst] has x's element type and equals that two-launch pair's output. Limits: b_size <= 8
+ * and K padded to 512 <= 32768, else B200Q_ERR_TOO_LARGE. Allocates and frees nothing. The first call on a device
+ * looks the array's address up (cudaGetSymbolAddress) and should therefore come before any stream capture. All
+ * calls on a device share the one array: nothing in it needs clearing between calls (each call rewrites every block
+ * it later reads, padding included), but two calls whose kernels can overlap on the GPU - different streams without
+ * an ordering between them - race on it. Every GPU that loads the library holds the array until the process exits. */
+int b200q_gemv_static_scratch(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_dst,
+                              int b_size, void* stream);
+
 /* Prefill GEMM on the tcgen05 tensor cores: y[M][ldy] = x[M][ldx] . W[N][K]^T with x, y of element type `elem`
  * (B200Q_BF16 or B200Q_F16), f32 accumulation in tensor memory. Weights are dequantized tile by tile inside the
  * kernel; activations are not quantized. Needs K a multiple of 64, x 16-byte aligned with ldx * 2 a multiple of 16.

@@ -13,7 +13,7 @@ int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int
 void gemv_describe(int type, int K, int N, int b, int* out);
 int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s);
 
-static thread_local char t_error[256] = "";
+static thread_local char t_error[320] = "";
 int set_error(int code, const char* msg) {
     std::snprintf(t_error, sizeof t_error, "%s", msg);
     return code;
