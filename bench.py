@@ -356,10 +356,15 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pkg.library()
 
-    model = workloads.LLAMA3_8B
+    # one GPU: the Llama-3-8B-shaped chain. Several GPUs: the Llama-3-70B-shaped chain, tensor-parallel as the reference
+    # splits it (q/k/v, gate/up and the head by output rows; attn_output and ffn_down by input columns in whole
+    # superblocks, each followed by a sum all-reduce of the [1, hidden] partial output over NCCL)
+    tp = world > 1
+    model = workloads.LLAMA3_70B if tp else workloads.LLAMA3_8B
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    projs = model.layer_projections()
-    head = model.output_projection()
+    full_projs = model.layer_projections()
+    projs = [workloads.shard(p, world) for p in full_projs]
+    head = workloads.shard(model.output_projection(), world)
     layers = [[random_blocks_device(torch, p.dtype, p.n, p.k, gen) for p in projs] for _ in range(model.layers)]
     head_w = random_blocks_device(torch, head.dtype, head.n, head.k, gen)
     ks = sorted({p.k for p in projs} | {head.k})
@@ -367,15 +372,21 @@ def main():
     x_dev = {k: v.cuda() for k, v in x_host.items()}
     outs = [[torch.empty(1, p.n, dtype=torch.bfloat16, device="cuda") for p in projs] for _ in range(model.layers)]
     logits = torch.empty(1, head.n, dtype=torch.bfloat16, device="cuda")
-    logits_host = torch.empty(1, head.n, dtype=torch.bfloat16).pin_memory()
+    logits_all = torch.empty(world, head.n, dtype=torch.bfloat16, device="cuda") if tp else logits
+    logits_host = torch.empty(1, head.n * world, dtype=torch.bfloat16).pin_memory()
     launches_per_step = model.layers * len(projs) + 1
-    bytes_per_step = model.weight_bytes_per_token()
+    bytes_per_step = model.layers * sum(p.weight_bytes for p in projs) + head.weight_bytes  # per GPU
+    allreduces_per_step = model.layers * sum(1 for p in projs if p.split == "row") if tp else 0
 
     def step():
         for li in range(model.layers):
             for p, w, o in zip(projs, layers[li], outs[li]):
                 ops.gemv(p.dtype, w, x_dev[p.k], p.n, out=o)
+                if tp and p.split == "row":
+                    dist.all_reduce(o)
         ops.gemv(head.dtype, head_w, x_dev[head.k], head.n, out=logits)
+        if tp:
+            dist.all_gather_into_tensor(logits_all, logits)
 
     stream = torch.cuda.Stream()
     torch.cuda.synchronize()
@@ -384,9 +395,14 @@ def main():
         stream.synchronize()
         graph = None
         if not args.no_graph:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                step()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    step()
+            except Exception as exc:  # e.g. a collective that cannot be captured: run the step eagerly
+                print(f"[bench] CUDA graph capture failed ({type(exc).__name__}: {exc}); running eagerly", file=sys.stderr)
+                graph = None
+                torch.cuda.synchronize()
 
         def run_step():
             if graph is not None:
@@ -417,14 +433,14 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         ms_per_step = ms / args.steps
-        tok_s = world * 1000.0 / ms_per_step  # replicas: each rank decodes its own token stream
+        tok_s = 1000.0 / ms_per_step  # tensor parallel: all ranks work on the same token
 
         # ---- end to end: host buffers in, logits out, every step
         def e2e_step():
             for k in ks:
                 x_dev[k].copy_(x_host[k], non_blocking=True)
             run_step()
-            logits_host.copy_(logits, non_blocking=True)
+            logits_host.view(-1)[: logits_all.numel()].copy_(logits_all.view(-1), non_blocking=True)
 
         for _ in range(3):
             e2e_step()
@@ -441,14 +457,15 @@ def main():
             t = torch.tensor([e2e_ms], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_ms = float(t.item())
-        e2e_tok_s = world * 1000.0 * args.steps / e2e_ms
+        e2e_tok_s = 1000.0 * args.steps / e2e_ms
         h2d = sum(v.numel() * v.element_size() for v in x_host.values())
         d2h = logits_host.numel() * logits_host.element_size()
 
         # ---- roofline of the dominant kernel: Q4_K GEMV at the ffn_gate / ffn_up shape over 64 distinct weights
         gate_idx = [i for i, p in enumerate(projs) if p.name in ("ffn_gate", "ffn_up")]
+        gate_idx = gate_idx if not tp else gate_idx[:1]
         gp = projs[gate_idx[0]]
-        dom_ws = [layers[li][i] for li in range(model.layers) for i in gate_idx]
+        dom_ws = [layers[li][i] for li in range(min(model.layers, 32)) for i in gate_idx]
         dom_out = torch.empty(1, gp.n, dtype=torch.bfloat16, device="cuda")
         dom_us = time_launch_list(torch, stream, [(lambda w=w: ops.gemv(gp.dtype, w, x_dev[gp.k], gp.n, out=dom_out))
                                                   for w in dom_ws], 10)
@@ -456,6 +473,33 @@ def main():
         peak, peak_src = load_peaks()
         achieved = dom_bytes / (dom_us * 1e-6) / 1e9
         clocks.__exit__(None, None, None)
+
+        prefill = None
+        if not tp:
+            prefill = []
+            bf16_peak = 1647.9
+            pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+            if os.path.exists(pk):
+                bf16_peak = float(json.load(open(pk))["bf16_tflops"])
+            for dt, k, n in ((pkg.GgmlDType.Q4K, 4096, 4096), (pkg.GgmlDType.Q4K, 14336, 4096), (pkg.GgmlDType.Q6K, 14336, 4096)):
+                for m in (512, 2048, 8192):
+                    wq = random_blocks_device(torch, dt, n, k, gen)
+                    xm = torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16)
+                    ym = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+                    for _ in range(3):
+                        ops.gemm(dt, wq, xm, n, out=ym)
+                    barrier()
+                    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    g0.record(stream)
+                    for _ in range(10):
+                        ops.gemm(dt, wq, xm, n, out=ym)
+                    g1.record(stream)
+                    barrier()
+                    us = g0.elapsed_time(g1) * 100.0
+                    tf = 2.0 * m * n * k / us / 1e6
+                    prefill.append({"type": dt.name, "k": k, "n": n, "m": m, "us": round(us, 1), "TFLOPs": round(tf, 1),
+                                    "frac_of_measured_bf16_peak": round(tf / bf16_peak, 3)})
+                    del wq, xm, ym
 
         sweep = None
         if args.sweep:
@@ -481,15 +525,16 @@ def main():
 
     line = {
         "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot, f32 accumulate",
-        "data": "synthetic",
-        "config": {"workload": "llama3-8b Q4_K_M decode matmul chain, batch 1 (225 GEMVs, 4.88 GB of weights per token)",
-                   "l2": "inputs larger than L2: every step streams 4.88 GB of distinct weights",
-                   "parallelism": "replicas only" if world > 1 else "1 gpu", "cuda_graph": graph is not None,
-                   "pdl": ops.get_option("pdl")},
-        "weights_GBps": bytes_per_step * (tok_s / world) / 1e9,
-        "hbm_frac_of_measured": bytes_per_step * (tok_s / world) / 1e9 / peak,
-        "hbm_frac_of_nominal_8TBps": bytes_per_step * (tok_s / world) / 8e12,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
+        "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
+        "config": {"workload": (f"{model.name} Q4_K_M decode matmul chain, batch 1 ({launches_per_step} GEMVs, "
+                                f"{bytes_per_step / 1e9:.2f} GB of weights per token and GPU)"),
+                   "l2": "inputs larger than L2: every step streams its GBs of distinct weights",
+                   "parallelism": f"tp{world}: column / row split, {allreduces_per_step} NCCL all-reduces per token" if tp else "1 gpu",
+                   "cuda_graph": graph is not None, "pdl": ops.get_option("pdl")},
+        "weights_GBps_per_gpu": bytes_per_step * tok_s / 1e9,
+        "hbm_frac_of_measured": bytes_per_step * tok_s / 1e9 / peak,
+        "hbm_frac_of_nominal_8TBps": bytes_per_step * tok_s / 8e12,
         "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "kernel": "gemv_staged_kernel<Q4_K, b=1, bf16>", "shape": f"K={gp.k} N={gp.n}",
@@ -498,6 +543,8 @@ def main():
         "clocks": clocks.summary(),
         "device_status": list(status),
     }
+    if prefill is not None:
+        line["prefill_gemm"] = prefill
     if sweep is not None:
         line["sweep"] = sweep
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -508,7 +555,13 @@ def main():
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing NCCL down: destroying a process group whose collectives were captured into a CUDA graph
+        # can block at exit, and nothing is left to flush
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
