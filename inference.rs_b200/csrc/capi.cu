@@ -38,6 +38,8 @@ int b200q_set_option(const char* name, int value) {
     else if (!std::strcmp(name, "gemv_stage_bytes")) {
         if (value < 1024) return set_error(B200Q_ERR_INVALID, "gemv_stage_bytes must be >= 1024");
         rt.gemv_stage_target = value;
+    } else if (!std::strcmp(name, "gemm_direct")) {
+        rt.gemm_direct = value ? 1 : 0;
     } else if (!std::strcmp(name, "gemv_ctas_per_sm")) {
         if (value != 1 && value != 2) return set_error(B200Q_ERR_INVALID, "gemv_ctas_per_sm is 1 or 2");
         rt.gemv_ctas_per_sm = value;
@@ -53,6 +55,7 @@ int b200q_get_option(const char* name, int* value) {
     else if (!std::strcmp(name, "force_simple_gemv")) *value = rt.force_simple;
     else if (!std::strcmp(name, "gemv_stage_bytes")) *value = rt.gemv_stage_target;
     else if (!std::strcmp(name, "gemv_ctas_per_sm")) *value = rt.gemv_ctas_per_sm;
+    else if (!std::strcmp(name, "gemm_direct")) *value = rt.gemm_direct;
     else if (!std::strcmp(name, "sm_count")) *value = rt.sm_count;
     else if (!std::strcmp(name, "smem_optin")) *value = rt.smem_optin;
     else return set_error(B200Q_ERR_INVALID, "unknown option");

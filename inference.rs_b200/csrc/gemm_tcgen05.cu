@@ -417,6 +417,365 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
 }
 
 // ---------------------------------------------------------------------------------------------
+// Second kernel: the same tile GEMM, but the packed weight rows first come into shared memory with asynchronous copies,
+// 256 k of every row of the tile at a time, and the dequantization warps read them from there. One row per lane in
+// global memory meant scattered 4-byte loads for the 2-byte-aligned Q6_K / Q8_0 blocks; here every global access is
+// a 144 .. 272 byte contiguous copy. Needs K a multiple of 256 and rows that start on 16-byte boundaries.
+//   warp 3    issues the packed-row copies (16-byte cp.async pieces, 256 k of every row per chunk)
+// The chunk of a row lands at raw + r * PITCH (PITCH an odd multiple of 16 bytes: conflict-free 128-bit reads with
+// one row per lane); for Q6_K the copy starts at the 16-byte boundary below the superblock, which then begins `o`
+// bytes into the slot with o = (210 * chunk) & 15 the same for every row.
+// ---------------------------------------------------------------------------------------------
+constexpr int GEMM2_STAGES = 3;
+constexpr int GEMM2_RAW_STAGES = 2;
+
+template <int TYPE> struct RawChunk;
+template <> struct RawChunk<TYPE_Q4_K> { static constexpr int BYTES = 144, COPY = 144, PITCH = 144; };
+template <> struct RawChunk<TYPE_Q6_K> { static constexpr int BYTES = 210, COPY = 224, PITCH = 240; };
+template <> struct RawChunk<TYPE_Q8_0> { static constexpr int BYTES = 272, COPY = 272, PITCH = 272; };
+
+struct Gemm2Barriers {
+    uint64_t full_a[GEMM2_STAGES];
+    uint64_t full_b[GEMM2_STAGES];
+    uint64_t empty[GEMM2_STAGES];
+    uint64_t raw_full[GEMM2_RAW_STAGES];
+    uint64_t raw_empty[GEMM2_RAW_STAGES];
+    uint64_t tmem_full;
+    uint32_t tmem_base;
+};
+
+// `NW` 32-bit words starting `O` bytes (even, compile time) into the 16-byte-aligned words c[]
+template <int O, int NW, int NC>
+__device__ __forceinline__ void extract_words(const uint32_t (&c)[NC], uint32_t (&out)[NW]) {
+    constexpr int wo = O >> 2;
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+        if constexpr ((O & 2) == 0) {
+            out[i] = c[wo + i];
+        } else if constexpr (wo + NW < NC) {
+            out[i] = __funnelshift_r(c[wo + i], c[wo + i + 1], 16);
+        } else {
+            // the last word's upper half would come from beyond c[]: the callers only use its lower half
+            out[i] = (wo + i + 1 < NC) ? __funnelshift_r(c[wo + i], c[(wo + i + 1 < NC) ? wo + i + 1 : NC - 1], 16) : (c[wo + i] >> 16);
+        }
+    }
+}
+template <int NCHUNK>
+__device__ __forceinline__ void lds_chunks(uint32_t addr, uint32_t (&c)[4 * NCHUNK]) {
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        const uint4 v = lds128(addr + 16 * i);
+        c[4 * i] = v.x; c[4 * i + 1] = v.y; c[4 * i + 2] = v.z; c[4 * i + 3] = v.w;
+    }
+}
+
+// 32 values of unit (k block j of the chunk, half h) of the row whose chunk starts at shared address `rb`
+template <int TYPE> struct RawDequant;
+
+template <> struct RawDequant<TYPE_Q4_K> {
+    template <int J>
+    static __device__ __forceinline__ void values(uint32_t rb, int, int h, float (&v)[32]) {
+        const uint4 hdr = lds128(rb);
+        const uint4 q0 = lds128(rb + 16 + 32 * J), q1 = lds128(rb + 32 + 32 * J);
+        const int j = 2 * J + h;  // sub-block
+        uint32_t sc, m;
+        if (j < 4) {
+            sc = (hdr.y >> (8 * j)) & 0x3fu;
+            m = (hdr.z >> (8 * j)) & 0x3fu;
+        } else {
+            const int jj = j - 4;
+            const uint32_t lo = (hdr.w >> (8 * jj)) & 0xffu;
+            sc = (lo & 0xfu) | ((((hdr.y >> (8 * jj)) & 0xffu) >> 6) << 4);
+            m = (lo >> 4) | ((((hdr.z >> (8 * jj)) & 0xffu) >> 6) << 4);
+        }
+        const float dl = half_bits_to_float(hdr.x) * byte_to_float(sc);
+        const float ml = half_bits_to_float(hdr.x >> 16) * byte_to_float(m);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const int sh = 4 * h;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t nib = (w[i] >> sh) & 0x0f0f0f0fu;
+            v[4 * i + 0] = fmaf(dl, byte_as_magic<0>(nib) - 8388608.0f, -ml);
+            v[4 * i + 1] = fmaf(dl, byte_as_magic<1>(nib) - 8388608.0f, -ml);
+            v[4 * i + 2] = fmaf(dl, byte_as_magic<2>(nib) - 8388608.0f, -ml);
+            v[4 * i + 3] = fmaf(dl, byte_as_magic<3>(nib) - 8388608.0f, -ml);
+        }
+    }
+};
+
+template <> struct RawDequant<TYPE_Q8_0> {
+    // block b = 2J + h of the eight in the chunk starts at byte 34 b: f16 d, 32 int8
+    template <int OFF>
+    static __device__ __forceinline__ void block(uint32_t rb, float (&v)[32]) {
+        constexpr int A = OFF & ~15, O = OFF & 15;
+        uint32_t c[12], w[9];
+        lds_chunks<3>(rb + A, c);
+        extract_words<O, 9>(c, w);  // bytes OFF .. OFF + 35
+        const float d = half_bits_to_float(w[0]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t q = __funnelshift_r(w[i], w[i + 1], 16) ^ 0x80808080u;
+            v[4 * i + 0] = d * (byte_as_magic<0>(q) - 8388736.0f);
+            v[4 * i + 1] = d * (byte_as_magic<1>(q) - 8388736.0f);
+            v[4 * i + 2] = d * (byte_as_magic<2>(q) - 8388736.0f);
+            v[4 * i + 3] = d * (byte_as_magic<3>(q) - 8388736.0f);
+        }
+    }
+    template <int J>
+    static __device__ __forceinline__ void values(uint32_t rb, int, int h, float (&v)[32]) {
+        if (h == 0) block<34 * (2 * J)>(rb, v);
+        else block<34 * (2 * J + 1)>(rb, v);
+    }
+};
+
+template <> struct RawDequant<TYPE_Q6_K> {
+    // O = where the superblock starts inside the 16-byte-aligned slot; every field offset used below is a multiple of 16,
+    // so all of them share that misalignment
+    template <int O>
+    static __device__ __forceinline__ void unit(uint32_t rb, int J, int h, float (&v)[32]) {
+        const int n = J >> 1, p = J & 1, qd = 2 * p + h;
+        uint32_t cl[12], ch[12], ql[8], qh[8];
+        lds_chunks<3>(rb + 64 * n + 32 * h, cl);   // bytes O .. O+31 of this window hold ql[64n + 32h ..]
+        lds_chunks<3>(rb + 128 + 32 * n, ch);      // qh[32n ..]
+        extract_words<O, 8>(cl, ql);
+        extract_words<O, 8>(ch, qh);
+        const uint32_t sc2 = lds16(rb + O + 192 + 8 * n + 2 * qd);
+        const float d = half_bits_to_float(lds16(rb + O + 208));
+        const float s0 = d * (float)(int)(int8_t)(sc2 & 0xffu), s1 = d * (float)(int)(int8_t)(sc2 >> 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t q4 = ((ql[i] >> (4 * p)) & 0x0f0f0f0fu) | (((qh[i] >> (2 * qd)) & 0x03030303u) << 4);
+            const float sc = i < 4 ? s0 : s1;
+            v[4 * i + 0] = sc * (byte_as_magic<0>(q4) - 8388640.0f);
+            v[4 * i + 1] = sc * (byte_as_magic<1>(q4) - 8388640.0f);
+            v[4 * i + 2] = sc * (byte_as_magic<2>(q4) - 8388640.0f);
+            v[4 * i + 3] = sc * (byte_as_magic<3>(q4) - 8388640.0f);
+        }
+    }
+    template <int J>
+    static __device__ __forceinline__ void values(uint32_t rb, int kc, int h, float (&v)[32]) {
+        switch (kc & 7) {  // (210 * kc) & 15 = 2 * (kc & 7)
+            case 0: unit<0>(rb, J, h, v); break;
+            case 1: unit<2>(rb, J, h, v); break;
+            case 2: unit<4>(rb, J, h, v); break;
+            case 3: unit<6>(rb, J, h, v); break;
+            case 4: unit<8>(rb, J, h, v); break;
+            case 5: unit<10>(rb, J, h, v); break;
+            case 6: unit<12>(rb, J, h, v); break;
+            default: unit<14>(rb, J, h, v); break;
+        }
+    }
+};
+
+template <int TYPE, typename T, int MT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_staged_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+    using RC = RawChunk<TYPE>;
+    constexpr int RAW_BYTES = GEMM_BN * RC::PITCH + 64;  // + slack: reads may run a few bytes past the last row's slot
+    extern __shared__ uint8_t gemm_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* a_stages = smem;                                         // [S][MT][16 KB]
+    uint8_t* b_stages = smem + GEMM2_STAGES * MT * GEMM_A_BYTES;      // [S][16 KB]
+    uint8_t* raw_stages = b_stages + GEMM2_STAGES * GEMM_B_BYTES;     // [2][RAW_BYTES rounded to 128]
+    constexpr int RAW_STRIDE = (RAW_BYTES + 127) & ~127;
+    Gemm2Barriers* bars = reinterpret_cast<Gemm2Barriers*>(raw_stages + GEMM2_RAW_STAGES * RAW_STRIDE);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * GEMM_BN;
+    const int m0 = blockIdx.y * (MT * GEMM_BM);
+    const int nkb = p.K / GEMM_BK;
+    const int nkc = p.K / 256;
+    constexpr uint32_t TMEM_COLS = MT * GEMM_BN;
+    const int rows_valid = min(GEMM_BN, p.N - n0);
+
+    if (tid == 0) {
+        for (int s = 0; s < GEMM2_STAGES; ++s) {
+            mbar_init(&bars->full_a[s], 1);
+            mbar_init(&bars->full_b[s], GEMM_DEQ_WARPS);
+            mbar_init(&bars->empty[s], 1);
+        }
+        for (int s = 0; s < GEMM2_RAW_STAGES; ++s) {
+            mbar_init(&bars->raw_full[s], 32);  // one arrival per lane of the packed-row producer warp
+            mbar_init(&bars->raw_empty[s], GEMM_DEQ_WARPS);
+        }
+        mbar_init(&bars->tmem_full, 1);
+        mbar_init_fence();
+    }
+    if (warp == 2) tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    if (warp == 0) {
+        // ---------------- TMA producer of the activations ----------------
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % GEMM2_STAGES;
+                if (!mbar_wait_bounded(&bars->empty[s], ((kb / GEMM2_STAGES) & 1) ^ 1)) {
+                    record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, kb);
+                    ok = false;
+                    break;
+                }
+                mbar_arrive_expect_tx(&bars->full_a[s], MT * GEMM_A_BYTES);
+#pragma unroll
+                for (int t = 0; t < MT; ++t)
+                    tma_load_2d(a_stages + (size_t)(s * MT + t) * GEMM_A_BYTES, &tmap_x, kb * GEMM_BK, m0 + t * GEMM_BM, &bars->full_a[s]);
+                issued = kb + 1;
+            }
+            if (!ok) {
+                for (int kb = max(0, issued - GEMM2_STAGES); kb < issued; ++kb)
+                    if (!mbar_wait_bounded(&bars->full_a[kb % GEMM2_STAGES], (kb / GEMM2_STAGES) & 1)) {
+                        record_failure(p.status, STATUS_WAIT_DRAIN_TIMEOUT, kb);
+                        break;
+                    }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_f16(ElemFormat<T>::value, GEMM_BM, GEMM_BN);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % GEMM2_STAGES;
+                const uint32_t ph = (kb / GEMM2_STAGES) & 1;
+                if (!mbar_wait_bounded(&bars->full_a[s], ph) || !mbar_wait_bounded(&bars->full_b[s], ph)) {
+                    record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, kb);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint64_t db = make_smem_desc_sw128(smem_u32(b_stages + (size_t)s * GEMM_B_BYTES));
+#pragma unroll
+                for (int t = 0; t < MT; ++t) {
+                    const uint64_t da = make_smem_desc_sw128(smem_u32(a_stages + (size_t)(s * MT + t) * GEMM_A_BYTES));
+#pragma unroll
+                    for (int k = 0; k < GEMM_BK / 16; ++k)
+                        tc_mma_f16(tmem_base + t * GEMM_BN, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                tc_commit(&bars->empty[s]);
+            }
+            if (ok) tc_commit(&bars->tmem_full);
+        }
+    } else if (warp == 3) {
+        // ---------------- packed-row producer: 4 rows per lane and 256-k chunk ----------------
+        bool ok = true;
+        int issued = 0;
+        for (int kc = 0; kc < nkc && ok; ++kc) {
+            const int rs = kc % GEMM2_RAW_STAGES;
+            if (!mbar_wait_bounded(&bars->raw_empty[rs], ((kc / GEMM2_RAW_STAGES) & 1) ^ 1)) {
+                if (lane == 0) record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, 1000 + kc);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            // 16-byte asynchronous copies, consecutive lanes on consecutive pieces of a row (a bulk copy per row would
+            // cost the TMA unit more per copy than these small rows are worth); each lane's copies signal the barrier
+            uint8_t* stage = raw_stages + (size_t)rs * RAW_STRIDE;
+            constexpr int PIECES = RC::COPY / 16;
+            const int total = rows_valid * PIECES;
+            for (int idx = lane; idx < total; idx += 32) {
+                const int r = idx / PIECES, piece = idx - r * PIECES;
+                const uint8_t* src = p.w + (size_t)(n0 + r) * p.row_bytes + (size_t)kc * RC::BYTES;
+                src = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)15) + 16 * piece;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(stage + (size_t)r * RC::PITCH + 16 * piece)), "l"(src) : "memory");
+            }
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars->raw_full[rs])) : "memory");
+            issued = kc + 1;
+        }
+        (void)issued;
+        asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this warp may still be writing when the CTA exits
+    } else if (warp >= 4) {
+        // ---------------- dequantization from the staged packed rows ----------------
+        const int dt = tid - 128;
+        const int r = dt & (GEMM_BN - 1);
+        const int h = dt >> 7;
+        const bool row_ok = r < rows_valid;
+        bool ok = true;
+        for (int kc = 0; kc < nkc; ++kc) {
+            const int rs = kc % GEMM2_RAW_STAGES;
+            if (ok && !mbar_wait_bounded(&bars->raw_full[rs], (kc / GEMM2_RAW_STAGES) & 1)) {
+                record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, 1000 + kc);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            const uint32_t rb = smem_u32(raw_stages + (size_t)rs * RAW_STRIDE) + (uint32_t)r * RC::PITCH;
+#pragma unroll
+            for (int J = 0; J < 4; ++J) {
+                const int kb = 4 * kc + J;
+                const int s = kb % GEMM2_STAGES;
+                float v[32];
+                if (ok && row_ok) {
+                    if (J == 0) RawDequant<TYPE>::template values<0>(rb, kc, h, v);
+                    else if (J == 1) RawDequant<TYPE>::template values<1>(rb, kc, h, v);
+                    else if (J == 2) RawDequant<TYPE>::template values<2>(rb, kc, h, v);
+                    else RawDequant<TYPE>::template values<3>(rb, kc, h, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                }
+                if (ok && !mbar_wait_bounded(&bars->empty[s], ((kb / GEMM2_STAGES) & 1) ^ 1)) {
+                    record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, kb);
+                    ok = false;
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok) {
+                    store_unit<T>(smem_u32(b_stages + (size_t)s * GEMM_B_BYTES), r, h, v);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->full_b[s]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->raw_empty[rs]);  // this warp has read the chunk
+        }
+        // ---------------- epilogue ----------------
+        const int t = (warp - 4) >> 2;
+        const int quarter = warp & 3;
+        if (t < MT) {
+            if (ok && !mbar_wait_bounded(&bars->tmem_full, 0)) {
+                record_failure(p.status, STATUS_WAIT_MMA_TIMEOUT, 0);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            const int row = m0 + t * GEMM_BM + quarter * 32 + lane;
+            T* yrow = reinterpret_cast<T*>(p.y) + (size_t)row * p.ldy;
+            const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && ((size_t)p.ldy * sizeof(T) % 16 == 0);
+            if (ok) {
+#pragma unroll 1
+                for (int c = 0; c < GEMM_BN / 32; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + t * GEMM_BN + c * 32, acc);
+                    const int col0 = n0 + c * 32;
+                    if (row < p.M) {
+                        if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint4 o;
+                                o.x = pack2<T>(__uint_as_float(acc[8 * q]), __uint_as_float(acc[8 * q + 1]));
+                                o.y = pack2<T>(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3]));
+                                o.z = pack2<T>(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5]));
+                                o.w = pack2<T>(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7]));
+                                *reinterpret_cast<uint4*>(yrow + col0 + 8 * q) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) yrow[col0 + j] = from_float<T>(__uint_as_float(acc[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -435,6 +794,23 @@ static EncodeTiledFn encode_tiled_fn() {
             cudaGetLastError();
     }
     return fn;
+}
+
+template <int TYPE, typename T, int MT>
+static int launch_gemm_staged_mt(const CUtensorMap& map, const GemmParams& p, cudaStream_t s) {
+    auto kernel = gemm_tcgen05_staged_kernel<TYPE, T, MT>;
+    constexpr int RAW_STRIDE = ((GEMM_BN * RawChunk<TYPE>::PITCH + 64) + 127) & ~127;
+    const size_t smem = 1024 + (size_t)GEMM2_STAGES * (MT * GEMM_A_BYTES + GEMM_B_BYTES) + (size_t)GEMM2_RAW_STAGES * RAW_STRIDE +
+                        sizeof(Gemm2Barriers);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((unsigned)((p.N + GEMM_BN - 1) / GEMM_BN), (unsigned)((p.M + MT * GEMM_BM - 1) / (MT * GEMM_BM)), 1);
+    kernel<<<grid, GEMM_THREADS, smem, s>>>(map, p);
+    return (int)cudaGetLastError();
 }
 
 template <int TYPE, typename T, int MT>
@@ -476,8 +852,12 @@ static int launch_gemm_t(const void* w, const void* x, void* y, int M, int N, in
     p.status = status_ptr();
     // two 128-token sub-tiles per CTA halve the dequantization work per flop; one keeps more CTAs busy on small problems
     const long long tiles2 = (long long)((N + GEMM_BN - 1) / GEMM_BN) * ((M + 2 * GEMM_BM - 1) / (2 * GEMM_BM));
-    if (M > GEMM_BM && tiles2 >= runtime_info().sm_count) return launch_gemm_mt<TYPE, T, 2>(map, p, s);
-    return launch_gemm_mt<TYPE, T, 1>(map, p, s);
+    const bool two = M > GEMM_BM && tiles2 >= runtime_info().sm_count;
+    // packed rows staged through shared memory when the layout allows it (whole 256-k chunks, 16-byte aligned rows)
+    const bool staged = runtime_info().gemm_direct == 0 && K % 256 == 0 && p.row_bytes % 16 == 0 &&
+                        reinterpret_cast<uintptr_t>(w) % 16 == 0;
+    if (staged) return two ? launch_gemm_staged_mt<TYPE, T, 2>(map, p, s) : launch_gemm_staged_mt<TYPE, T, 1>(map, p, s);
+    return two ? launch_gemm_mt<TYPE, T, 2>(map, p, s) : launch_gemm_mt<TYPE, T, 1>(map, p, s);
 }
 
 int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s) {

@@ -20,6 +20,7 @@ struct RuntimeInfo {
     int use_pdl;           // launch with programmatic stream serialization
     int force_simple;      // route every GEMV to the simple kernel (testing)
     int gemv_stage_target; // bytes per shared-memory stage the GEMV planner aims at
+    int gemm_direct;       // 1: the GEMM reads packed weights straight from global memory (no shared-memory staging)
     int gemv_ctas_per_sm;  // CTAs of one GEMV grid per SM: 2, or 1 to leave the other slot to the next grid
 };
 
