@@ -309,6 +309,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-group", action="store_true", help="one launch per projection instead of grouped q/k/v and gate/up")
     ap.add_argument("--sweep", action="store_true", help="also time every shape of the decode sweep")
     ap.add_argument("--single", nargs=4, metavar=("TYPE", "K", "N", "B"), help="time one GEMV shape only (q4_k|q6_k|q8_0)")
     ap.add_argument("--gemm", nargs=4, metavar=("TYPE", "K", "N", "M"), help="time one prefill GEMM shape only")
@@ -378,9 +379,24 @@ def main():
     bytes_per_step = model.layers * sum(p.weight_bytes for p in projs) + head.weight_bytes  # per GPU
     allreduces_per_step = model.layers * sum(1 for p in projs if p.split == "row") if tp else 0
 
+    # projections that read the same input go out in one launch: q/k/v, gate/up (the reference's fused_qkv / fused_glu
+    # matvec launches, crates/inference-quant/src/lib.rs:2441-2776)
+    groups = []
+    if not args.no_group:
+        names = [p.name for p in projs]
+        for members in (("attn_q", "attn_k", "attn_v"), ("ffn_gate", "ffn_up")):
+            groups.append([names.index(m) for m in members])
+    grouped = {i for g in groups for i in g}
+    launches_per_step = model.layers * (len(projs) - len(grouped) + len(groups)) + 1
+
     def step():
         for li in range(model.layers):
-            for p, w, o in zip(projs, layers[li], outs[li]):
+            for g in groups:
+                ops.gemv_group([projs[i].dtype for i in g], [layers[li][i] for i in g], x_dev[projs[g[0]].k],
+                               [projs[i].n for i in g], outs=[outs[li][i] for i in g])
+            for i, (p, w, o) in enumerate(zip(projs, layers[li], outs[li])):
+                if i in grouped:
+                    continue
                 ops.gemv(p.dtype, w, x_dev[p.k], p.n, out=o)
                 if tp and p.split == "row":
                     dist.all_reduce(o)
@@ -527,11 +543,12 @@ def main():
         "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
         "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
-        "config": {"workload": (f"{model.name} Q4_K_M decode matmul chain, batch 1 ({launches_per_step} GEMVs, "
+        "config": {"workload": (f"{model.name} Q4_K_M decode matmul chain, batch 1 ({model.layers * len(projs) + 1} GEMVs in {launches_per_step} launches, "
                                 f"{bytes_per_step / 1e9:.2f} GB of weights per token and GPU)"),
                    "l2": "inputs larger than L2: every step streams its GBs of distinct weights",
                    "parallelism": f"tp{world}: column / row split, {allreduces_per_step} NCCL all-reduces per token" if tp else "1 gpu",
-                   "cuda_graph": graph is not None, "pdl": ops.get_option("pdl")},
+                   "cuda_graph": graph is not None, "pdl": ops.get_option("pdl"),
+                   "grouped_launches": not args.no_group},
         "weights_GBps_per_gpu": bytes_per_step * tok_s / 1e9,
         "hbm_frac_of_measured": bytes_per_step * tok_s / 1e9 / peak,
         "hbm_frac_of_nominal_8TBps": bytes_per_step * tok_s / 8e12,

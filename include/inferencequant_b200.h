@@ -123,6 +123,15 @@ int b200q_set_trace_buffer(void* dev, int records);
 int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
                int b_size, int act_quant, void* stream);
 
+/* Grouped decode GEMV: nmat (1..4) weight matrices of GGUF types types[i] with N[i] rows and the same K, applied to the
+ * same single activation row x [K] (element type `elem`) in ONE launch; output i goes to dsts[i] [N[i]] in x's type.
+ * Activations are quantized to Q8_1 in the prologue, so each output equals b200q_gemv(..., act_quant 0) on that matrix.
+ * Takes the place of the reference's fused q/k/v and gate/up matvec launches without their epilogues
+ * (launch_mmvq_gguf_<type>_<dst>_fused_qkv / _fused_glu, crates/inference-quant/src/gguf/ffi.rs:1032-1118) and, unlike
+ * them, accepts matrices of different types. The pointer arrays are host arrays read during the call. */
+int b200q_gemv_group(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, int elem,
+                     const void* x, void* stream);
+
 /* No counterpart in the reference. The decode GEMV for callers that cannot allocate device memory (their memory
  * belongs to a pool of their own, or they may not call cudaMalloc because it synchronizes the device and stalls
  * every other stream): quantizes x [b_size][K] (contiguous rows, element type `elem`) to Q8_1 blocks in a fixed

@@ -11,6 +11,8 @@ int gemv_q4_k(int, const void*, const void*, void*, int, int, int, int, int, int
 int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
 int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
 void gemv_describe(int type, int K, int N, int b, int* out);
+int gemv_group(int elem, int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, const void* x,
+               cudaStream_t s);
 int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s);
 
 static thread_local char t_error[320] = "";
@@ -107,6 +109,18 @@ int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int 
     if (rc == B200Q_ERR_UNSUPPORTED)
         return set_error(rc, "no one-launch GEMV for this shape or alignment: quantize to Q8_1 and use launch_mmvq_gguf_*_plain");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemv failed");
+    return B200Q_OK;
+}
+
+// Grouped decode GEMV: nmat (1..4) weight matrices with the same K applied to the same activation row x [K] in one launch.
+int b200q_gemv_group(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, int elem,
+                     const void* x, void* stream) {
+    if (!types || !ws || !dsts || !Ns || !x) return set_error(B200Q_ERR_INVALID, "null pointer");
+    if (nmat < 1 || nmat > 4) return set_error(B200Q_ERR_INVALID, "b200q_gemv_group takes 1..4 matrices");
+    const int rc = gemv_group(elem, nmat, types, ws, dsts, Ns, K, x, (cudaStream_t)stream);
+    if (rc == B200Q_ERR_UNSUPPORTED)
+        return set_error(rc, "group not supported (K must be a multiple of 128, weights 16-byte aligned): launch the matrices one by one");
+    if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "grouped gemv failed");
     return B200Q_OK;
 }
 

@@ -380,7 +380,7 @@ template <> struct Weights<TYPE_Q4_K> {
     }
 };
 template <> struct Acts<TYPE_Q4_K> : ActPair {};
-__device__ __forceinline__ float dot(const Weights<TYPE_Q4_K>& W, const Acts<TYPE_Q4_K>& A) {
+__device__ __forceinline__ float dot(const Weights<TYPE_Q4_K>& W, const ActPair& A) {
     float accd = 0.0f, accm = 0.0f;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
@@ -451,7 +451,7 @@ template <> struct Acts<TYPE_Q6_K> {
         }
     }
 };
-__device__ __forceinline__ float dot(const Weights<TYPE_Q6_K>& W, const Acts<TYPE_Q6_K>& A) {
+__device__ __forceinline__ float dot_q6k(const Weights<TYPE_Q6_K>& W, const uint32_t (&aq)[32], const float (&ad)[4]) {
     int acc[4][2];
 #pragma unroll
     for (int qd = 0; qd < 4; ++qd) acc[qd][0] = acc[qd][1] = 0;
@@ -463,10 +463,10 @@ __device__ __forceinline__ float dot(const Weights<TYPE_Q6_K>& W, const Acts<TYP
         const uint32_t w2 = ((la >> 2) & 0x3c3c3c3cu) | (((h << 2) & 0xc0c0c0c0u) ^ 0x80808080u);
         const uint32_t w3 = ((lb >> 2) & 0x3c3c3c3cu) | ((h & 0xc0c0c0c0u) ^ 0x80808080u);
         const int g = t >> 2;
-        acc[0][g] = dp4a_ss(w0, A.q[t], acc[0][g]);
-        acc[1][g] = dp4a_ss(w1, A.q[8 + t], acc[1][g]);
-        acc[2][g] = dp4a_ss(w2, A.q[16 + t], acc[2][g]);
-        acc[3][g] = dp4a_ss(w3, A.q[24 + t], acc[3][g]);
+        acc[0][g] = dp4a_ss(w0, aq[t], acc[0][g]);
+        acc[1][g] = dp4a_ss(w1, aq[8 + t], acc[1][g]);
+        acc[2][g] = dp4a_ss(w2, aq[16 + t], acc[2][g]);
+        acc[3][g] = dp4a_ss(w3, aq[24 + t], acc[3][g]);
     }
     float part = 0.0f;
 #pragma unroll
@@ -474,10 +474,13 @@ __device__ __forceinline__ float dot(const Weights<TYPE_Q6_K>& W, const Acts<TYP
         const uint32_t word = qd < 2 ? W.scw[0] : W.scw[1];
         const int s0 = (int)(int8_t)((word >> (16 * (qd & 1))) & 0xffu);
         const int s1 = (int)(int8_t)((word >> (16 * (qd & 1) + 8)) & 0xffu);
-        part += A.d[qd] * (float)(s0 * acc[qd][0] + s1 * acc[qd][1]);
+        part += ad[qd] * (float)(s0 * acc[qd][0] + s1 * acc[qd][1]);
     }
     return W.d * part;
 }
+
+__device__ __forceinline__ float dot(const Weights<TYPE_Q6_K>& W, const Acts<TYPE_Q6_K>& A) { return dot_q6k(W, A.q, A.d); }
+__device__ __forceinline__ float dot(const Weights<TYPE_Q6_K>& W, const ActPair& A) { return dot_q6k(W, A.q, A.d); }
 
 // ---- Q8_0: item = four 34-byte blocks.
 template <> struct Weights<TYPE_Q8_0> {
@@ -501,7 +504,7 @@ template <> struct Weights<TYPE_Q8_0> {
     }
 };
 template <> struct Acts<TYPE_Q8_0> : ActPair {};
-__device__ __forceinline__ float dot(const Weights<TYPE_Q8_0>& W, const Acts<TYPE_Q8_0>& A) {
+__device__ __forceinline__ float dot(const Weights<TYPE_Q8_0>& W, const ActPair& A) {
     float part = 0.0f;
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
@@ -733,6 +736,232 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         if (lane == 0) mbar_arrive(&empty[s]);
     }
     GEMV_TRACE(4);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Grouped GEMV: up to four weight matrices with the same K applied to the same single activation row in ONE launch
+// (q/k/v of an attention block, gate/up of an MLP: the reference's fused_qkv / fused_glu matvecs,
+// crates/inference-quant/kernels/cuda/mmvq_gguf/mmvq_gguf.cuh:761-962, without the activation epilogue). The matrices may
+// have different types and row counts; each has its own output. The fixed cost of a launch (launch gap, barrier set-up,
+// activation quantization, first bytes from HBM) is paid once for the group. Every CTA takes its share of the rows of
+// every matrix, one matrix after the other, through the same stage ring.
+// ---------------------------------------------------------------------------------------------
+constexpr int GEMV_GROUP_MAX = 4;
+
+struct GemvGroupParams {
+    const uint8_t* w[GEMV_GROUP_MAX];
+    void* dst[GEMV_GROUP_MAX];
+    int N[GEMV_GROUP_MAX];
+    int type[GEMV_GROUP_MAX];
+    int row_bytes[GEMV_GROUP_MAX];
+    int rows_per_stage[GEMV_GROUP_MAX];
+    int row_align[GEMV_GROUP_MAX];
+    int units_per_cta[GEMV_GROUP_MAX];
+    int units_extra[GEMV_GROUP_MAX];
+    int nmat;
+    const void* act;  // one raw activation row of K values
+    int K;
+    int warps_per_row, items_per_lane;
+    int nstages, stage_bytes, act_bytes, max_rows_per_stage;
+    int use_pdl, act_vec;
+    unsigned int* status;
+};
+
+// rows [row0, row1) of matrix m that CTA `cta` owns
+__device__ __forceinline__ void group_rows(const GemvGroupParams& p, int m, int cta, int& row0, int& row1) {
+    const int unit0 = cta * p.units_per_cta[m] + min(cta, p.units_extra[m]);
+    row0 = unit0 * p.row_align[m];
+    row1 = (unit0 + p.units_per_cta[m] + (cta < p.units_extra[m] ? 1 : 0)) * p.row_align[m];
+    if (row1 > p.N[m]) row1 = p.N[m];
+    if (row1 < row0) row1 = row0;
+}
+
+template <int TYPE, typename dst_t, int NREG>
+__device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint32_t st, int row_bytes, int rows_here, int rbase,
+                                                 int my_slot, int rows_per_pass, int item0, int item_step, int items, int islots,
+                                                 int lane_i, int WPR, int wslice, int IPL, uint32_t acts_addr,
+                                                 const ActPair (&areg)[NREG > 0 ? NREG : 1], float* part_base, int* cnt_base,
+                                                 dst_t* dst, bool alive) {
+    for (int pass0 = 0; pass0 < rows_here; pass0 += rows_per_pass) {
+        const int r_in = pass0 + my_slot;
+        const bool has_row = r_in < rows_here;
+        float acc = 0.0f;
+        if (alive && has_row) {
+            const uint32_t row_addr = st + (uint32_t)r_in * (uint32_t)row_bytes;
+            if (NREG > 0) {
+#pragma unroll
+                for (int j = 0; j < (NREG > 0 ? NREG : 1); ++j) {
+                    const int item = item0 + j * item_step;
+                    if (item < items) {
+                        Weights<TYPE> W;
+                        W.load(row_addr, item);
+                        acc += dot(W, areg[j]);
+                    }
+                }
+            } else {
+                for (int j = 0; j < IPL; ++j) {
+                    const int item = item0 + j * item_step;
+                    if (item < items) {
+                        Weights<TYPE> W;
+                        W.load(row_addr, item);
+                        ActPair A;
+                        A.load(acts_addr, item);
+                        acc += dot(W, A);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1)
+            if (m < islots) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+        if (lane_i == 0 && has_row) {
+            if (WPR == 1) {
+                dst[rbase + r_in] = from_float<dst_t>(acc);
+            } else {
+                float* part = part_base + (size_t)r_in * WPR;
+                part[wslice] = acc;
+                __threadfence_block();
+                const int arrived = atomicAdd(&cnt_base[r_in], 1);
+                if (arrived == WPR - 1) {
+                    __threadfence_block();
+                    cnt_base[r_in] = 0;
+                    float v = 0.0f;
+                    for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w];
+                    dst[rbase + r_in] = from_float<dst_t>(v);
+                }
+            }
+        }
+    }
+}
+
+template <typename dst_t, typename act_t, int NREG>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvGroupParams p) {
+    constexpr int ACT = ACT_RAW_Q8_1;  // activations quantized to Q8_1, as the two-launch protocol does
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + GEMV_MAX_STAGES;
+    uint8_t* acts = smem + GEMV_BARRIER_BYTES;
+    const int S = p.nstages, WPR = p.warps_per_row, IPL = p.items_per_lane, RMAX = p.max_rows_per_stage;
+    float* partial = reinterpret_cast<float*>(acts + p.act_bytes);  // [S][RMAX][WPR]
+    const int partial_floats = WPR > 1 ? S * RMAX * WPR : 0;
+    int* counters = reinterpret_cast<int*>(partial + partial_floats);  // [S][RMAX]
+    const int counter_ints = WPR > 1 ? S * RMAX : 0;
+    uint8_t* ring = acts + p.act_bytes + (((partial_floats + counter_ints) * 4 + 127) & ~127);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x;
+    if (p.use_pdl) {
+        grid_launch_dependents();
+        if (warp != GEMV_CONSUMER_WARPS) grid_dependency_wait();
+    }
+    ActPrefetch<ACT, act_t> pre;
+    if (warp != GEMV_CONSUMER_WARPS) pre.issue(p.act, 1, p.K, p.K, p.act_vec != 0, tid);
+
+    const bool is_producer = (warp == GEMV_CONSUMER_WARPS);
+    if (is_producer && lane == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], GEMV_CONSUMER_WARPS);
+        }
+        mbar_init_fence();
+    }
+    for (int i = tid; i < counter_ints; i += GEMV_THREADS) counters[i] = 0;
+    __syncthreads();
+
+    if (is_producer) {
+        // ---------------- producer: this CTA's rows of every matrix, in order, through one ring ----------------
+        if (lane == 0) {
+            bool ok = true;
+            int g = 0;  // running stage number over all matrices
+            for (int m = 0; m < p.nmat && ok; ++m) {
+                int row0, row1;
+                group_rows(p, m, cta, row0, row1);
+                const int R = p.rows_per_stage[m];
+                for (int r = row0; r < row1 && ok; r += R, ++g) {
+                    const int s = g % S;
+                    if (g >= S) {
+                        ok = mbar_wait_bounded(&empty[s], ((g / S) - 1) & 1);
+                        if (!ok) { record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, g); break; }
+                    }
+                    const int rows = min(R, row1 - r);
+                    const uint32_t bytes = ((uint32_t)rows * (uint32_t)p.row_bytes[m] + 15u) & ~15u;
+                    mbar_arrive_expect_tx(&full[s], bytes);
+                    bulk_copy_g2s(ring + (size_t)s * p.stage_bytes, p.w[m] + (size_t)r * p.row_bytes[m], bytes, &full[s]);
+                }
+            }
+            if (!ok) {
+                for (int q = max(0, g - S); q < g; ++q)
+                    if (!mbar_wait_bounded(&full[q % S], (q / S) & 1)) {
+                        record_failure(p.status, STATUS_WAIT_DRAIN_TIMEOUT, q);
+                        break;
+                    }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    // the activation row is quantized once for all matrices
+    stage_acts_raw<1, act_t, TYPE_Q4_K, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.K, p.act_vec != 0, tid,
+                                             GEMV_CONSUMER_THREADS, pre);
+    named_bar_sync(1, GEMV_CONSUMER_THREADS);
+
+    const int items = p.K / 128;
+    int islots = 32;
+    while (islots > 1 && (islots >> 1) >= items) islots >>= 1;
+    const int rpw = 32 / islots;
+    const int lane_i = lane & (islots - 1), lane_r = lane / islots;
+    const int nrg = GEMV_CONSUMER_WARPS / WPR;
+    const int wgroup = warp / WPR, wslice = warp % WPR;
+    const int row_slot = wgroup * rpw + lane_r;
+    const int rows_per_pass = nrg * rpw;
+    const int item0 = wslice * 32 + lane_i;
+    const int item_step = 32 * WPR;
+    const uint32_t acts_addr = smem_u32(acts);
+    const uint32_t ring_addr = smem_u32(ring);
+
+    ActPair areg[NREG > 0 ? NREG : 1];
+    if (NREG > 0) {
+#pragma unroll
+        for (int j = 0; j < (NREG > 0 ? NREG : 1); ++j)
+            if (item0 + j * item_step < items) areg[j].load(acts_addr, item0 + j * item_step);
+    }
+
+    bool alive = true;
+    int g = 0;
+    int rot_rows = 0;  // rows handed out so far: rotates the row-to-warp assignment across stages
+    for (int m = 0; m < p.nmat; ++m) {
+        int row0, row1;
+        group_rows(p, m, cta, row0, row1);
+        const int R = p.rows_per_stage[m];
+        const int mtype = p.type[m];
+        dst_t* dst = reinterpret_cast<dst_t*>(p.dst[m]);
+        for (int r = row0; r < row1; r += R, ++g) {
+            const int s = g % S;
+            if (alive && !mbar_wait_bounded(&full[s], (g / S) & 1)) {
+                record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, g);
+                alive = false;
+            }
+            const uint32_t st = ring_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
+            const int rows_here = min(R, row1 - r);
+            const int rot = rot_rows % rows_per_pass;
+            const int my_slot = row_slot >= rot ? row_slot - rot : row_slot - rot + rows_per_pass;
+            rot_rows += rows_here;
+            float* part_base = partial + (size_t)s * RMAX * WPR;
+            int* cnt_base = counters + s * RMAX;
+            if (mtype == TYPE_Q4_K)
+                group_stage_rows<TYPE_Q4_K, dst_t, NREG>(p, st, p.row_bytes[m], rows_here, r, my_slot, rows_per_pass, item0, item_step,
+                                                         items, islots, lane_i, WPR, wslice, IPL, acts_addr, areg, part_base, cnt_base, dst, alive);
+            else if (mtype == TYPE_Q6_K)
+                group_stage_rows<TYPE_Q6_K, dst_t, NREG>(p, st, p.row_bytes[m], rows_here, r, my_slot, rows_per_pass, item0, item_step,
+                                                         items, islots, lane_i, WPR, wslice, IPL, acts_addr, areg, part_base, cnt_base, dst, alive);
+            else
+                group_stage_rows<TYPE_Q8_0, dst_t, NREG>(p, st, p.row_bytes[m], rows_here, r, my_slot, rows_per_pass, item0, item_step,
+                                                         items, islots, lane_i, WPR, wslice, IPL, acts_addr, areg, part_base, cnt_base, dst, alive);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -986,6 +1215,81 @@ static inline int launch_gemv(const void* vx, const void* act, void* dst, int K,
         case 8: return launch_gemv_b<TYPE, 8, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, s);
         default: return B200Q_ERR_UNSUPPORTED;
     }
+}
+
+// Plans and launches a grouped GEMV (one activation row). Returns B200Q_ERR_UNSUPPORTED when the group does not fit
+// the staged kernel's preconditions; the caller then launches the matrices one by one.
+template <typename dst_t>
+static inline int launch_gemv_group(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K,
+                                    const void* x, cudaStream_t s) {
+    const RuntimeInfo& rt = runtime_info();
+    if (nmat < 1 || nmat > GEMV_GROUP_MAX || K <= 0 || K % 128 != 0 || rt.force_simple) return B200Q_ERR_UNSUPPORTED;
+    GemvGroupParams p{};
+    p.nmat = nmat;
+    p.K = K;
+    p.act = x;
+    p.act_bytes = (((K / 64) * ACT_REC_BYTES) + 127) & ~127;
+    p.act_vec = (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+    p.use_pdl = rt.use_pdl;
+    p.status = status_ptr();
+    int grid = rt.sm_count, max_stage = 0, max_R = 0, wpr = 0, ipl = 0;
+    for (int m = 0; m < nmat; ++m) {
+        if (type_block_bytes(types[m]) == 0 || K % type_block_elems(types[m]) != 0) return B200Q_ERR_UNSUPPORTED;
+        if (reinterpret_cast<uintptr_t>(ws[m]) % 16 != 0 || Ns[m] <= 0) return B200Q_ERR_UNSUPPORTED;
+        const GemvPlan one = plan_gemv(types[m], K, Ns[m], 1, ws[m]);
+        if (!one.staged) return B200Q_ERR_UNSUPPORTED;
+        if (m == 0) { wpr = one.p.warps_per_row; ipl = one.p.items_per_lane; }
+        if (one.p.warps_per_row != wpr || one.p.items_per_lane != ipl) return B200Q_ERR_UNSUPPORTED;  // same K: cannot differ
+        p.w[m] = static_cast<const uint8_t*>(ws[m]);
+        p.dst[m] = dsts[m];
+        p.N[m] = Ns[m];
+        p.type[m] = types[m];
+        p.row_bytes[m] = one.p.row_bytes;
+        p.rows_per_stage[m] = one.p.rows_per_stage;
+        p.row_align[m] = one.p.row_align;
+        if (one.p.stage_bytes > max_stage) max_stage = one.p.stage_bytes;
+        if (one.p.rows_per_stage > max_R) max_R = one.p.rows_per_stage;
+    }
+    for (int m = 0; m < nmat; ++m) {
+        const long long units = (p.N[m] + p.row_align[m] - 1) / p.row_align[m];
+        p.units_per_cta[m] = (int)(units / grid);
+        p.units_extra[m] = (int)(units % grid);
+    }
+    p.warps_per_row = wpr;
+    p.items_per_lane = ipl;
+    p.stage_bytes = max_stage;
+    p.max_rows_per_stage = max_R;
+    const int budget = rt.smem_optin - 1024;
+    int S = 0;
+    size_t smem = 0;
+    for (S = GEMV_MAX_STAGES; S >= 2; --S) {
+        const int combine = wpr > 1 ? (((S * max_R * wpr + S * max_R) * 4 + 127) & ~127) : 0;
+        if (GEMV_BARRIER_BYTES + p.act_bytes + combine + S * max_stage <= budget) {
+            smem = (size_t)GEMV_BARRIER_BYTES + p.act_bytes + combine + (size_t)S * max_stage;
+            break;
+        }
+    }
+    if (S < 2) return B200Q_ERR_UNSUPPORTED;
+    p.nstages = S;
+    const int nreg = ipl <= 2 ? ipl : 0;
+    auto launch = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, rt.smem_optin - 1024);
+        if (e != cudaSuccess) return (int)e;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)grid, 1, 1);
+        cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = p.use_pdl ? 1 : 0;
+        return (int)cudaLaunchKernelEx(&cfg, kernel, p);
+    };
+    if (nreg == 1) return launch(gemv_group_kernel<dst_t, dst_t, 1>);
+    if (nreg == 2) return launch(gemv_group_kernel<dst_t, dst_t, 2>);
+    return launch(gemv_group_kernel<dst_t, dst_t, 0>);
 }
 
 // One weight type's dispatcher over the output element type; defined once per type in gemv_<type>.cu.

@@ -97,6 +97,23 @@ def gemv(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.
     return dst
 
 
+def gemv_group(dtypes, ws, x: torch.Tensor, ns, outs=None):
+    """`b200q_gemv_group`: several weight matrices (same K) on one activation row x [1, k] in one launch."""
+    _require_cuda(x, *ws)
+    if x.dim() != 2 or x.shape[0] != 1:
+        raise ValueError("gemv_group takes a single activation row [1, k]")
+    k = x.shape[1]
+    n = len(ws)
+    if outs is None:
+        outs = [torch.empty((1, ni), dtype=x.dtype, device=x.device) for ni in ns]
+    types = (C.c_int * n)(*[int(d) for d in dtypes])
+    wp = (C.c_void_p * n)(*[w.data_ptr() for w in ws])
+    dp = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+    nn = (C.c_int * n)(*[int(v) for v in ns])
+    kl.check(kl.library().b200q_gemv_group(n, types, wp, dp, nn, k, elem_of(x.dtype), x.data_ptr(), _stream()), "b200q_gemv_group")
+    return outs
+
+
 def gemm(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
     """`b200q_gemm`: prefill tile GEMM on the tensor cores. x [m, k] bf16/f16 -> [m, n] of x's dtype."""
     _require_cuda(w, x)

@@ -173,3 +173,24 @@ def test_unsupported_batch_is_refused():
     x = torch.zeros(9, 256, device="cuda")
     with pytest.raises(kl.KernelLibraryError, match="1..8"):
         ops.gemv(DT[kq.Q4_K], w_dev, x, 8)
+
+
+def test_grouped_launch_equals_separate_launches():
+    """q/k/v (mixed Q4_K and Q6_K) and gate/up in one launch each give exactly the single-matrix results."""
+    k = 4096
+    for shapes in ([(kq.Q4_K, 4096), (kq.Q4_K, 1024), (kq.Q6_K, 1024)], [(kq.Q4_K, 14336), (kq.Q4_K, 14336)],
+                   [(kq.Q8_0, 100), (kq.Q6_K, 37), (kq.Q4_K, 515), (kq.Q8_0, 1)]):
+        x = seeded_acts(1, k, 31, torch.bfloat16).cuda()
+        ws = [ops.upload_weights(random_packed(t, n, k, seed=n + int(t)), DT[t]) for t, n in shapes]
+        outs = ops.gemv_group([DT[t] for t, _ in shapes], ws, x, [n for _, n in shapes])
+        for (t, n), w, o in zip(shapes, ws, outs):
+            assert torch.equal(o, ops.gemv(DT[t], w, x, n)), (kq.TYPE_NAMES[t], n)
+    # a long row (several warps per row) as in ffn_down
+    k = 14336
+    x = seeded_acts(1, k, 32, torch.float32).cuda()
+    shapes = [(kq.Q6_K, 300), (kq.Q4_K, 200)]
+    ws = [ops.upload_weights(random_packed(t, n, k, seed=n), DT[t]) for t, n in shapes]
+    outs = ops.gemv_group([DT[t] for t, _ in shapes], ws, x, [n for _, n in shapes])
+    for (t, n), w, o in zip(shapes, ws, outs):
+        assert torch.equal(o, ops.gemv(DT[t], w, x, n))
+    assert_device_ok()
