@@ -158,6 +158,11 @@ def run_single(args):
                     vy = ops.quantize_q8_1(x)
                     ops.mmvq_plain(dt, w, vy, n, k, b, torch.bfloat16)
                 return fn
+        elif args.tc:
+            tc_ws = ops.gemv_tc_workspace(dt, k)
+
+            def mk(w):
+                return lambda: ops.gemv_tc(dt, w, x, n, out=out, workspace=tc_ws)
         else:
             def mk(w):
                 return lambda: ops.gemv(dt, w, x, n, out=out)
@@ -180,7 +185,7 @@ def run_single(args):
     alg = wbytes + b * k * 2 + b * n * 2
     print(json.dumps({"single": tname, "k": k, "n": n, "b": b, "copies": copies, "us_per_launch": us,
                       "GBps": alg / us / 1e3, "frac_of_" + src: alg / us / 1e3 / peak, "algorithmic_bytes": alg,
-                      "plan": ops.gemv_plan(dt, k, n, b), "device_status": list(pkg.kernel_library.device_status())}),
+                      "kernel": "gemv_tc" if args.tc else "gemv", "plan": None if (args.tc or b > 8) else ops.gemv_plan(dt, k, n, b), "device_status": list(pkg.kernel_library.device_status())}),
           flush=True)
 
 
@@ -312,6 +317,7 @@ def main():
     ap.add_argument("--no-group", action="store_true", help="one launch per projection instead of grouped q/k/v and gate/up")
     ap.add_argument("--sweep", action="store_true", help="also time every shape of the decode sweep")
     ap.add_argument("--single", nargs=4, metavar=("TYPE", "K", "N", "B"), help="time one GEMV shape only (q4_k|q6_k|q8_0)")
+    ap.add_argument("--tc", action="store_true", help="with --single: the small-batch tensor-core kernel (B up to 16)")
     ap.add_argument("--gemm", nargs=4, metavar=("TYPE", "K", "N", "M"), help="time one prefill GEMM shape only")
     ap.add_argument("--copies", type=int, default=0, help="--single: number of rotating weight copies")
     ap.add_argument("--two-launch", action="store_true", help="--single: quantize launcher + GEMV launcher instead of one launch")

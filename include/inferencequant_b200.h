@@ -152,6 +152,23 @@ int b200q_gemv_static_scratch(int type, int elem, const void* w, const void* x, 
  * which quantizes activations to Q8_1 blocks and runs launch_mmq_gguf_<type> (ffi.rs:911-927). */
 int b200q_gemm(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* stream);
 
+/* Small batches (M = 1..16 activation rows, B200Q_ERR_TOO_LARGE above) on the tcgen05 tensor cores with 8-bit integer
+ * operands: y[M][ldy] = x[M][ldx] . W[N][K]^T, x and y of element type `elem` (f32, f16 or bf16). Two launches on
+ * `stream`: x is quantized into `workspace` (int8, one f16-rounded scale d = amax / 127 and the integer sum per 32
+ * values: the layout kernel mmvq_tc_quantize of the reference, mmvq_gguf/mmvq_quantize.cu:157-190, computes the same
+ * values), then one persistent CTA per SM streams its share of the packed weight rows once, unpacks them to int8 and
+ * multiplies 128 rows x 32 k blocks by all rows of x with tcgen05.mma kind::i8; block scales are applied in f32.
+ * Takes the place of the reference's tensor-core matvec tier for 2..16 rows: fast_mmvq::tiled_plain
+ * (crates/inference-quant/src/gguf/fast_mmvq.rs:2049-2126) with launch_mmvq_tc_quantize_<elem> +
+ * launch_mmvq_tc_gguf_<type>_<elem>_plain (ffi.rs:631-652,954-998; kernel mmvq_gguf/mmvq_tc_k.cuh:221-329).
+ * Needs K a multiple of 256, w 16-byte aligned with a row size that is a multiple of 16 bytes (Q6_K: K a multiple of
+ * 2048), workspace 128-byte aligned and at least b200q_gemv_tc_workspace_bytes(type, K) bytes (0 = unsupported K);
+ * the workspace is the caller's, as the reference's activation scratch is (gguf/thread_workspace.rs:94-146), and
+ * must not be shared by calls that can overlap on the GPU. */
+long long b200q_gemv_tc_workspace_bytes(int type, int K);
+int b200q_gemv_tc(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace,
+                  long long workspace_bytes, void* stream);
+
 /* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,
  *        item slots per lane, register-resident slots} */
 int b200q_gemv_plan(int type, int K, int N, int b_size, int out[10]);

@@ -14,6 +14,8 @@ void gemv_describe(int type, int K, int N, int b, int* out);
 int gemv_group(int elem, int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, const void* x,
                cudaStream_t s);
 int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s);
+int gemv_tc_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace, cudaStream_t s);
+size_t gemv_tc_workspace_bytes(int type, int K);
 
 static thread_local char t_error[320] = "";
 int set_error(int code, const char* msg) {
@@ -133,6 +135,28 @@ int b200q_gemm(int type, int elem, const void* w, const void* x, void* y, int M,
     if (rc == B200Q_ERR_UNSUPPORTED)
         return set_error(rc, "b200q_gemm needs K a multiple of 64 and of the block size, 16-byte aligned activation rows and Q4_K weights");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemm failed");
+    return B200Q_OK;
+}
+
+// Small batches (1..16 rows) on the tensor cores with int8 operands: quantizes x into `workspace`, then streams the weights once.
+long long b200q_gemv_tc_workspace_bytes(int type, int K) {
+    if (type_block_bytes(type) == 0 || K <= 0 || K % 256 != 0) return 0;
+    return (long long)gemv_tc_workspace_bytes(type, K);
+}
+
+int b200q_gemv_tc(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace,
+                  long long workspace_bytes, void* stream) {
+    if (!w || !x || !y || !workspace) return set_error(B200Q_ERR_INVALID, "null pointer");
+    if (type_block_bytes(type) == 0) return set_error(B200Q_ERR_UNSUPPORTED, "weight type is not Q8_0, Q4_K or Q6_K");
+    if (elem != ELEM_BF16 && elem != ELEM_F16 && elem != ELEM_F32) return set_error(B200Q_ERR_INVALID, "unknown element type");
+    if (M > 16) return set_error(B200Q_ERR_TOO_LARGE, "b200q_gemv_tc takes at most 16 activation rows");
+    if (K <= 0 || K % 256 != 0) return set_error(B200Q_ERR_UNSUPPORTED, "b200q_gemv_tc needs K a multiple of 256");
+    if (workspace_bytes < (long long)gemv_tc_workspace_bytes(type, K)) return set_error(B200Q_ERR_INVALID, "workspace smaller than b200q_gemv_tc_workspace_bytes");
+    const int rc = gemv_tc_dispatch(type, elem, w, x, y, M, N, K, ldx, ldy, workspace, (cudaStream_t)stream);
+    if (rc == B200Q_ERR_UNSUPPORTED)
+        return set_error(rc, "b200q_gemv_tc needs 16-byte aligned weights whose rows are a multiple of 16 bytes (Q6_K: K a multiple of 2048)");
+    if (rc == B200Q_ERR_INVALID) return set_error(rc, "workspace must be 128-byte aligned");
+    if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemv_tc failed");
     return B200Q_OK;
 }
 

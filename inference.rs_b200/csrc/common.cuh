@@ -145,6 +145,23 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// Three barriers at once: the polls are issued back to back so that their shared-memory round trips overlap (a poll
+// queues behind whatever loads and stores the CTA's other warps have in flight, which can be hundreds of cycles).
+__device__ __forceinline__ bool mbar_wait3_bounded(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1, uint64_t* b2, uint32_t p2) {
+    bool d0 = false, d1 = false, d2 = false;
+    for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+        const bool t0 = d0 || mbar_try_wait(b0, p0);
+        const bool t1 = d1 || mbar_try_wait(b1, p1);
+        const bool t2 = d2 || mbar_try_wait(b2, p2);
+        d0 = t0;
+        d1 = t1;
+        d2 = t2;
+        if (d0 && d1 && d2) return true;
+        if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
+    }
+    return false;
+}
+
 // 1-D bulk copy global -> shared through the TMA unit; completion counted in bytes on `bar`.
 // dst, src and bytes must be multiples of 16.
 __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
@@ -188,6 +205,32 @@ __device__ __forceinline__ uint32_t lds16(uint32_t a) {
     return v;
 }
 __device__ __forceinline__ float lds_f32(uint32_t a) { return __uint_as_float(lds32(a)); }
+
+// `NW` 32-bit words starting `O` bytes (even, compile time) into the 16-byte-aligned words c[]
+template <int O, int NW, int NC>
+__device__ __forceinline__ void extract_words(const uint32_t (&c)[NC], uint32_t (&out)[NW]) {
+    constexpr int wo = O >> 2;
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+        if constexpr ((O & 2) == 0) {
+            out[i] = c[wo + i];
+        } else if constexpr (wo + NW < NC) {
+            out[i] = __funnelshift_r(c[wo + i], c[wo + i + 1], 16);
+        } else {
+            // the last word's upper half would come from beyond c[]: the callers only use its lower half
+            out[i] = (wo + i + 1 < NC) ? __funnelshift_r(c[wo + i], c[(wo + i + 1 < NC) ? wo + i + 1 : NC - 1], 16) : (c[wo + i] >> 16);
+        }
+    }
+}
+template <int NCHUNK>
+__device__ __forceinline__ void lds_chunks(uint32_t addr, uint32_t (&c)[4 * NCHUNK]) {
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+        const uint4 v = lds128(addr + 16 * i);
+        c[4 * i] = v.x; c[4 * i + 1] = v.y; c[4 * i + 2] = v.z; c[4 * i + 3] = v.w;
+    }
+}
+
 
 // int -> float without the conversion unit: exact for |v| < 2^22 (adds v ulps to 1.5 * 2^23, then subtracts it)
 __device__ __forceinline__ float int_to_float_small(int v) { return __int_as_float(0x4B400000 + v) - 12582912.0f; }

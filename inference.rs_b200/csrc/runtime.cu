@@ -61,6 +61,10 @@ void set_trace_buffer(unsigned long long* dev, int records) {
     g_trace_records = records;
     g_trace_next = 0;
 }
+unsigned long long* trace_buffer(int* slots) {
+    *slots = g_trace ? g_trace_records * 16 : 0;
+    return g_trace;
+}
 unsigned long long* trace_slot() {
     if (g_trace == nullptr || g_trace_records <= 0) return nullptr;
     const int i = g_trace_next.fetch_add(1) % g_trace_records;

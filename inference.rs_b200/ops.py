@@ -124,6 +124,31 @@ def gemm(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.
     return y
 
 
+def gemv_tc_workspace(dtype: GgmlDType, k: int, device="cuda") -> torch.Tensor:
+    """Scratch for `gemv_tc`: `b200q_gemv_tc_workspace_bytes` bytes, 128-byte aligned (torch's allocations are)."""
+    nbytes = int(kl.library().b200q_gemv_tc_workspace_bytes(int(dtype), k))
+    if nbytes <= 0:
+        raise kl.KernelLibraryError(f"b200q_gemv_tc does not take K = {k}")
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+
+def gemv_tc(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.Tensor | None = None,
+            workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """`b200q_gemv_tc`: 1..16 activation rows on the tensor cores (int8). x [m, k] (rows may be strided) -> [m, n] of
+    x's dtype. `workspace` from `gemv_tc_workspace`; allocated per call when not given."""
+    if not (w.is_cuda and x.is_cuda) or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("expected CUDA tensors and rows of unit stride")
+    m, k = x.shape
+    y = torch.empty((m, n), dtype=x.dtype, device=x.device) if out is None else out
+    if y.stride(1) != 1:
+        raise ValueError("expected output rows of unit stride")
+    ws = gemv_tc_workspace(dtype, k, x.device) if workspace is None else workspace
+    kl.check(kl.library().b200q_gemv_tc(int(dtype), elem_of(x.dtype), w.data_ptr(), x.data_ptr(), y.data_ptr(), m, n, k,
+                                        x.stride(0), y.stride(0), ws.data_ptr(), ws.numel() * ws.element_size(), _stream()),
+             "b200q_gemv_tc")
+    return y
+
+
 def gemv_plan(dtype: GgmlDType, k: int, n: int, b: int) -> dict:
     out = (C.c_int * 10)()
     kl.check(kl.library().b200q_gemv_plan(int(dtype), k, n, b, C.byref(out)), "b200q_gemv_plan")

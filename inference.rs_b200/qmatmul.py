@@ -15,6 +15,37 @@ from . import ops
 from .dtypes import MATRIX_ROW_PADDING, GgmlDType, pad
 
 MMVQ_MAX_BATCH = 8  # rows the decode GEMV launchers take (fast_mmvq.rs:84)
+TENSOR_CORE_MAX_ROWS = 16  # rows the small-batch tensor-core kernel takes (fast_mmvq.rs:86)
+# 3..8 rows: the tier pays once a CTA's share of the weight rows fills enough of its 128-row MMAs (measured on B200
+# against the dp4a GEMV at the Llama-3-8B shapes); 9..16 rows: always (the alternative is the prefill GEMM)
+TENSOR_CORE_MIN_WEIGHT_ROWS = {3: 16384, 4: 16384, 5: 8192, 6: 8192, 7: 8192, 8: 8192}
+
+_tc_workspaces: dict = {}
+
+
+def _tc_workspace(dtype: GgmlDType, k: int, device: torch.device) -> torch.Tensor:
+    """One scratch buffer per (device, stream, type, k), like the reference's per-thread, per-stream activation
+    workspace (crates/inference-quant/src/gguf/thread_workspace.rs:94-146): its address is stable, so captured
+    graphs can replay, and calls on one stream are ordered, so they never overlap on it."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream, int(dtype), k)
+    ws = _tc_workspaces.get(key)
+    if ws is None:
+        ws = _tc_workspaces[key] = ops.gemv_tc_workspace(dtype, k, device)
+    return ws
+
+
+def tensor_core_rows_supported(dtype: GgmlDType, k: int) -> bool:
+    """Shapes `b200q_gemv_tc` takes: whole 256-value chunks and packed rows of a multiple of 16 bytes."""
+    return k % 256 == 0 and dtype.row_bytes(k) % 16 == 0
+
+
+def prefers_tensor_core_rows(dtype: GgmlDType, rows: int, n: int, k: int) -> bool:
+    """The small-batch tensor-core tier (fast_mmvq.rs:118-134: 2..16 rows where a type has it). Here: 9..16 rows
+    always, 3..8 rows when the matrix has enough rows to fill the 128-row tiles of 148 CTAs; 1..2 rows stay on the
+    one-launch GEMV."""
+    if rows > TENSOR_CORE_MAX_ROWS or rows < 3 or not tensor_core_rows_supported(dtype, k):
+        return False
+    return rows > MMVQ_MAX_BATCH or n >= TENSOR_CORE_MIN_WEIGHT_ROWS[rows]
 
 
 class QTensor:
@@ -76,8 +107,8 @@ class QMatMul:
 
 
 def prefers_mmvq(rows: int) -> bool:
-    """Decode GEMV for up to MMVQ_MAX_BATCH rows, the prefill GEMM above (fast_mmvq.rs:96-134 collapses to this once the
-    small-batch tensor-core matvec is not in play)."""
+    """Decode GEMV for up to MMVQ_MAX_BATCH rows where the tensor-core tier does not take them, the prefill GEMM above
+    (fast_mmvq.rs:96-134)."""
     return rows <= MMVQ_MAX_BATCH
 
 
@@ -86,6 +117,8 @@ def _forward_rows(w: QTensor, x: torch.Tensor, act_quant: int) -> torch.Tensor:
     rows = x.shape[0]
     if rows == 0:
         return torch.empty((0, n), dtype=x.dtype, device=x.device)
+    if act_quant == ops.ACT_QUANT_Q8_1 and prefers_tensor_core_rows(w.dtype, rows, n, k):
+        return ops.gemv_tc(w.dtype, w.data, x, n, workspace=_tc_workspace(w.dtype, k, x.device))
     if prefers_mmvq(rows):
         if k % 128 == 0:
             return ops.gemv(w.dtype, w.data, x, n, act_quant=act_quant)

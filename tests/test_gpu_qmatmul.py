@@ -40,6 +40,41 @@ def test_qmatmul_forward_matches_the_cpu_path(type_id, rows):
     assert_device_ok()
 
 
+@pytest.mark.parametrize("type_id", TYPES)
+def test_rows_3_to_16_take_the_tensor_core_tier_where_it_pays(type_id):
+    from inference_rs_b200 import qmatmul as qm
+    n, k = 9000, 2048
+    dt = DT[type_id]
+    assert qm.prefers_tensor_core_rows(dt, 5, n, k) and qm.prefers_tensor_core_rows(dt, 12, n, k) and not qm.prefers_tensor_core_rows(dt, 3, n, k)
+    assert qm.prefers_tensor_core_rows(dt, 12, 64, k) and not qm.prefers_tensor_core_rows(dt, 5, 64, k)
+    assert not qm.prefers_tensor_core_rows(dt, 2, n, k) and not qm.prefers_tensor_core_rows(dt, 17, n, k)
+    assert not qm.prefers_tensor_core_rows(pkg.GgmlDType.Q6K, 12, n, 512)  # 210-byte blocks: rows not a multiple of 16 bytes
+    packed = kq.quantize(type_id, seeded_weights(n, k, 51))
+    qmm = QMatMul.from_qtensor(QTensor.from_packed(packed, dt, (n, k)))
+    for rows in (5, 12):
+        for dtype in (torch.float32, torch.bfloat16):
+            x = seeded_acts(rows, k, 70 + rows, dtype)
+            y = qmm.forward(x.cuda())
+            assert y.shape == (rows, n) and y.dtype == dtype
+            cpu = kq.matmul(type_id, as_f32_numpy(x), packed, n)
+            err = np.abs(as_f32_numpy(y) - cpu).max()
+            assert err <= 1e-3 + 1e-2 * np.abs(cpu).max(), (rows, dtype, err)
+    # the tier's scratch keeps its address per stream, so a captured forward can be replayed
+    x = seeded_acts(12, k, 90, torch.bfloat16).cuda()
+    eager = qmm.forward(x)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        qmm.forward(x)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            out = qmm.forward(x)
+        g.replay()
+        stream.synchronize()
+    assert torch.equal(out, eager)
+    assert_device_ok()
+
+
 def test_qmatmul_errors_mirror_the_reference():
     q = QTensor.from_packed(kq.quantize(kq.Q4_K, seeded_weights(8, 256, 1)), DT[kq.Q4_K], (8, 256))
     qmm = QMatMul.from_qtensor(q)
