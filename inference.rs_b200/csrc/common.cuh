@@ -145,6 +145,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// Two barriers at once (see mbar_wait3_bounded).
+__device__ __forceinline__ bool mbar_wait2_bounded(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1) {
+    bool d0 = false, d1 = false;
+    for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+        const bool t0 = d0 || mbar_try_wait(b0, p0);
+        const bool t1 = d1 || mbar_try_wait(b1, p1);
+        d0 = t0;
+        d1 = t1;
+        if (d0 && d1) return true;
+        if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
+    }
+    return false;
+}
+
 // Three barriers at once: the polls are issued back to back so that their shared-memory round trips overlap (a poll
 // queues behind whatever loads and stores the CTA's other warps have in flight, which can be hundreds of cycles).
 __device__ __forceinline__ bool mbar_wait3_bounded(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1, uint64_t* b2, uint32_t p2) {

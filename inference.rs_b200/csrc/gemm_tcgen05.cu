@@ -550,24 +550,41 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_staged_kernel(co
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_f16(ElemFormat<T>::value, GEMM_BM, GEMM_BN);
             bool ok = true;
+            const uint64_t da0 = make_smem_desc_sw128(smem_u32(a_stages));
+            const uint64_t db0 = make_smem_desc_sw128(smem_u32(b_stages));
+            int s = 0;
+            uint32_t ph = 0;
+            bool ready = false;  // the polls made while the previous block's MMAs were issued found this block complete
             for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % GEMM2_STAGES;
-                const uint32_t ph = (kb / GEMM2_STAGES) & 1;
-                if (!mbar_wait_bounded(&bars->full_a[s], ph) || !mbar_wait_bounded(&bars->full_b[s], ph)) {
+                // both barriers polled together: a poll's round trip through the busy shared-memory pipe costs hundreds
+                // of cycles, more than the tensor core needs for a block, so they must not add up
+                if (!ready && !mbar_wait2_bounded(&bars->full_a[s], ph, &bars->full_b[s], ph)) {
                     record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, kb);
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint64_t db = make_smem_desc_sw128(smem_u32(b_stages + (size_t)s * GEMM_B_BYTES));
+                const uint64_t db = db0 + (uint64_t)(s * (GEMM_B_BYTES >> 4));
+                const uint64_t da = da0 + (uint64_t)(s * MT * (GEMM_A_BYTES >> 4));
+                const int cur = s;
+                if (++s == GEMM2_STAGES) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+                bool n0 = false, n1 = false;
+                if (kb + 1 < nkb) {
+                    n0 = mbar_try_wait(&bars->full_a[s], ph);
+                    n1 = mbar_try_wait(&bars->full_b[s], ph);
+                }
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
-                    const uint64_t da = make_smem_desc_sw128(smem_u32(a_stages + (size_t)(s * MT + t) * GEMM_A_BYTES));
 #pragma unroll
                     for (int k = 0; k < GEMM_BK / 16; ++k)
-                        tc_mma_f16(tmem_base + t * GEMM_BN, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        tc_mma_f16(tmem_base + t * GEMM_BN, da + (uint64_t)(t * (GEMM_A_BYTES >> 4) + 2 * k), db + 2 * k, idesc,
+                                   (kb > 0 || k > 0) ? 1u : 0u);
                 }
-                tc_commit(&bars->empty[s]);
+                tc_commit(&bars->empty[cur]);
+                ready = n0 && n1;
             }
             if (ok) tc_commit(&bars->tmem_full);
         }
@@ -619,6 +636,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_staged_kernel(co
                 const int kb = 4 * kc + J;
                 const int s = kb % GEMM2_STAGES;
                 float v[32];
+                // polled before the arithmetic so that the poll's round trip overlaps it
+                const bool free_now = mbar_try_wait(&bars->empty[s], ((kb / GEMM2_STAGES) & 1) ^ 1);
                 if (ok && row_ok) {
                     if (J == 0) RawDequant<TYPE>::template values<0>(rb, kc, h, v);
                     else if (J == 1) RawDequant<TYPE>::template values<1>(rb, kc, h, v);
@@ -628,7 +647,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_staged_kernel(co
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.0f;
                 }
-                if (ok && !mbar_wait_bounded(&bars->empty[s], ((kb / GEMM2_STAGES) & 1) ^ 1)) {
+                if (ok && !free_now && !mbar_wait_bounded(&bars->empty[s], ((kb / GEMM2_STAGES) & 1) ^ 1)) {
                     record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, kb);
                     ok = false;
                 }
