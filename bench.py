@@ -133,6 +133,11 @@ def time_launch_list(torch, stream, launches, reps):
     return e0.elapsed_time(e1) * 1000.0 / (reps * len(launches))
 
 
+# DRAM bytes per launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum); the summaries are under profiles/
+NCU_TRAFFIC_GEMV_Q4K_4096_14336 = 33085184
+NCU_TRAFFIC_GROUP_GATE_UP = 66442752
+
+
 def run_single(args):
     """--single TYPE K N B: one GEMV shape over rotating weight copies (> L2 in total); prints one JSON line. This is
     the small case profiler captures run on."""
@@ -158,6 +163,11 @@ def run_single(args):
                     vy = ops.quantize_q8_1(x)
                     ops.mmvq_plain(dt, w, vy, n, k, b, torch.bfloat16)
                 return fn
+        elif args.group2:
+            outs2 = [torch.empty(b, n, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+
+            def mk(w):
+                return lambda: ops.gemv_group([dt, dt], [w, ws[0]], x, [n, n], outs=outs2)
         elif args.tc:
             tc_ws = ops.gemv_tc_workspace(dt, k)
 
@@ -183,9 +193,11 @@ def run_single(args):
             us = time_launch_list(torch, stream, launches, args.steps)
     peak, src = load_peaks()
     alg = wbytes + b * k * 2 + b * n * 2
+    if args.group2:
+        alg = 2 * wbytes + b * k * 2 + 2 * b * n * 2
     print(json.dumps({"single": tname, "k": k, "n": n, "b": b, "copies": copies, "us_per_launch": us,
                       "GBps": alg / us / 1e3, "frac_of_" + src: alg / us / 1e3 / peak, "algorithmic_bytes": alg,
-                      "kernel": "gemv_tc" if args.tc else "gemv", "plan": None if (args.tc or b > 8) else ops.gemv_plan(dt, k, n, b), "device_status": list(pkg.kernel_library.device_status())}),
+                      "kernel": "gemv_tc" if args.tc else ("gemv_group x2" if args.group2 else "gemv"), "plan": None if (args.tc or b > 8) else ops.gemv_plan(dt, k, n, b), "device_status": list(pkg.kernel_library.device_status())}),
           flush=True)
 
 
@@ -317,6 +329,7 @@ def main():
     ap.add_argument("--no-group", action="store_true", help="one launch per projection instead of grouped q/k/v and gate/up")
     ap.add_argument("--sweep", action="store_true", help="also time every shape of the decode sweep")
     ap.add_argument("--single", nargs=4, metavar=("TYPE", "K", "N", "B"), help="time one GEMV shape only (q4_k|q6_k|q8_0)")
+    ap.add_argument("--group2", action="store_true", help="with --single: two matrices of the shape in one grouped launch (B = 1)")
     ap.add_argument("--tc", action="store_true", help="with --single: the small-batch tensor-core kernel (B up to 16)")
     ap.add_argument("--gemm", nargs=4, metavar=("TYPE", "K", "N", "M"), help="time one prefill GEMM shape only")
     ap.add_argument("--copies", type=int, default=0, help="--single: number of rotating weight copies")
@@ -483,15 +496,29 @@ def main():
         h2d = sum(v.numel() * v.element_size() for v in x_host.values())
         d2h = logits_host.numel() * logits_host.element_size()
 
-        # ---- roofline of the dominant kernel: Q4_K GEMV at the ffn_gate / ffn_up shape over 64 distinct weights
+        # ---- roofline of the dominant launch (largest share of the step's device time in the ncu launch list): the
+        # ffn_gate + ffn_up GEMVs, one grouped launch per layer when grouping is on, timed alone over all layers'
+        # distinct weights (2 GB, far beyond L2)
         gate_idx = [i for i, p in enumerate(projs) if p.name in ("ffn_gate", "ffn_up")]
-        gate_idx = gate_idx if not tp else gate_idx[:1]
         gp = projs[gate_idx[0]]
-        dom_ws = [layers[li][i] for li in range(min(model.layers, 32)) for i in gate_idx]
-        dom_out = torch.empty(1, gp.n, dtype=torch.bfloat16, device="cuda")
-        dom_us = time_launch_list(torch, stream, [(lambda w=w: ops.gemv(gp.dtype, w, x_dev[gp.k], gp.n, out=dom_out))
-                                                  for w in dom_ws], 10)
-        dom_bytes = gp.weight_bytes + gp.k * 2 + gp.n * 2
+        nl = min(model.layers, 32)
+        if not args.no_group and not tp and len(gate_idx) == 2:
+            dom_kernel = "gemv_group_kernel<bf16, b=1> (ffn_gate + ffn_up, Q4_K)"
+            dom_outs = [torch.empty(1, gp.n, dtype=torch.bfloat16, device="cuda") for _ in gate_idx]
+            dom_list = [(lambda li=li: ops.gemv_group([gp.dtype, gp.dtype], [layers[li][i] for i in gate_idx], x_dev[gp.k],
+                                                      [gp.n, gp.n], outs=dom_outs)) for li in range(nl)]
+            dom_bytes = 2 * gp.weight_bytes + gp.k * 2 + 2 * gp.n * 2
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape (ncu capture
+            # summarised in profiles/gemv_group_q4k_gate_up.txt)
+            dom_traffic = NCU_TRAFFIC_GROUP_GATE_UP if (gp.k, gp.n) == (4096, 14336) else None
+        else:
+            dom_kernel = "gemv_staged_kernel<Q4_K, b=1, bf16>"
+            dom_out = torch.empty(1, gp.n, dtype=torch.bfloat16, device="cuda")
+            dom_list = [(lambda w=layers[li][i]: ops.gemv(gp.dtype, w, x_dev[gp.k], gp.n, out=dom_out))
+                        for li in range(nl) for i in gate_idx[:1 if tp else 2]]
+            dom_bytes = gp.weight_bytes + gp.k * 2 + gp.n * 2
+            dom_traffic = NCU_TRAFFIC_GEMV_Q4K_4096_14336 if (gp.k, gp.n) == (4096, 14336) else None
+        dom_us = time_launch_list(torch, stream, dom_list, 10)
         peak, peak_src = load_peaks()
         achieved = dom_bytes / (dom_us * 1e-6) / 1e9
         clocks.__exit__(None, None, None)
@@ -522,6 +549,26 @@ def main():
                     prefill.append({"type": dt.name, "k": k, "n": n, "m": m, "us": round(us, 1), "TFLOPs": round(tf, 1),
                                     "frac_of_measured_bf16_peak": round(tf / bf16_peak, 3)})
                     del wq, xm, ym
+
+        small = None
+        if not tp:
+            # the decode sweep's batch 4 and 16 through the operator (QMatMul picks the kernel): weights-only GB/s
+            small = []
+            for dt, k, n in ((pkg.GgmlDType.Q4K, 4096, 6144), (pkg.GgmlDType.Q4K, 4096, 28672), (pkg.GgmlDType.Q4K, 14336, 4096),
+                             (pkg.GgmlDType.Q6K, 14336, 4096), (pkg.GgmlDType.Q6K, 4096, 128256)):
+                wbytes = n * dt.row_bytes(k)
+                copies = max(2, min(8, int(600e6 // wbytes) + 1))
+                qms = [pkg.QMatMul.from_qtensor(pkg.QTensor(random_blocks_device(torch, dt, n, k, gen), dt, (n, k))) for _ in range(copies)]
+                for b in (4, 16):
+                    xb = torch.randn(b, k, device="cuda", generator=gen).to(torch.bfloat16)
+                    qms[0].forward(xb)
+                    us = time_launch_list(torch, stream, [(lambda q=q: q.forward(xb)) for q in qms], max(3, int(2e9 // (wbytes * copies))))
+                    from inference_rs_b200 import qmatmul as _qm
+                    kern = ("gemv_tc" if _qm.prefers_tensor_core_rows(dt, b, n, k) else ("gemv" if b <= 8 else "gemm"))
+                    small.append({"type": dt.name, "k": k, "n": n, "b": b, "kernel": kern, "us": round(us, 2),
+                                  "GBps": round((wbytes + b * k * 2 + b * n * 2) / us / 1e3, 1),
+                                  "frac_of_measured_hbm": round((wbytes + b * k * 2 + b * n * 2) / us / 1e3 / peak, 3)})
+                del qms
 
         sweep = None
         if args.sweep:
@@ -560,14 +607,16 @@ def main():
         "hbm_frac_of_nominal_8TBps": bytes_per_step * tok_s / 8e12,
         "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "gemv_staged_kernel<Q4_K, b=1, bf16>", "shape": f"K={gp.k} N={gp.n}",
+        "roofline": {"bound": "hbm", "kernel": dom_kernel, "shape": f"K={gp.k} N={gp.n}",
                      "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
-                     "us_per_launch": dom_us, "algorithmic_bytes": dom_bytes, "traffic": None},
+                     "us_per_launch": dom_us, "algorithmic_bytes": dom_bytes, "traffic": dom_traffic},
         "clocks": clocks.summary(),
         "device_status": list(status),
     }
     if prefill is not None:
         line["prefill_gemm"] = prefill
+    if small is not None:
+        line["small_batch"] = small
     if sweep is not None:
         line["sweep"] = sweep
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
