@@ -162,7 +162,8 @@ int b200q_gemm(int type, int elem, const void* w, const void* x, void* y, int M,
  * (crates/inference-quant/src/gguf/fast_mmvq.rs:2049-2126) with launch_mmvq_tc_quantize_<elem> +
  * launch_mmvq_tc_gguf_<type>_<elem>_plain (ffi.rs:631-652,954-998; kernel mmvq_gguf/mmvq_tc_k.cuh:221-329).
  * Needs K a multiple of 256, w 16-byte aligned with a row size that is a multiple of 16 bytes (Q6_K: K a multiple of
- * 2048), workspace 128-byte aligned and at least b200q_gemv_tc_workspace_bytes(type, K) bytes (0 = unsupported K);
+ * 2048), workspace 128-byte aligned and at least b200q_gemv_tc_workspace_bytes(type, K) bytes (0 = unsupported K;
+ * 18 K bytes, 34 K for Q6_K, plus 1.3 MB for the partial outputs of matrices that are split along K);
  * the workspace is the caller's, as the reference's activation scratch is (gguf/thread_workspace.rs:94-146), and
  * must not be shared by calls that can overlap on the GPU. */
 long long b200q_gemv_tc_workspace_bytes(int type, int K);

@@ -42,6 +42,8 @@ int b200q_set_option(const char* name, int value) {
     else if (!std::strcmp(name, "gemv_stage_bytes")) {
         if (value < 1024) return set_error(B200Q_ERR_INVALID, "gemv_stage_bytes must be >= 1024");
         rt.gemv_stage_target = value;
+    } else if (!std::strcmp(name, "tc_ksplit")) {
+        rt.tc_ksplit = value ? 1 : 0;
     } else if (!std::strcmp(name, "gemm_direct")) {
         rt.gemm_direct = value ? 1 : 0;
     } else if (!std::strcmp(name, "gemv_ctas_per_sm")) {
@@ -60,6 +62,7 @@ int b200q_get_option(const char* name, int* value) {
     else if (!std::strcmp(name, "gemv_stage_bytes")) *value = rt.gemv_stage_target;
     else if (!std::strcmp(name, "gemv_ctas_per_sm")) *value = rt.gemv_ctas_per_sm;
     else if (!std::strcmp(name, "gemm_direct")) *value = rt.gemm_direct;
+    else if (!std::strcmp(name, "tc_ksplit")) *value = rt.tc_ksplit;
     else if (!std::strcmp(name, "sm_count")) *value = rt.sm_count;
     else if (!std::strcmp(name, "smem_optin")) *value = rt.smem_optin;
     else return set_error(B200Q_ERR_INVALID, "unknown option");

@@ -21,7 +21,10 @@
 //                     into its own TMEM columns (no accumulation across blocks: scales differ);
 //        warps 12-27  read the integer sums from TMEM (thread = weight row), apply block and activation scales and
 //                     accumulate in f32 registers; at the end of a tile they store the outputs.
-//      TMEM holds two stages' sums so that scaling stage g overlaps the MMAs of stage g + 1.
+//      TMEM holds several stages' sums so that scaling stage g overlaps the MMAs of the following stages.
+//      A matrix with too few rows to give every SM a useful tile (N <= 74 tiles of 128 rows) is split along K as
+//      well: each CTA takes a run of 256-k stages of ONE full-height tile, writes its partial outputs to the
+//      workspace, and the last CTA to arrive for a tile's 32-row quarter adds the partials in split order.
 //
 // Every wait is bounded; a wait that gives up records a code in the device status word, work is skipped, and the
 // kernel still frees its TMEM columns before it returns.
@@ -43,6 +46,9 @@ constexpr int TCQ_SCALE_WARPS = 16;            // warps 12..27
 constexpr int TCQ_THREADS = 32 * (4 + TCQ_UNPACK_WARPS + TCQ_SCALE_WARPS);
 constexpr int TCQ_OUT_BYTES = TCQ_ROWS * TCQ_TOKENS * 4;  // partial-sum exchange between the scaling warps of a row
 constexpr int TCQ_SMEM_LIMIT = 232448;
+constexpr int TCQ_MAX_CTAS = 160;                       // K-split mode: at most one CTA per SM
+constexpr int TCQ_COUNTERS = TCQ_MAX_CTAS * 4;          // one per (tile, TMEM lane quarter)
+constexpr size_t TCQ_PARTIAL_BYTES = (size_t)TCQ_MAX_CTAS * TCQ_ROWS * TCQ_TOKENS * sizeof(float);  // sum over tiles of ksplit * 16 * rows
 
 // X_STAGES: the activation ring is deep because an SM's loads return in order: a tile requested now arrives after the
 // packed-row stages already in flight, several stage times later.
@@ -80,6 +86,13 @@ struct TcqParams {
     int tile_rows;                 // rows a tile loads (multiple of 8, <= 128)
     int a_stages, raw_stages;      // ring depths (2..4 and 2..8), as many as the tile's stage sizes leave room for
     int rows_per_cta, rows_extra;  // CTA c owns rows [c * q + min(c, r), ...) with q = rows_per_cta, r = rows_extra
+    // matrices with too few rows to give every SM a useful tile are split along K as well: ksplit > 1 makes CTA c take
+    // the 256-k stages [s * nkc / ksplit, (s + 1) * nkc / ksplit), s = c % ksplit, of the single tile c / ksplit; the
+    // splits' partial outputs meet in `partial` [ksplit][16][N] and the last to arrive (counter per tile and lane
+    // quarter, zeroed by the quantize launch) adds them in split order and stores
+    int ksplit;
+    float* partial;
+    unsigned int* counters;
     unsigned int* status;
     unsigned long long* trace;  // optional: SM clock of CTA 0's pipeline events, [event 0..7][stage 0..trace_stages)
     int trace_stages;
@@ -96,8 +109,13 @@ struct TcqParams {
 // ---------------------------------------------------------------------------------------------
 template <typename src_t, bool SPLIT_HALVES>
 __global__ void __launch_bounds__(32 * TCQ_TOKENS) tcq_quantize_kernel(const src_t* __restrict__ x, int8_t* __restrict__ q,
-                                                                      float2* __restrict__ ds, int K, int M, int ldx) {
+                                                                      float2* __restrict__ ds, int K, int M, int ldx,
+                                                                      unsigned int* __restrict__ counters) {
     const int kb = blockIdx.x, row = threadIdx.y, lane = threadIdx.x;
+    if (kb == 0) {  // the K-split arrival counters of the launch that follows
+        const int i = row * 32 + lane;
+        for (int c = i; c < TCQ_COUNTERS; c += 32 * TCQ_TOKENS) counters[c] = 0u;
+    }
     const int k = kb * 32 + lane;
     const float xi = row < M ? to_float<src_t>(x[(size_t)row * ldx + k]) : 0.0f;
     const float amax = warp_max(fabsf(xi));
@@ -319,11 +337,22 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
-    const int row0 = cta * p.rows_per_cta + min(cta, p.rows_extra);
-    const int row1 = min(p.N, row0 + p.rows_per_cta + (cta < p.rows_extra ? 1 : 0));
+    const int nkc_all = p.K / TCQ_KC;
+    int row0, row1, kc0, kc1;
+    if (p.ksplit > 1) {
+        const int tile = cta / p.ksplit, split = cta - tile * p.ksplit;
+        row0 = tile * TH;
+        row1 = min(p.N, row0 + TH);
+        kc0 = split * nkc_all / p.ksplit;
+        kc1 = (split + 1) * nkc_all / p.ksplit;
+    } else {
+        row0 = cta * p.rows_per_cta + min(cta, p.rows_extra);
+        row1 = min(p.N, row0 + p.rows_per_cta + (cta < p.rows_extra ? 1 : 0));
+        kc0 = 0;
+        kc1 = nkc_all;
+    }
     const int ntiles = row1 > row0 ? (row1 - row0 + TH - 1) / TH : 0;
-    const int nkc = p.K / TCQ_KC;
-    const int nstages = ntiles * nkc;
+    const int nstages = ntiles * (kc1 - kc0);
 
     if (tid == 0) {
         for (int s = 0; s < NR; ++s) {
@@ -359,7 +388,7 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
         // ---------------- activation tiles (two XROWS x 128-byte boxes) and their scales ----------------
         if (lane == 0) {
             TcqRing xr;
-            int kc = 0, g = 0;
+            int kc = kc0, g = 0;
             bool ok = true;
             for (; g < nstages; ++g) {
                 if (!mbar_wait_bounded(&bars->x_empty[xr.i], xr.ph ^ 1)) {
@@ -374,7 +403,7 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
                 tma_load_2d(st + TT::XROWS * 128, &tmap_x, kc * TCQ_KC + 128, 0, &bars->x_full[xr.i]);
                 bulk_copy_g2s(st + TT::XROWS * TCQ_KC, p.ds + (size_t)kc * TCQ_DS_BYTES, TCQ_DS_BYTES, &bars->x_full[xr.i]);
                 xr.next(XS);
-                if (++kc == nkc) kc = 0;
+                if (++kc == kc1) kc = kc0;
             }
             if (!ok) {  // let the copies already issued land before the CTA may exit: the last min(g, XS) stages
                 for (int q = 0; q < min(g, XS); ++q) {
@@ -391,7 +420,7 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
         // ---------------- packed rows: one box of tile_rows x chunk bytes per stage ----------------
         if (lane == 0) {
             TcqRing rr;
-            int kc = 0, t = 0, g = 0;
+            int kc = kc0, t = 0, g = 0;
             bool ok = true;
             for (; g < nstages; ++g) {
                 if (!mbar_wait_bounded(&bars->raw_empty[rr.i], rr.ph ^ 1)) {
@@ -406,8 +435,8 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
                 else xcoord = (kc * TT::CHUNK) & ~15;                             // bytes, rounded down to the TMA grain
                 tma_load_2d(raw_stages + (size_t)rr.i * raw_bytes, &tmap_w, xcoord, row0 + t * TH, &bars->raw_full[rr.i]);
                 rr.next(NR);
-                if (++kc == nkc) {
-                    kc = 0;
+                if (++kc == kc1) {
+                    kc = kc0;
                     ++t;
                 }
             }
@@ -469,12 +498,12 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
         const int grp = ut >> 7;
         const int r = ut & (TCQ_ROWS - 1);
         TcqRing rr, ar, sr;
-        int kc = 0;
+        int kc = kc0;
         if (grp == 1) {  // first stage of this group is g = 1
             rr.next(NR);
             ar.next(NA);
             sr.next(TCQ_SC_STAGES);
-            if (++kc == nkc) kc = 0;
+            if (++kc == kc1) kc = kc0;
         }
         bool ok = true;
         for (int g = grp; g < nstages; g += 2) {
@@ -505,7 +534,7 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
                 rr.next(NR);
                 ar.next(NA);
                 sr.next(TCQ_SC_STAGES);
-                if (++kc == nkc) kc = 0;
+                if (++kc == kc1) kc = kc0;
             }
         }
     } else if (warp >= 4 + TCQ_UNPACK_WARPS) {
@@ -520,7 +549,7 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
 #pragma unroll
         for (int t = 0; t < TOK; ++t) acc[t] = 0.0f;
         TcqRing xr, sr, tr;
-        int kc = 0, t = 0;
+        int kc = kc0, t = 0;
         bool ok = true;
         for (int g = 0; g < nstages; ++g) {
             ok = mbar_wait3_bounded(&bars->tmem_full[tr.i], tr.ph, &bars->sc_full[sr.i], sr.ph, &bars->x_full[xr.i], xr.ph);
@@ -578,8 +607,8 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
             xr.next(XS);
             sr.next(TCQ_SC_STAGES);
             tr.next(TB);
-            if (++kc == nkc) {
-                kc = 0;
+            if (++kc == kc1) {
+                kc = kc0;
                 // ---------------- end of a tile: the four warps of a row add up through shared memory in a fixed
                 // order (block pairs 0, 1, 2, 3: results do not depend on timing), the last one stores ----------------
                 float* o = out_buf + r * TCQ_TOKENS;
@@ -608,11 +637,43 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
                         for (int tt = 0; tt < TOK; ++tt) o[tt] = acc[tt];
                     } else {
                         const int grow = row0 + t * TH + r;
-                        if (r < TH && grow < row1) {
-                            dst_t* y = reinterpret_cast<dst_t*>(p.y) + grow;
+                        const bool row_ok = r < TH && grow < row1;
+                        dst_t* y = reinterpret_cast<dst_t*>(p.y) + grow;
+                        if (p.ksplit <= 1) {
+                            if (row_ok) {
 #pragma unroll
-                            for (int tt = 0; tt < TOK; ++tt)
-                                if (tt < p.M) y[(size_t)tt * p.ldy] = from_float<dst_t>(acc[tt]);
+                                for (int tt = 0; tt < TOK; ++tt)
+                                    if (tt < p.M) y[(size_t)tt * p.ldy] = from_float<dst_t>(acc[tt]);
+                            }
+                        } else {
+                            // this split's share of the row's outputs -> global; the last split to arrive for these 32
+                            // rows adds all shares in split order (timing does not change the result) and stores
+                            const int split = cta % p.ksplit;
+                            float* mine = p.partial + ((size_t)split * TCQ_TOKENS) * p.N + grow;
+                            if (row_ok) {
+#pragma unroll
+                                for (int tt = 0; tt < TOK; ++tt)
+                                    if (tt < p.M) mine[(size_t)tt * p.N] = acc[tt];
+                            }
+                            __threadfence();
+                            __syncwarp();
+                            unsigned int arrived = 0;
+                            if (lane == 0) arrived = atomicAdd(p.counters + (cta / p.ksplit) * 4 + quarter, 1u);
+                            arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                            if (arrived == (unsigned int)p.ksplit - 1u) {
+                                __threadfence();
+                                if (row_ok) {
+#pragma unroll
+                                    for (int tt = 0; tt < TOK; ++tt) {
+                                        if (tt < p.M) {
+                                            float v = 0.0f;
+                                            for (int sp = 0; sp < p.ksplit; ++sp)
+                                                v += __ldcg(p.partial + ((size_t)sp * TCQ_TOKENS + tt) * p.N + grow);
+                                            y[(size_t)tt * p.ldy] = from_float<dst_t>(v);
+                                        }
+                                    }
+                                }
+                            }
                         }
                     }
                     __syncwarp();
@@ -632,9 +693,13 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
-size_t gemv_tc_workspace_bytes(int type, int K) {
+// workspace: int8 activations [xrows][K] | float2 scales [K / 32][16] | K-split counters | K-split partial outputs
+static size_t tcq_quant_bytes(int type, int K) {
     const size_t xrows = type == TYPE_Q6_K ? 32 : 16;
     return xrows * (size_t)K + (size_t)(K / 32) * TCQ_TOKENS * sizeof(float2);
+}
+size_t gemv_tc_workspace_bytes(int type, int K) {
+    return ((tcq_quant_bytes(type, K) + 255) & ~(size_t)255) + TCQ_COUNTERS * sizeof(unsigned int) + TCQ_PARTIAL_BYTES;
 }
 
 template <int TYPE, typename T, int TOK>
@@ -673,13 +738,34 @@ static int launch_gemv_tc_i8(const void* w, const void* x, void* y, int M, int N
         p.trace = trace_buffer(&slots);
         p.trace_stages = slots / 8;
     }
-    int grid = runtime_info().sm_count;
-    if (grid > N) grid = N;
-    p.rows_per_cta = N / grid;
-    p.rows_extra = N % grid;
-    const int max_rows = p.rows_per_cta + (p.rows_extra ? 1 : 0);
-    const int tiles = (max_rows + TCQ_ROWS - 1) / TCQ_ROWS;
-    p.tile_rows = (((max_rows + tiles - 1) / tiles) + 7) & ~7;
+    uint8_t* after = static_cast<uint8_t*>(workspace) + ((tcq_quant_bytes(TYPE, K) + 255) & ~(size_t)255);
+    p.counters = reinterpret_cast<unsigned int*>(after);
+    p.partial = reinterpret_cast<float*>(after + TCQ_COUNTERS * sizeof(unsigned int));
+    const int sms = runtime_info().sm_count < TCQ_MAX_CTAS ? runtime_info().sm_count : TCQ_MAX_CTAS;
+    const int nkc = K / TCQ_KC;
+    const int row_tiles = (N + TCQ_ROWS - 1) / TCQ_ROWS;
+    int grid;
+    p.ksplit = 1;
+    if (2 * row_tiles <= sms && nkc >= 4 && runtime_info().tc_ksplit) {
+        // few rows: full-height tiles, K shared out so that most SMs get a unit of at least two stages
+        int ks = sms / row_tiles;
+        if (ks > nkc / 2) ks = nkc / 2;
+        p.ksplit = ks;
+    }
+    if (p.ksplit > 1) {
+        p.tile_rows = N < TCQ_ROWS ? ((N + 7) & ~7) : TCQ_ROWS;
+        p.rows_per_cta = p.tile_rows;
+        p.rows_extra = 0;
+        grid = row_tiles * p.ksplit;
+    } else {
+        grid = sms;
+        if (grid > N) grid = N;
+        p.rows_per_cta = N / grid;
+        p.rows_extra = N % grid;
+        const int max_rows = p.rows_per_cta + (p.rows_extra ? 1 : 0);
+        const int tiles = (max_rows + TCQ_ROWS - 1) / TCQ_ROWS;
+        p.tile_rows = (((max_rows + tiles - 1) / tiles) + 7) & ~7;
+    }
     // ring depths: prefer four A stages if at least three packed-row stages still fit, else three (two at worst)
     const int a_bytes = 2 * p.tile_rows * 128, raw_bytes = (p.tile_rows * TT::PITCH + 127) & ~127;
     const int room = TCQ_SMEM_LIMIT - L::FIXED;
@@ -713,7 +799,7 @@ static int launch_gemv_tc_i8(const void* w, const void* x, void* y, int M, int N
         if (r != CUDA_SUCCESS) return B200Q_ERR_INVALID;
     }
 
-    tcq_quantize_kernel<T, TYPE == TYPE_Q6_K><<<K / 32, dim3(32, TCQ_TOKENS), 0, s>>>(static_cast<const T*>(x), q, ds, K, M, ldx);
+    tcq_quantize_kernel<T, TYPE == TYPE_Q6_K><<<K / 32, dim3(32, TCQ_TOKENS), 0, s>>>(static_cast<const T*>(x), q, ds, K, M, ldx, p.counters);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
 

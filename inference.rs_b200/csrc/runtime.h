@@ -22,6 +22,7 @@ struct RuntimeInfo {
     int gemv_stage_target; // bytes per shared-memory stage the GEMV planner aims at
     int gemm_direct;       // 1: the GEMM reads packed weights straight from global memory (no shared-memory staging)
     int gemv_ctas_per_sm;  // CTAs of one GEMV grid per SM: 2, or 1 to leave the other slot to the next grid
+    int tc_ksplit;         // small-batch tensor-core kernel: split K over CTAs for matrices with few rows (1, testing: 0)
 };
 
 const RuntimeInfo& runtime_info();

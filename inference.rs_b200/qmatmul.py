@@ -16,12 +16,17 @@ from .dtypes import MATRIX_ROW_PADDING, GgmlDType, pad
 
 MMVQ_MAX_BATCH = 8  # rows the decode GEMV launchers take (fast_mmvq.rs:84)
 TENSOR_CORE_MAX_ROWS = 16  # rows the small-batch tensor-core kernel takes (fast_mmvq.rs:86)
-# 3..8 rows: the tier pays once a CTA's share of the weight rows fills enough of its 128-row MMAs; the row counts below
-# are the crossovers measured on B200 against the dp4a GEMV at the Llama-3-8B shapes (Q6_K's unpacking is the most
-# expensive, so it needs taller matrices). 9..16 rows: always (the alternative is the prefill GEMM).
-_TC_MIN_N_LIGHT = {3: 16384, 4: 16384, 5: 8192, 6: 8192, 7: 0, 8: 0}
-_TC_MIN_N_Q6K = {3: 65536, 4: 65536, 5: 16384, 6: 16384, 7: 16384, 8: 16384}
-TENSOR_CORE_MIN_WEIGHT_ROWS = {GgmlDType.Q4K: _TC_MIN_N_LIGHT, GgmlDType.Q8_0: _TC_MIN_N_LIGHT, GgmlDType.Q6K: _TC_MIN_N_Q6K}
+# 3..8 rows: the crossovers measured on B200 against the dp4a GEMV at the Llama-3-8B shapes. The tier's cost hardly
+# grows with the row count, the GEMV's grows linearly; Q6_K's unpacking is the most expensive, so it needs more rows
+# or a bigger matrix. 9..16 rows: always (the alternative is the prefill GEMM).
+
+
+def _tensor_core_pays(dtype: GgmlDType, rows: int, n: int, k: int) -> bool:
+    big = k >= 8192 or n >= 16384
+    if dtype == GgmlDType.Q6K:
+        return rows >= 7 or (rows >= 4 and big) or n >= 65536
+    return rows >= 5 or big
+
 
 _tc_workspaces: dict = {}
 
@@ -44,11 +49,10 @@ def tensor_core_rows_supported(dtype: GgmlDType, k: int) -> bool:
 
 def prefers_tensor_core_rows(dtype: GgmlDType, rows: int, n: int, k: int) -> bool:
     """The small-batch tensor-core tier (fast_mmvq.rs:118-134: 2..16 rows where a type has it). Here: 9..16 rows
-    always, 3..8 rows when the matrix has enough rows to fill the 128-row tiles of 148 CTAs; 1..2 rows stay on the
-    one-launch GEMV."""
+    always, 3..8 rows from the measured crossover with the dp4a GEMV on; 1..2 rows stay on the one-launch GEMV."""
     if rows > TENSOR_CORE_MAX_ROWS or rows < 3 or not tensor_core_rows_supported(dtype, k):
         return False
-    return rows > MMVQ_MAX_BATCH or n >= TENSOR_CORE_MIN_WEIGHT_ROWS[dtype][rows]
+    return rows > MMVQ_MAX_BATCH or _tensor_core_pays(dtype, rows, n, k)
 
 
 class QTensor:

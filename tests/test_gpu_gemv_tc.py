@@ -163,6 +163,27 @@ def test_results_do_not_depend_on_timing(m):
     assert_device_ok()
 
 
+@pytest.mark.parametrize("type_id", TYPES)
+@pytest.mark.parametrize("m,n,k", [(4, 4096, 4096), (16, 1024, 4096), (9, 6144, 2048), (3, 100, 4096)])
+def test_matrices_with_few_rows_are_split_along_k(type_id, m, n, k):
+    # few row tiles: the 256-k stages of a tile are shared out over several CTAs whose partial outputs are added in a
+    # fixed order; same gates, bit-reproducible, and close to the unsplit kernel (different f32 summation order only)
+    packed = random_packed(type_id, n, k, seed=n + k)
+    y = run_tc(type_id, m, n, k, packed=packed, seed=m)
+    w_dev = ops.upload_weights(packed, DT[type_id])
+    x = (seeded_acts(m, k, 6000 + m, torch.float32)).to(torch.bfloat16).cuda()
+    again = ops.gemv_tc(DT[type_id], w_dev, x, n)
+    assert torch.equal(again, y)
+    ops.set_option("tc_ksplit", 0)
+    try:
+        whole = ops.gemv_tc(DT[type_id], w_dev, x, n)
+    finally:
+        ops.set_option("tc_ksplit", 1)
+    torch.cuda.synchronize()
+    assert (whole.float() - y.float()).abs().max().item() <= 2.0 ** -7 * y.float().abs().max().item()
+    assert_device_ok()
+
+
 def test_unsupported_inputs_are_refused():
     w_dev = ops.upload_weights(random_packed(kq.Q4_K, 128, 256, 1), DT[kq.Q4_K])
     with pytest.raises(kl.KernelLibraryError, match="at most 16"):

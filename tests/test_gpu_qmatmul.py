@@ -45,14 +45,13 @@ def test_rows_3_to_16_take_the_tensor_core_tier_where_it_pays(type_id):
     from inference_rs_b200 import qmatmul as qm
     n, k = 9000, 2048
     dt = DT[type_id]
-    n = 20000 if type_id == kq.Q6_K else 9000
-    assert qm.prefers_tensor_core_rows(dt, 5, n, k) and qm.prefers_tensor_core_rows(dt, 12, n, k) and not qm.prefers_tensor_core_rows(dt, 3, 9000, k)
-    assert qm.prefers_tensor_core_rows(dt, 12, 64, k) and not qm.prefers_tensor_core_rows(dt, 5, 64, k)
+    assert qm.prefers_tensor_core_rows(dt, 7, n, k) and qm.prefers_tensor_core_rows(dt, 12, n, k) and not qm.prefers_tensor_core_rows(dt, 3, n, k)
+    assert qm.prefers_tensor_core_rows(dt, 12, 64, k) and qm.prefers_tensor_core_rows(dt, 4, 4096, 14336)
     assert not qm.prefers_tensor_core_rows(dt, 2, n, k) and not qm.prefers_tensor_core_rows(dt, 17, n, k)
     assert not qm.prefers_tensor_core_rows(pkg.GgmlDType.Q6K, 12, n, 512)  # 210-byte blocks: rows not a multiple of 16 bytes
     packed = kq.quantize(type_id, seeded_weights(n, k, 51))
     qmm = QMatMul.from_qtensor(QTensor.from_packed(packed, dt, (n, k)))
-    for rows in (5, 12):
+    for rows in (7, 12):
         for dtype in (torch.float32, torch.bfloat16):
             x = seeded_acts(rows, k, 70 + rows, dtype)
             y = qmm.forward(x.cuda())
