@@ -8,3 +8,4 @@ from . import kernel_library  # noqa: F401
 from .kernel_library import KernelLibraryError, library  # noqa: F401
 from .dtypes import GgmlDType  # noqa: F401
 from .qmatmul import GgufMatMul, QMatMul, QTensor  # noqa: F401
+from . import gguf_file  # noqa: F401

@@ -75,6 +75,34 @@ def test_rows_3_to_16_take_the_tensor_core_tier_where_it_pays(type_id):
     assert_device_ok()
 
 
+def test_weights_loaded_from_a_gguf_file_give_the_same_matmul_and_go_back_unchanged():
+    import io
+    from inference_rs_b200 import gguf_file as gf
+    n, k = 96, 512
+    files = {}
+    for type_id in TYPES:
+        files[type_id] = kq.quantize(type_id, seeded_weights(n, k, 80 + type_id))
+    buf = io.BytesIO()
+    gf.write(buf, [("general.architecture", gf.Value.string("llama"))],
+             [(f"w{t}", t, (n, k), files[t]) for t in TYPES] + [("norm", 0, (k,), np.ones(k, dtype=np.float32).view(np.uint8))])
+    c = gf.Content.read(buf)
+    x = seeded_acts(2, k, 81, torch.bfloat16).cuda()
+    loaded = []
+    for t in TYPES:
+        q = c.tensor(buf, f"w{t}")
+        assert isinstance(q, QTensor) and q.shape == (n, k) and int(q.dtype) == t
+        direct = QTensor.from_packed(files[t], DT[t], (n, k))
+        assert torch.equal(QMatMul.from_qtensor(q).forward(x), QMatMul.from_qtensor(direct).forward(x))
+        loaded.append((f"w{t}", q))
+    assert c.tensor(buf, "norm").dtype == torch.float32 and float(c.tensor(buf, "norm").sum()) == k
+    out = io.BytesIO()
+    gf.write_qtensors(out, [], loaded)
+    c2 = gf.Content.read(out)
+    for t in TYPES:
+        assert c2.tensor_bytes(out, f"w{t}")[1].tobytes() == files[t].tobytes()
+    assert_device_ok()
+
+
 def test_qmatmul_errors_mirror_the_reference():
     q = QTensor.from_packed(kq.quantize(kq.Q4_K, seeded_weights(8, 256, 1)), DT[kq.Q4_K], (8, 256))
     qmm = QMatMul.from_qtensor(q)
