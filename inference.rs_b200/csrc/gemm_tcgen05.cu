@@ -378,7 +378,7 @@ struct Gemm2Barriers {
     uint64_t empty[GEMM2_STAGES];
     uint64_t raw_full[GEMM2_RAW_STAGES];
     uint64_t raw_empty[GEMM2_RAW_STAGES];
-    uint64_t tmem_full;
+    uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
 };
 
@@ -480,8 +480,16 @@ template <> struct RawDequant<TYPE_Q6_K> {
     }
 };
 
+// Persistent: a CTA walks the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (tile index = weight tile fastest, so the
+// CTAs running at one time share activation tiles through L2). The accumulators are double-buffered in TMEM and drained by
+// warps of their own, so the epilogue of a tile and the pipeline fill of the next overlap the MMAs.
+//   warp 0  TMA producer of the activations       warps 4-11           dequantization
+//   warp 1  tcgen05.mma issuer                    warps 12-(11 + 4 MT) epilogue
+//   warp 2  TMEM allocation                       warp 3               packed-row copies
+template <int MT> constexpr int gemm2_threads() { return 32 * (4 + GEMM_DEQ_WARPS + 4 * MT); }
+
 template <int TYPE, typename T, int MT>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_staged_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+__global__ void __launch_bounds__(gemm2_threads<MT>(), 1) gemm_tcgen05_staged_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     using RC = RawChunk<TYPE>;
     constexpr int RAW_BYTES = GEMM_BN * RC::PITCH + 64;  // + slack: reads may run a few bytes past the last row's slot
     extern __shared__ uint8_t gemm_smem_raw[];
@@ -493,12 +501,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_staged_kernel(co
     Gemm2Barriers* bars = reinterpret_cast<Gemm2Barriers*>(raw_stages + GEMM2_RAW_STAGES * RAW_STRIDE);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * GEMM_BN;
-    const int m0 = blockIdx.y * (MT * GEMM_BM);
     const int nkb = p.K / GEMM_BK;
     const int nkc = p.K / 256;
-    constexpr uint32_t TMEM_COLS = MT * GEMM_BN;
-    const int rows_valid = min(GEMM_BN, p.N - n0);
+    const int nx = (p.N + GEMM_BN - 1) / GEMM_BN;
+    const int ntiles = nx * ((p.M + MT * GEMM_BM - 1) / (MT * GEMM_BM));
+    constexpr uint32_t BUF_COLS = MT * GEMM_BN;
+    constexpr uint32_t TMEM_COLS = 2 * BUF_COLS;
 
     if (tid == 0) {
         for (int s = 0; s < GEMM2_STAGES; ++s) {
@@ -510,7 +518,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_staged_kernel(co
             mbar_init(&bars->raw_full[s], 32);  // one arrival per lane of the packed-row producer warp
             mbar_init(&bars->raw_empty[s], GEMM_DEQ_WARPS);
         }
-        mbar_init(&bars->tmem_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&bars->tmem_full[s], 1);
+            mbar_init(&bars->tmem_empty[s], 4 * MT);
+        }
         mbar_init_fence();
     }
     if (warp == 2) tmem_alloc(&bars->tmem_base, TMEM_COLS);
@@ -522,25 +533,27 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_staged_kernel(co
     if (warp == 0) {
         // ---------------- TMA producer of the activations ----------------
         if (lane == 0) {
-            int issued = 0;
+            int kbg = 0;  // k-blocks issued so far, over all tiles
             bool ok = true;
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % GEMM2_STAGES;
-                if (!mbar_wait_bounded(&bars->empty[s], ((kb / GEMM2_STAGES) & 1) ^ 1)) {
-                    record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, kb);
-                    ok = false;
-                    break;
-                }
-                mbar_arrive_expect_tx(&bars->full_a[s], MT * GEMM_A_BYTES);
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / nx) * (MT * GEMM_BM);
+                for (int kb = 0; kb < nkb; ++kb, ++kbg) {
+                    const int s = kbg % GEMM2_STAGES;
+                    if (!mbar_wait_bounded(&bars->empty[s], ((kbg / GEMM2_STAGES) & 1) ^ 1)) {
+                        record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, kbg);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&bars->full_a[s], MT * GEMM_A_BYTES);
 #pragma unroll
-                for (int t = 0; t < MT; ++t)
-                    tma_load_2d(a_stages + (size_t)(s * MT + t) * GEMM_A_BYTES, &tmap_x, kb * GEMM_BK, m0 + t * GEMM_BM, &bars->full_a[s]);
-                issued = kb + 1;
+                    for (int t = 0; t < MT; ++t)
+                        tma_load_2d(a_stages + (size_t)(s * MT + t) * GEMM_A_BYTES, &tmap_x, kb * GEMM_BK, m0 + t * GEMM_BM, &bars->full_a[s]);
+                }
             }
-            if (!ok) {
-                for (int kb = max(0, issued - GEMM2_STAGES); kb < issued; ++kb)
-                    if (!mbar_wait_bounded(&bars->full_a[kb % GEMM2_STAGES], (kb / GEMM2_STAGES) & 1)) {
-                        record_failure(p.status, STATUS_WAIT_DRAIN_TIMEOUT, kb);
+            if (!ok) {  // let every copy already issued land before the CTA may exit
+                for (int q = max(0, kbg - GEMM2_STAGES); q < kbg; ++q)
+                    if (!mbar_wait_bounded(&bars->full_a[q % GEMM2_STAGES], (q / GEMM2_STAGES) & 1)) {
+                        record_failure(p.status, STATUS_WAIT_DRAIN_TIMEOUT, q);
                         break;
                     }
             }
@@ -555,151 +568,179 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_staged_kernel(co
             int s = 0;
             uint32_t ph = 0;
             bool ready = false;  // the polls made while the previous block's MMAs were issued found this block complete
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                // both barriers polled together: a poll's round trip through the busy shared-memory pipe costs hundreds
-                // of cycles, more than the tensor core needs for a block, so they must not add up
-                if (!ready && !mbar_wait2_bounded(&bars->full_a[s], ph, &bars->full_b[s], ph)) {
-                    record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, kb);
+            int ti = 0;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++ti) {
+                const int buf = ti & 1;
+                if (!mbar_wait_bounded(&bars->tmem_empty[buf], ((ti >> 1) & 1) ^ 1)) {  // the epilogue has drained this buffer
+                    record_failure(p.status, STATUS_WAIT_MMA_TIMEOUT, 2000 + ti);
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint64_t db = db0 + (uint64_t)(s * (GEMM_B_BYTES >> 4));
-                const uint64_t da = da0 + (uint64_t)(s * MT * (GEMM_A_BYTES >> 4));
-                const int cur = s;
-                if (++s == GEMM2_STAGES) {
-                    s = 0;
-                    ph ^= 1u;
-                }
-                bool n0 = false, n1 = false;
-                if (kb + 1 < nkb) {
-                    n0 = mbar_try_wait(&bars->full_a[s], ph);
-                    n1 = mbar_try_wait(&bars->full_b[s], ph);
-                }
+                const uint32_t d0 = tmem_base + buf * BUF_COLS;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    // both barriers polled together: a poll's round trip through the busy shared-memory pipe costs
+                    // hundreds of cycles, more than the tensor core needs for a block, so they must not add up
+                    if (!ready && !mbar_wait2_bounded(&bars->full_a[s], ph, &bars->full_b[s], ph)) {
+                        record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, kb);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t db = db0 + (uint64_t)(s * (GEMM_B_BYTES >> 4));
+                    const uint64_t da = da0 + (uint64_t)(s * MT * (GEMM_A_BYTES >> 4));
+                    const int cur = s;
+                    if (++s == GEMM2_STAGES) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                    // the next block's barriers (of this tile or the next): their answers come back during the issue
+                    bool n0 = false, n1 = false;
+                    if (kb + 1 < nkb || tile + (int)gridDim.x < ntiles) {  // not after the very last block: nothing would ever arrive
+                        n0 = mbar_try_wait(&bars->full_a[s], ph);
+                        n1 = mbar_try_wait(&bars->full_b[s], ph);
+                    }
 #pragma unroll
-                for (int t = 0; t < MT; ++t) {
+                    for (int t = 0; t < MT; ++t) {
 #pragma unroll
-                    for (int k = 0; k < GEMM_BK / 16; ++k)
-                        tc_mma_f16(tmem_base + t * GEMM_BN, da + (uint64_t)(t * (GEMM_A_BYTES >> 4) + 2 * k), db + 2 * k, idesc,
-                                   (kb > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < GEMM_BK / 16; ++k)
+                            tc_mma_f16(d0 + t * GEMM_BN, da + (uint64_t)(t * (GEMM_A_BYTES >> 4) + 2 * k), db + 2 * k, idesc,
+                                       (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&bars->empty[cur]);
+                    ready = n0 && n1;
                 }
-                tc_commit(&bars->empty[cur]);
-                ready = n0 && n1;
+                if (ok) tc_commit(&bars->tmem_full[buf]);
             }
-            if (ok) tc_commit(&bars->tmem_full);
         }
     } else if (warp == 3) {
-        // ---------------- packed-row producer: 4 rows per lane and 256-k chunk ----------------
+        // ---------------- packed-row producer: 256 k of every row of the tile per chunk ----------------
         bool ok = true;
-        int issued = 0;
-        for (int kc = 0; kc < nkc && ok; ++kc) {
-            const int rs = kc % GEMM2_RAW_STAGES;
-            if (!mbar_wait_bounded(&bars->raw_empty[rs], ((kc / GEMM2_RAW_STAGES) & 1) ^ 1)) {
-                if (lane == 0) record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, 1000 + kc);
-                ok = false;
+        int kcg = 0;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            const int n0 = (tile % nx) * GEMM_BN;
+            const int rows_valid = min(GEMM_BN, p.N - n0);
+            for (int kc = 0; kc < nkc; ++kc, ++kcg) {
+                const int rs = kcg % GEMM2_RAW_STAGES;
+                if (!mbar_wait_bounded(&bars->raw_empty[rs], ((kcg / GEMM2_RAW_STAGES) & 1) ^ 1)) {
+                    if (lane == 0) record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, 1000 + kcg);
+                    ok = false;
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                // 16-byte asynchronous copies, consecutive lanes on consecutive pieces of a row (a bulk copy per row would
+                // cost the TMA unit more per copy than these small rows are worth); each lane's copies signal the barrier
+                uint8_t* stage = raw_stages + (size_t)rs * RAW_STRIDE;
+                constexpr int PIECES = RC::COPY / 16;
+                const int total = rows_valid * PIECES;
+                for (int idx = lane; idx < total; idx += 32) {
+                    const int r = idx / PIECES, piece = idx - r * PIECES;
+                    const uint8_t* src = p.w + (size_t)(n0 + r) * p.row_bytes + (size_t)kc * RC::BYTES;
+                    src = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)15) + 16 * piece;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(stage + (size_t)r * RC::PITCH + 16 * piece)), "l"(src) : "memory");
+                }
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars->raw_full[rs])) : "memory");
             }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            // 16-byte asynchronous copies, consecutive lanes on consecutive pieces of a row (a bulk copy per row would
-            // cost the TMA unit more per copy than these small rows are worth); each lane's copies signal the barrier
-            uint8_t* stage = raw_stages + (size_t)rs * RAW_STRIDE;
-            constexpr int PIECES = RC::COPY / 16;
-            const int total = rows_valid * PIECES;
-            for (int idx = lane; idx < total; idx += 32) {
-                const int r = idx / PIECES, piece = idx - r * PIECES;
-                const uint8_t* src = p.w + (size_t)(n0 + r) * p.row_bytes + (size_t)kc * RC::BYTES;
-                src = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)15) + 16 * piece;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(stage + (size_t)r * RC::PITCH + 16 * piece)), "l"(src) : "memory");
-            }
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars->raw_full[rs])) : "memory");
-            issued = kc + 1;
         }
-        (void)issued;
         asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this warp may still be writing when the CTA exits
-    } else if (warp >= 4) {
+    } else if (warp >= 4 && warp < 4 + GEMM_DEQ_WARPS) {
         // ---------------- dequantization from the staged packed rows ----------------
         const int dt = tid - 128;
         const int r = dt & (GEMM_BN - 1);
         const int h = dt >> 7;
-        const bool row_ok = r < rows_valid;
         bool ok = true;
-        for (int kc = 0; kc < nkc; ++kc) {
-            const int rs = kc % GEMM2_RAW_STAGES;
-            if (ok && !mbar_wait_bounded(&bars->raw_full[rs], (kc / GEMM2_RAW_STAGES) & 1)) {
-                record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, 1000 + kc);
-                ok = false;
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            const uint32_t rb = smem_u32(raw_stages + (size_t)rs * RAW_STRIDE) + (uint32_t)r * RC::PITCH;
-#pragma unroll
-            for (int J = 0; J < 4; ++J) {
-                const int kb = 4 * kc + J;
-                const int s = kb % GEMM2_STAGES;
-                float v[32];
-                // polled before the arithmetic so that the poll's round trip overlaps it
-                const bool free_now = mbar_try_wait(&bars->empty[s], ((kb / GEMM2_STAGES) & 1) ^ 1);
-                if (ok && row_ok) {
-                    if (J == 0) RawDequant<TYPE>::template values<0>(rb, kc, h, v);
-                    else if (J == 1) RawDequant<TYPE>::template values<1>(rb, kc, h, v);
-                    else if (J == 2) RawDequant<TYPE>::template values<2>(rb, kc, h, v);
-                    else RawDequant<TYPE>::template values<3>(rb, kc, h, v);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-                }
-                if (ok && !free_now && !mbar_wait_bounded(&bars->empty[s], ((kb / GEMM2_STAGES) & 1) ^ 1)) {
-                    record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, kb);
+        int kcg = 0;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            const int n0 = (tile % nx) * GEMM_BN;
+            const bool row_ok = r < min(GEMM_BN, p.N - n0);
+            for (int kc = 0; kc < nkc; ++kc, ++kcg) {
+                const int rs = kcg % GEMM2_RAW_STAGES;
+                if (ok && !mbar_wait_bounded(&bars->raw_full[rs], (kcg / GEMM2_RAW_STAGES) & 1)) {
+                    record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, 1000 + kcg);
                     ok = false;
                 }
                 ok = __all_sync(0xffffffffu, ok);
-                if (ok) {
+                if (!ok) break;
+                const uint32_t rb = smem_u32(raw_stages + (size_t)rs * RAW_STRIDE) + (uint32_t)r * RC::PITCH;
+#pragma unroll
+                for (int J = 0; J < 4; ++J) {
+                    const int kbg = 4 * kcg + J;  // every tile has 4 nkc k-blocks, so this also counts over tiles
+                    const int s = kbg % GEMM2_STAGES;
+                    float v[32];
+                    // polled before the arithmetic so that the poll's round trip overlaps it
+                    const bool free_now = mbar_try_wait(&bars->empty[s], ((kbg / GEMM2_STAGES) & 1) ^ 1);
+                    if (row_ok) {
+                        if (J == 0) RawDequant<TYPE>::template values<0>(rb, kc, h, v);
+                        else if (J == 1) RawDequant<TYPE>::template values<1>(rb, kc, h, v);
+                        else if (J == 2) RawDequant<TYPE>::template values<2>(rb, kc, h, v);
+                        else RawDequant<TYPE>::template values<3>(rb, kc, h, v);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                    }
+                    if (!free_now && !mbar_wait_bounded(&bars->empty[s], ((kbg / GEMM2_STAGES) & 1) ^ 1)) {
+                        record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, kbg);
+                        ok = false;
+                    }
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
                     store_unit<T>(smem_u32(b_stages + (size_t)s * GEMM_B_BYTES), r, h, v);
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->full_b[s]);
                 }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->raw_empty[rs]);  // this warp has read the chunk
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->raw_empty[rs]);  // this warp has read the chunk
         }
-        // ---------------- epilogue ----------------
-        const int t = (warp - 4) >> 2;
-        const int quarter = warp & 3;
-        if (t < MT) {
-            if (ok && !mbar_wait_bounded(&bars->tmem_full, 0)) {
-                record_failure(p.status, STATUS_WAIT_MMA_TIMEOUT, 0);
+    } else if (warp >= 4 + GEMM_DEQ_WARPS) {
+        // ---------------- epilogue: one warp per 32 token rows of a sub-tile ----------------
+        const int e = warp - (4 + GEMM_DEQ_WARPS);
+        const int t = e >> 2;
+        const int quarter = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4)
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && ((size_t)p.ldy * sizeof(T) % 16 == 0);
+        bool ok = true;
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++ti) {
+            const int buf = ti & 1;
+            const int n0 = (tile % nx) * GEMM_BN;
+            const int m0 = (tile / nx) * (MT * GEMM_BM);
+            if (!mbar_wait_bounded(&bars->tmem_full[buf], (ti >> 1) & 1)) {
+                record_failure(p.status, STATUS_WAIT_MMA_TIMEOUT, ti);
                 ok = false;
             }
             ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             tc_fence_after();
             const int row = m0 + t * GEMM_BM + quarter * 32 + lane;
             T* yrow = reinterpret_cast<T*>(p.y) + (size_t)row * p.ldy;
-            const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && ((size_t)p.ldy * sizeof(T) % 16 == 0);
-            if (ok) {
 #pragma unroll 1
-                for (int c = 0; c < GEMM_BN / 32; ++c) {
-                    uint32_t acc[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + t * GEMM_BN + c * 32, acc);
-                    const int col0 = n0 + c * 32;
-                    if (row < p.M) {
-                        if (vec_ok && col0 + 32 <= p.N) {
+            for (int c = 0; c < GEMM_BN / 32; ++c) {
+                uint32_t acc[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BUF_COLS + t * GEMM_BN + c * 32, acc);
+                const int col0 = n0 + c * 32;
+                if (row < p.M) {
+                    if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                uint4 o;
-                                o.x = pack2<T>(__uint_as_float(acc[8 * q]), __uint_as_float(acc[8 * q + 1]));
-                                o.y = pack2<T>(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3]));
-                                o.z = pack2<T>(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5]));
-                                o.w = pack2<T>(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7]));
-                                *reinterpret_cast<uint4*>(yrow + col0 + 8 * q) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N) yrow[col0 + j] = from_float<T>(__uint_as_float(acc[j]));
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 o;
+                            o.x = pack2<T>(__uint_as_float(acc[8 * q]), __uint_as_float(acc[8 * q + 1]));
+                            o.y = pack2<T>(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3]));
+                            o.z = pack2<T>(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5]));
+                            o.w = pack2<T>(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7]));
+                            *reinterpret_cast<uint4*>(yrow + col0 + 8 * q) = o;
                         }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.N) yrow[col0 + j] = from_float<T>(__uint_as_float(acc[j]));
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->tmem_empty[buf]);  // the accumulators are in registers or stored: reuse the buffer
         }
     }
     tc_fence_before();
@@ -722,8 +763,9 @@ static int launch_gemm_staged_mt(const CUtensorMap& map, const GemmParams& p, cu
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((unsigned)((p.N + GEMM_BN - 1) / GEMM_BN), (unsigned)((p.M + MT * GEMM_BM - 1) / (MT * GEMM_BM)), 1);
-    kernel<<<grid, GEMM_THREADS, smem, s>>>(map, p);
+    const int ntiles = ((p.N + GEMM_BN - 1) / GEMM_BN) * ((p.M + MT * GEMM_BM - 1) / (MT * GEMM_BM));
+    const int sms = runtime_info().sm_count;
+    kernel<<<ntiles < sms ? ntiles : sms, gemm2_threads<MT>(), smem, s>>>(map, p);
     return (int)cudaGetLastError();
 }
 
