@@ -240,10 +240,11 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
     const int lane = tid & 31;
     constexpr bool PER_256 = (MODE == ACT_RAW_CPU) && (TYPE != TYPE_Q8_0);
     const unsigned gmask = PER_256 ? 0xffffffffu : (0xFu << (lane & 28));
-    for (int i = tid; i < B * chunks; i += nthreads) {
-        const int b = i / chunks, c = i - b * chunks;
+    int u = 0;  // which of this thread's chunks
+    for (int i = tid; i < B * chunks; i += nthreads, ++u) {
+        // integer divisions are dozens of dependent instructions on a path every launch runs exactly once
+        const int b = B == 1 ? 0 : i / chunks, c = B == 1 ? i : i - b * chunks;
         float v[8];
-        const int u = (i - tid) / nthreads;
         if (u == 0) pre.get(0, v);
         else if (u == 1) pre.get(1, v);
         else if (u == 2) pre.get(2, v);
