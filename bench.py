@@ -329,6 +329,7 @@ def main():
     ap.add_argument("--no-group", action="store_true", help="one launch per projection instead of grouped q/k/v and gate/up")
     ap.add_argument("--sweep", action="store_true", help="also time every shape of the decode sweep")
     ap.add_argument("--single", nargs=4, metavar=("TYPE", "K", "N", "B"), help="time one GEMV shape only (q4_k|q6_k|q8_0)")
+    ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: NCCL all-reduce instead of the peer-memory kernel")
     ap.add_argument("--group2", action="store_true", help="with --single: two matrices of the shape in one grouped launch (B = 1)")
     ap.add_argument("--tc", action="store_true", help="with --single: the small-batch tensor-core kernel (B up to 16)")
     ap.add_argument("--gemm", nargs=4, metavar=("TYPE", "K", "N", "M"), help="time one prefill GEMM shape only")
@@ -408,6 +409,11 @@ def main():
     grouped = {i for g in groups for i in g}
     launches_per_step = model.layers * (len(projs) - len(grouped) + len(groups)) + 1
 
+    peer_ar = None
+    if tp and not args.nccl_allreduce:
+        from inference_rs_b200.tensor_parallel import PeerSumAllReduce
+        peer_ar = PeerSumAllReduce(capacity=1 << 16)
+
     def step():
         for li in range(model.layers):
             for g in groups:
@@ -418,7 +424,10 @@ def main():
                     continue
                 ops.gemv(p.dtype, w, x_dev[p.k], p.n, out=o)
                 if tp and p.split == "row":
-                    dist.all_reduce(o)
+                    if peer_ar is not None:
+                        peer_ar.sum_all_reduce_(o)
+                    else:
+                        dist.all_reduce(o)
         ops.gemv(head.dtype, head_w, x_dev[head.k], head.n, out=logits)
         if tp:
             dist.all_gather_into_tensor(logits_all, logits)
@@ -599,7 +608,8 @@ def main():
         "config": {"workload": (f"{model.name} Q4_K_M decode matmul chain, batch 1 ({model.layers * len(projs) + 1} GEMVs in {launches_per_step} launches, "
                                 f"{bytes_per_step / 1e9:.2f} GB of weights per token and GPU)"),
                    "l2": "inputs larger than L2: every step streams its GBs of distinct weights",
-                   "parallelism": f"tp{world}: column / row split, {allreduces_per_step} NCCL all-reduces per token" if tp else "1 gpu",
+                   "parallelism": (f"tp{world}: column / row split, {allreduces_per_step} "
+                                   f"{'peer-memory (b200q_peer_allreduce)' if peer_ar is not None else 'NCCL'} all-reduces per token") if tp else "1 gpu",
                    "cuda_graph": graph is not None, "pdl": ops.get_option("pdl"),
                    "grouped_launches": not args.no_group},
         "weights_GBps_per_gpu": bytes_per_step * tok_s / 1e9,

@@ -170,6 +170,20 @@ long long b200q_gemv_tc_workspace_bytes(int type, int K);
 int b200q_gemv_tc(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace,
                   long long workspace_bytes, void* stream);
 
+/* One-shot sum all-reduce of a small vector over NVLink peer memory, for the partial outputs of row-parallel matmuls
+ * at decode (the exchange the reference does with an NCCL all-reduce in SumAllReduce,
+ * crates/inference-quant/src/distributed/mod.rs:516-670; distributed/layers.rs:814-1190). Every rank calls it with the
+ * same n and elem; out = sum over ranks of in, added in rank order in f32, so all ranks hold identical bits; in == out
+ * is allowed. `bufs` is a host array of `world` device pointers: every rank's exchange buffer as mapped in THIS
+ * process (bufs[rank] is the local one), each b200q_peer_allreduce_buffer_bytes(capacity) bytes, zeroed once before
+ * the first call and otherwise touched only by this function; capacity (bytes, multiple of 16) bounds n * sizeof(elem).
+ * Needs 16-byte aligned in / out and n * sizeof(elem) a multiple of 16; world <= 8. Device-side sequence numbers only:
+ * captured calls can be replayed. A rank that never arrives makes the others give up after about a second, set the
+ * device status word (b200q_device_status) and leave `out` unwritten. */
+long long b200q_peer_allreduce_buffer_bytes(long long capacity);
+int b200q_peer_allreduce(const void* const* bufs, int rank, int world, long long capacity, int elem, const void* in, void* out,
+                         long long n, void* stream);
+
 /* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,
  *        item slots per lane, register-resident slots} */
 int b200q_gemv_plan(int type, int K, int N, int b_size, int out[10]);

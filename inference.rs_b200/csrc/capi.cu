@@ -16,6 +16,9 @@ int gemv_group(int elem, int nmat, const int* types, const void* const* ws, void
 int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s);
 int gemv_tc_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace, cudaStream_t s);
 size_t gemv_tc_workspace_bytes(int type, int K);
+long long peer_allreduce_buffer_bytes(long long capacity);
+int peer_allreduce(const void* const* bufs, int rank, int world, long long capacity, int elem, const void* in, void* out, long long n,
+                   cudaStream_t s);
 
 static thread_local char t_error[320] = "";
 int set_error(int code, const char* msg) {
@@ -160,6 +163,24 @@ int b200q_gemv_tc(int type, int elem, const void* w, const void* x, void* y, int
         return set_error(rc, "b200q_gemv_tc needs 16-byte aligned weights whose rows are a multiple of 16 bytes (Q6_K: K a multiple of 2048)");
     if (rc == B200Q_ERR_INVALID) return set_error(rc, "workspace must be 128-byte aligned");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemv_tc failed");
+    return B200Q_OK;
+}
+
+// One-shot sum all-reduce over peer-mapped buffers (tensor-parallel decode): see peer_allreduce.cu.
+long long b200q_peer_allreduce_buffer_bytes(long long capacity) {
+    if (capacity <= 0 || capacity % 16 != 0) return 0;
+    return peer_allreduce_buffer_bytes(capacity);
+}
+
+int b200q_peer_allreduce(const void* const* bufs, int rank, int world, long long capacity, int elem, const void* in, void* out,
+                         long long n, void* stream) {
+    if (!bufs || !in || !out) return set_error(B200Q_ERR_INVALID, "null pointer");
+    if (elem != ELEM_BF16 && elem != ELEM_F16 && elem != ELEM_F32) return set_error(B200Q_ERR_INVALID, "unknown element type");
+    const int rc = peer_allreduce(bufs, rank, world, capacity, elem, in, out, n, (cudaStream_t)stream);
+    if (rc == B200Q_ERR_INVALID) return set_error(rc, "b200q_peer_allreduce: 1..8 ranks, 16-byte aligned buffers, capacity a multiple of 16");
+    if (rc == B200Q_ERR_TOO_LARGE) return set_error(rc, "b200q_peer_allreduce: the vector is larger than the staging capacity");
+    if (rc == B200Q_ERR_UNSUPPORTED) return set_error(rc, "b200q_peer_allreduce needs 16-byte aligned in / out and a size that is a multiple of 16 bytes");
+    if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "peer all-reduce failed");
     return B200Q_OK;
 }
 

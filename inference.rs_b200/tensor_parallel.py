@@ -122,6 +122,62 @@ class SumAllReduce:
         return out
 
 
+class PeerSumAllReduce(SumAllReduce):
+    """`SumAllReduce` through `b200q_peer_allreduce`: one small kernel per call over NVLink peer memory instead of an
+    NCCL collective, for the latency-bound `[rows, hidden]` sums of decode. The exchange buffers come from torch's
+    symmetric memory (one allocation per rank, mapped into every rank of the group); vectors larger than `capacity`
+    bytes fall through to NCCL. All ranks must make the same calls in the same order."""
+
+    def __init__(self, group=None, capacity: int = 1 << 20, device=None):
+        super().__init__(group)
+        import ctypes
+        import os
+
+        # plain peer mappings are all this needs; no NVLink multicast object is bound to the buffer
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import kernel_library as kl
+        self._kl = kl
+        self.capacity = (capacity + 15) & ~15
+        pg = group if group is not None else dist.group.WORLD
+        nbytes = int(kl.library().b200q_peer_allreduce_buffer_bytes(self.capacity))
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, pg)
+        self.buffer.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=pg)  # nobody signals before everybody's flags are zero
+        self.rank, self.world = int(self.handle.rank), int(self.handle.world_size)
+        if self.world > 8:
+            raise ValueError("b200q_peer_allreduce takes at most 8 ranks")
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
+
+    def sum_all_reduce(self, xs: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return xs
+        if not xs.is_contiguous():
+            raise ValueError("sum_all_reduce expects a contiguous tensor")
+        nbytes = xs.numel() * xs.element_size()
+        if nbytes > self.capacity or nbytes % 16 or xs.data_ptr() % 16 or xs.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            return super().sum_all_reduce(xs)
+        from .ops import _stream, elem_of
+        out = torch.empty_like(xs)
+        self._kl.check(self._kl.library().b200q_peer_allreduce(self._ptrs, self.rank, self.world, self.capacity, elem_of(xs.dtype),
+                                                               xs.data_ptr(), out.data_ptr(), xs.numel(), _stream()),
+                       "b200q_peer_allreduce")
+        return out
+
+    def sum_all_reduce_(self, xs: torch.Tensor) -> torch.Tensor:
+        """In place (no allocation: for captured decode steps)."""
+        from .ops import _stream, elem_of
+        self._kl.check(self._kl.library().b200q_peer_allreduce(self._ptrs, self.rank, self.world, self.capacity, elem_of(xs.dtype),
+                                                               xs.data_ptr(), xs.data_ptr(), xs.numel(), _stream()),
+                       "b200q_peer_allreduce")
+        return xs
+
+
 class ColumnParallelLayer:
     """Output rows `[rank * n / w, (rank + 1) * n / w)` of the weight; the bias is sharded with them (layers.rs:1193-1700)."""
 
@@ -148,11 +204,12 @@ class RowParallelLayer:
     all-reduce, then the bias once (layers.rs:814-1190, forward_raw :1036-1046)."""
 
     def __init__(self, packed: np.ndarray, dtype: GgmlDType, shape: tuple[int, int], rank: int, world_size: int,
-                 bias: torch.Tensor | None = None, device="cuda", group=None):
+                 bias: torch.Tensor | None = None, device="cuda", group=None, all_reduce: SumAllReduce | None = None):
         q = load_linear_shard(packed, dtype, shape, Shard.simple(1, rank, world_size), device)
         self.weight = GgufMatMul.from_qtensor(q, None)  # a row shard never carries the bias (layers.rs:869-878)
         self.bias = None if bias is None else bias.to(device)
-        self.all_reduce = SumAllReduce(group)
+        # layers of one model share one exchange object (pass a PeerSumAllReduce for the peer-memory kernel)
+        self.all_reduce = all_reduce if all_reduce is not None else SumAllReduce(group)
         self.rank, self.world_size = rank, world_size
 
     def is_distributed(self) -> bool:

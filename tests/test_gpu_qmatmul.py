@@ -173,6 +173,67 @@ def _tp_rank(rank, world, port, ret):
         dist.destroy_process_group()
 
 
+def _peer_rank(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from inference_rs_b200.tensor_parallel import PeerSumAllReduce
+        ar = PeerSumAllReduce(capacity=1 << 16)
+        worst = 0.0
+        same = True
+        for i, (shape, dtype) in enumerate([((1, 8192), torch.bfloat16), ((2, 4096), torch.bfloat16), ((1, 8), torch.bfloat16),
+                                            ((3, 1000), torch.float32), ((16, 2048), torch.float16), ((1, 8192), torch.bfloat16)] * 3):
+            g = torch.Generator().manual_seed(1000 * i + rank)
+            x = torch.randn(*shape, generator=g).to(dtype).cuda(rank)
+            got = ar.sum_all_reduce(x)
+            ref = x.float().clone()
+            dist.all_reduce(ref)  # f32 sum of the same inputs
+            tol = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -22}[dtype]
+            worst = max(worst, float(((got.float() - ref).abs() / (ref.abs() + 1e-3)).max()) / tol)
+            gathered = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(gathered, got)
+            same = same and all(torch.equal(gathered[0], t) for t in gathered)  # identical bits on every rank
+        # a vector beyond the capacity goes through NCCL
+        big = torch.ones(1, 1 << 16, dtype=torch.bfloat16, device=f"cuda:{rank}")
+        assert float(ar.sum_all_reduce(big)[0, 0]) == world
+        # captured and replayed: device-side sequence numbers only
+        x = torch.full((1, 8192), float(rank + 1), dtype=torch.bfloat16, device=f"cuda:{rank}")
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            ar.sum_all_reduce_(x.clone())
+            stream.synchronize()
+            y = x.clone()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                ar.sum_all_reduce_(y)  # y <- sum over ranks, in place: each replay multiplies the common part
+            for _ in range(3):
+                y.copy_(x)
+                graph.replay()
+            stream.synchronize()
+        replay_ok = float(y[0, 0]) == world * (world + 1) / 2
+        torch.cuda.synchronize()
+        import inference_rs_b200 as pkg_
+        ret[rank] = (worst, same, replay_ok, list(pkg_.kernel_library.device_status()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_memory_all_reduce_matches_nccl_and_is_identical_on_all_ranks():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_peer_rank, args=(world, port, ret), nprocs=world, join=True)
+        for r in range(world):
+            worst, same, replay_ok, status = ret[r]
+            assert worst <= 1.01 and same and replay_ok and status[0] == 0, dict(ret)
+
+
 def test_column_then_row_parallel_over_nccl():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
