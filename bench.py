@@ -329,6 +329,8 @@ def main():
     ap.add_argument("--no-group", action="store_true", help="one launch per projection instead of grouped q/k/v and gate/up")
     ap.add_argument("--sweep", action="store_true", help="also time every shape of the decode sweep")
     ap.add_argument("--single", nargs=4, metavar=("TYPE", "K", "N", "B"), help="time one GEMV shape only (q4_k|q6_k|q8_0)")
+    ap.add_argument("--unfused-allreduce", action="store_true", help="N > 1: the peer-memory all-reduce as a launch of its own")
+    ap.add_argument("--shard-of", type=int, default=0, help="N = 1 only: run one rank's share of the N-way 70B chain, no exchanges")
     ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: NCCL all-reduce instead of the peer-memory kernel")
     ap.add_argument("--group2", action="store_true", help="with --single: two matrices of the shape in one grouped launch (B = 1)")
     ap.add_argument("--tc", action="store_true", help="with --single: the small-batch tensor-core kernel (B up to 16)")
@@ -381,11 +383,14 @@ def main():
     # splits it (q/k/v, gate/up and the head by output rows; attn_output and ffn_down by input columns in whole
     # superblocks, each followed by a sum all-reduce of the [1, hidden] partial output over NCCL)
     tp = world > 1
-    model = workloads.LLAMA3_70B if tp else workloads.LLAMA3_8B
+    # --shard-of N on one GPU: one rank's share of the N-way tensor-parallel 70B chain without the exchanges (what the
+    # compute alone costs at those shard shapes)
+    shards = args.shard_of if (args.shard_of and not tp) else world
+    model = workloads.LLAMA3_70B if (tp or shards > 1) else workloads.LLAMA3_8B
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
     full_projs = model.layer_projections()
-    projs = [workloads.shard(p, world) for p in full_projs]
-    head = workloads.shard(model.output_projection(), world)
+    projs = [workloads.shard(p, shards) for p in full_projs]
+    head = workloads.shard(model.output_projection(), shards)
     layers = [[random_blocks_device(torch, p.dtype, p.n, p.k, gen) for p in projs] for _ in range(model.layers)]
     head_w = random_blocks_device(torch, head.dtype, head.n, head.k, gen)
     ks = sorted({p.k for p in projs} | {head.k})
@@ -421,6 +426,9 @@ def main():
                                [projs[i].n for i in g], outs=[outs[li][i] for i in g])
             for i, (p, w, o) in enumerate(zip(projs, layers[li], outs[li])):
                 if i in grouped:
+                    continue
+                if tp and p.split == "row" and peer_ar is not None and not args.unfused_allreduce:
+                    peer_ar.gemv_sum(p.dtype, w, x_dev[p.k], p.n, out=o)  # matmul + exchange in one launch
                     continue
                 ops.gemv(p.dtype, w, x_dev[p.k], p.n, out=o)
                 if tp and p.split == "row":
@@ -609,7 +617,7 @@ def main():
                                 f"{bytes_per_step / 1e9:.2f} GB of weights per token and GPU)"),
                    "l2": "inputs larger than L2: every step streams its GBs of distinct weights",
                    "parallelism": (f"tp{world}: column / row split, {allreduces_per_step} "
-                                   f"{'peer-memory (b200q_peer_allreduce)' if peer_ar is not None else 'NCCL'} all-reduces per token") if tp else "1 gpu",
+                                   f"{('peer-memory all-reduces fused into the row-parallel GEMVs (b200q_gemv_allreduce)' if not args.unfused_allreduce else 'peer-memory all-reduces (b200q_peer_allreduce)') if peer_ar is not None else 'NCCL all-reduces'} per token") if tp else "1 gpu",
                    "cuda_graph": graph is not None, "pdl": ops.get_option("pdl"),
                    "grouped_launches": not args.no_group},
         "weights_GBps_per_gpu": bytes_per_step * tok_s / 1e9,

@@ -175,7 +175,7 @@ int b200q_gemv_tc(int type, int elem, const void* w, const void* x, void* y, int
  * crates/inference-quant/src/distributed/mod.rs:516-670; distributed/layers.rs:814-1190). Every rank calls it with the
  * same n and elem; out = sum over ranks of in, added in rank order in f32, so all ranks hold identical bits; in == out
  * is allowed. `bufs` is a host array of `world` device pointers: every rank's exchange buffer as mapped in THIS
- * process (bufs[rank] is the local one), each b200q_peer_allreduce_buffer_bytes(capacity) bytes, zeroed once before
+ * process (bufs[rank] is the local one), each b200q_peer_allreduce_buffer_bytes(capacity) = 1024 + 4 capacity bytes, zeroed once before
  * the first call and otherwise touched only by this function; capacity (bytes, multiple of 16) bounds n * sizeof(elem).
  * Needs 16-byte aligned in / out and n * sizeof(elem) a multiple of 16; world <= 8. Device-side sequence numbers only:
  * captured calls can be replayed. A rank that never arrives makes the others give up after about a second, set the
@@ -183,6 +183,17 @@ int b200q_gemv_tc(int type, int elem, const void* w, const void* x, void* y, int
 long long b200q_peer_allreduce_buffer_bytes(long long capacity);
 int b200q_peer_allreduce(const void* const* bufs, int rank, int world, long long capacity, int elem, const void* in, void* out,
                          long long n, void* stream);
+
+/* The row-parallel matmul and its exchange in ONE launch (the reference runs them as two operations:
+ * RowParallelLayer::forward_raw, crates/inference-quant/src/distributed/layers.rs:1036-1046): b200q_gemv on contiguous
+ * x [b_size][K] -> dst [b_size][N] whose last CTA to finish (device-wide arrival counter in the exchange buffer) runs
+ * b200q_peer_allreduce's protocol on dst in place, so that after the launch every rank's dst holds the sum of all
+ * ranks' partial outputs, bit-identical on all ranks and to b200q_gemv followed by b200q_peer_allreduce. Same `bufs`,
+ * `capacity` and calling discipline as b200q_peer_allreduce (all ranks, same order); b_size * N * sizeof(elem) must be a
+ * multiple of 16 and at most `capacity`, dst 16-byte aligned; B200Q_ERR_UNSUPPORTED otherwise or where b200q_gemv has
+ * no staged kernel for the shape (then: the two separate calls). world == 1 is a plain b200q_gemv. */
+int b200q_gemv_allreduce(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int b_size,
+                         const void* const* bufs, int rank, int world, long long capacity, void* stream);
 
 /* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,
  *        item slots per lane, register-resident slots} */

@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "peer_allreduce.cuh"
 #include "runtime.h"
 
 namespace b200q {
@@ -17,6 +18,7 @@ int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int
 int gemv_tc_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace, cudaStream_t s);
 size_t gemv_tc_workspace_bytes(int type, int K);
 long long peer_allreduce_buffer_bytes(long long capacity);
+int fill_peer_exchange(PeerExchange& px, const void* const* bufs, int rank, int world, long long capacity);
 int peer_allreduce(const void* const* bufs, int rank, int world, long long capacity, int elem, const void* in, void* out, long long n,
                    cudaStream_t s);
 
@@ -182,6 +184,20 @@ int b200q_peer_allreduce(const void* const* bufs, int rank, int world, long long
     if (rc == B200Q_ERR_UNSUPPORTED) return set_error(rc, "b200q_peer_allreduce needs 16-byte aligned in / out and a size that is a multiple of 16 bytes");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "peer all-reduce failed");
     return B200Q_OK;
+}
+
+// Row-parallel matmul and its sum over the ranks in ONE launch: b200q_gemv whose last CTA to finish runs the peer-memory
+// all-reduce on the output, in place.
+int b200q_gemv_allreduce(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int b_size, const void* const* bufs,
+                         int rank, int world, long long capacity, void* stream) {
+    if (!bufs) return set_error(B200Q_ERR_INVALID, "null pointer");
+    PeerExchange px{};
+    if (fill_peer_exchange(px, bufs, rank, world, capacity) != 0)
+        return set_error(B200Q_ERR_INVALID, "b200q_gemv_allreduce: 1..8 ranks, 16-byte aligned buffers, capacity a multiple of 16");
+    set_pending_peer_exchange(world > 1 ? &px : nullptr);
+    const int rc = b200q_gemv(type, elem, w, x, dst, K, N, K, N, b_size, 0, stream);
+    set_pending_peer_exchange(nullptr);
+    return rc;
 }
 
 // out[10] = {staged, grid, smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,

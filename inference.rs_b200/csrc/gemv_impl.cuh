@@ -21,6 +21,7 @@
 //  * Every mbarrier wait is bounded and reports through the device status word.
 #pragma once
 #include "common.cuh"
+#include "peer_allreduce.cuh"
 #include "runtime.h"
 
 namespace b200q {
@@ -55,6 +56,7 @@ struct GemvParams {
     int act_vec;         // raw activations: rows are 16-byte aligned
     unsigned int* status;  // device status word
     unsigned long long* trace;  // optional: 8 timestamps (ns) written by the first and the last CTA, or nullptr
+    PeerExchange px;     // px.world > 1: the last CTA to finish sums dst over the ranks in place (row-parallel matmul)
 };
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -736,6 +738,26 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }
+    if (p.px.world > 1) {
+        // fused exchange: the CTA that finishes last (device-wide arrival counter in the exchange buffer) sums the
+        // output over the ranks through peer memory, in place; no second launch, no second trip through the host queue
+        __shared__ unsigned int s_px[3];
+        __threadfence();  // this CTA's outputs, before it is counted
+        named_bar_sync(1, GEMV_CONSUMER_THREADS);
+        if (tid == 0) {
+            unsigned int* counter = reinterpret_cast<unsigned int*>(p.px.bufs[p.px.rank] + PAR_COUNTER_OFFSET);
+            const unsigned int before = atomicAdd(counter, 1u);
+            s_px[2] = before == gridDim.x - 1 ? 1u : 0u;
+            if (s_px[2]) *counter = 0u;  // for the next launch
+        }
+        named_bar_sync(1, GEMV_CONSUMER_THREADS);
+        if (s_px[2]) {
+            __threadfence();
+            const long long units = (long long)B * p.N * (long long)sizeof(dst_t) / 16;
+            peer_allreduce_slice<dst_t, true>(p.px, PAR_HEADER_BYTES + 2 * (size_t)p.px.capacity, PAR_FUSED_BLOCK, p.dst, p.dst, 0, units, tid,
+                                              GEMV_CONSUMER_THREADS, p.status, s_px);
+        }
+    }
     GEMV_TRACE(4);
 }
 
@@ -1187,6 +1209,14 @@ static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int 
     plan.p.stride_dst = stride_dst;
     plan.p.status = status_ptr();
     plan.p.trace = trace_slot();
+    plan.p.px.world = 0;
+    if (const PeerExchange* px = take_pending_peer_exchange()) {
+        // fused all-reduce: the staged kernel only, contiguous [B][N] output of whole 16-byte units within the capacity
+        const long long bytes = (long long)B * N * (long long)sizeof(dst_t);
+        if (!plan.staged || stride_dst != N || bytes % 16 != 0 || bytes > px->capacity || reinterpret_cast<uintptr_t>(dst) % 16 != 0)
+            return B200Q_ERR_UNSUPPORTED;
+        plan.p.px = *px;
+    }
     if (plan.staged) {
         if (act_mode == ACT_Q8_1) return launch_staged<TYPE, B, dst_t, ACT_Q8_1, float>(plan, s);
         // raw activations have the output's type

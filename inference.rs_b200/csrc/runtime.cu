@@ -61,6 +61,14 @@ void set_trace_buffer(unsigned long long* dev, int records) {
     g_trace_records = records;
     g_trace_next = 0;
 }
+static thread_local const PeerExchange* t_pending_px = nullptr;
+void set_pending_peer_exchange(const PeerExchange* px) { t_pending_px = px; }
+const PeerExchange* take_pending_peer_exchange() {
+    const PeerExchange* px = t_pending_px;
+    t_pending_px = nullptr;
+    return px;
+}
+
 unsigned long long* trace_buffer(int* slots) {
     *slots = g_trace ? g_trace_records * 16 : 0;
     return g_trace;

@@ -31,7 +31,13 @@ unsigned int* status_ptr();          // device address of the status word of the
 // diagnostics: when a trace buffer is set, every GEMV launch gets the next 16-slot record of it (wrapping)
 void set_trace_buffer(unsigned long long* dev, int records);
 unsigned long long* trace_slot();
-unsigned long long* trace_buffer(int* slots);  // the whole buffer (16 slots per record), or nullptr
+unsigned long long* trace_buffer(int* slots);
+
+// The exchange buffers a fused matmul + all-reduce call hands to the next GEMV launch of this host thread (the launch
+// takes and clears it); nullptr otherwise.
+struct PeerExchange;
+void set_pending_peer_exchange(const PeerExchange* px);
+const PeerExchange* take_pending_peer_exchange();  // the whole buffer (16 slots per record), or nullptr
 int note_launch_status(int status);  // remembers the first non-zero status; returns its argument
 int take_launch_status();            // returns and clears it
 

@@ -47,6 +47,7 @@ SYMBOLS.update({
     "b200q_gemv_tc_workspace_bytes": ([_i32, _i32], _i64),
     "b200q_peer_allreduce_buffer_bytes": ([_i64], _i64),
     "b200q_peer_allreduce": ([_vp, _i32, _i32, _i64, _i32, _vp, _vp, _i64, _vp], _i32),
+    "b200q_gemv_allreduce": ([_i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _i32, _i32, _i64, _vp], _i32),
     "b200q_gemv_group": ([_i32, C.POINTER(_i32), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i32), _i32, _i32, _vp, _vp], _i32),
     "b200q_gemv_static_scratch": ([_i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
     "b200q_gemv_plan": ([_i32, _i32, _i32, _i32, C.POINTER(_i32 * 10)], _i32),

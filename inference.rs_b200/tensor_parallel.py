@@ -169,6 +169,18 @@ class PeerSumAllReduce(SumAllReduce):
                        "b200q_peer_allreduce")
         return out
 
+    def gemv_sum(self, dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
+        """`b200q_gemv_allreduce`: this rank's row-parallel matmul (x `[rows <= 8, k / w]` contiguous) and the sum over
+        the ranks in one launch. Raises `KernelLibraryError` where the fused launch does not apply (shape, alignment,
+        capacity): callers then use `ops.gemv` + `sum_all_reduce_`."""
+        from .ops import _stream, elem_of
+        rows, k = x.shape
+        y = torch.empty((rows, n), dtype=x.dtype, device=x.device) if out is None else out
+        self._kl.check(self._kl.library().b200q_gemv_allreduce(int(dtype), elem_of(x.dtype), w.data_ptr(), x.data_ptr(), y.data_ptr(), k, n,
+                                                               rows, self._ptrs, self.rank, self.world, self.capacity, _stream()),
+                       "b200q_gemv_allreduce")
+        return y
+
     def sum_all_reduce_(self, xs: torch.Tensor) -> torch.Tensor:
         """In place (no allocation: for captured decode steps)."""
         from .ops import _stream, elem_of

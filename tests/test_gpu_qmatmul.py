@@ -196,6 +196,17 @@ def _peer_rank(rank, world, port, ret):
             gathered = [torch.empty_like(got) for _ in range(world)]
             dist.all_gather(gathered, got)
             same = same and all(torch.equal(gathered[0], t) for t in gathered)  # identical bits on every rank
+        # the fused launch (row-parallel matmul + exchange) equals the two separate calls bit for bit
+        from inference_rs_b200 import ops as ops_
+        fused_ok = True
+        for type_id, n, k, rows in ((kq.Q4_K, 8192, 1024, 1), (kq.Q6_K, 4096, 2048, 2), (kq.Q8_0, 1000, 512, 1)):
+            packed = kq.quantize(type_id, seeded_weights(n, k, 300 + rank + type_id))
+            w_dev = ops_.upload_weights(packed, DT[type_id], f"cuda:{rank}")
+            xr = seeded_acts(rows, k, 400 + rank, torch.bfloat16).cuda(rank)
+            two = ar.sum_all_reduce(ops_.gemv(DT[type_id], w_dev, xr, n))
+            for _ in range(2):
+                one = ar.gemv_sum(DT[type_id], w_dev, xr, n)
+                fused_ok = fused_ok and torch.equal(one, two)
         # a vector beyond the capacity goes through NCCL
         big = torch.ones(1, 1 << 16, dtype=torch.bfloat16, device=f"cuda:{rank}")
         assert float(ar.sum_all_reduce(big)[0, 0]) == world
@@ -216,7 +227,7 @@ def _peer_rank(rank, world, port, ret):
         replay_ok = float(y[0, 0]) == world * (world + 1) / 2
         torch.cuda.synchronize()
         import inference_rs_b200 as pkg_
-        ret[rank] = (worst, same, replay_ok, list(pkg_.kernel_library.device_status()))
+        ret[rank] = (worst, same, replay_ok and fused_ok, list(pkg_.kernel_library.device_status()))
     finally:
         dist.destroy_process_group()
 
