@@ -529,7 +529,9 @@ __device__ __forceinline__ float dot(const Weights<TYPE_Q8_0>& W, const ActPair&
 // lane owns items slice*32 + lane + j*32*WPR, j < IPL. With fewer, a warp works on 32 / islots rows at once
 // (islots = items rounded up to a power of two): lane = rsub * islots + item.
 // ---------------------------------------------------------------------------------------------
-template <int TYPE, int B, typename dst_t, int ACT, typename act_t, int NREG>
+// AR: the variant whose last CTA sums the output over the tensor-parallel ranks (its own instantiation, so that the
+// plain kernel carries none of it)
+template <int TYPE, int B, typename dst_t, int ACT, typename act_t, int NREG, bool AR = false>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -738,7 +740,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }
-    if (p.px.world > 1) {
+    if constexpr (AR) {
         // fused exchange: the CTA that finishes last (device-wide arrival counter in the exchange buffer) sums the
         // output over the ranks through peer memory, in place; no second launch, no second trip through the host queue
         __shared__ unsigned int s_px[3];
@@ -1178,9 +1180,9 @@ static inline cudaError_t launch_gemv_kernel(Kern kernel, int grid, int block, s
     return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
-template <int TYPE, int B, typename dst_t, int ACT, typename act_t, int NREG>
-static inline int launch_staged_n(const GemvPlan& plan, cudaStream_t s) {
-    auto kernel = gemv_staged_kernel<TYPE, B, dst_t, ACT, act_t, NREG>;
+template <int TYPE, int B, typename dst_t, int ACT, typename act_t, int NREG, bool AR>
+static inline int launch_staged_ar(const GemvPlan& plan, cudaStream_t s) {
+    auto kernel = gemv_staged_kernel<TYPE, B, dst_t, ACT, act_t, NREG, AR>;
     static bool configured = false;  // per instantiation; the attribute is set on the first launch
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1189,6 +1191,16 @@ static inline int launch_staged_n(const GemvPlan& plan, cudaStream_t s) {
         configured = true;
     }
     return (int)launch_gemv_kernel(kernel, plan.grid, GEMV_THREADS, plan.smem, s, plan.p.use_pdl != 0, plan.p);
+}
+
+template <int TYPE, int B, typename dst_t, int ACT, typename act_t, int NREG>
+static inline int launch_staged_n(const GemvPlan& plan, cudaStream_t s) {
+    if (plan.p.px.world > 1) {
+        // the fused exchange exists for raw activations in the decode quantizer's arithmetic (what b200q_gemv runs)
+        if constexpr (ACT == ACT_RAW_Q8_1) return launch_staged_ar<TYPE, B, dst_t, ACT, act_t, NREG, true>(plan, s);
+        else return B200Q_ERR_UNSUPPORTED;
+    }
+    return launch_staged_ar<TYPE, B, dst_t, ACT, act_t, NREG, false>(plan, s);
 }
 
 template <int TYPE, int B, typename dst_t, int ACT, typename act_t>
