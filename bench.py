@@ -417,7 +417,17 @@ def main():
     peer_ar = None
     if tp and not args.nccl_allreduce:
         from inference_rs_b200.tensor_parallel import PeerSumAllReduce
-        peer_ar = PeerSumAllReduce(capacity=1 << 16)
+        made = 1
+        try:
+            peer_ar = PeerSumAllReduce(capacity=1 << 16)
+        except Exception as exc:  # no peer mappings on this machine: every rank falls back to NCCL together
+            print(f"[bench] rank {rank}: peer-memory exchange unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+            made = 0
+        agree = torch.tensor([made], device="cuda")
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if int(agree.item()) == 0:
+            peer_ar = None
+    fused_ok = {}  # projection index -> the fused matmul + exchange launch takes this shape (found out on the first, eager step)
 
     def step():
         for li in range(model.layers):
@@ -427,9 +437,12 @@ def main():
             for i, (p, w, o) in enumerate(zip(projs, layers[li], outs[li])):
                 if i in grouped:
                     continue
-                if tp and p.split == "row" and peer_ar is not None and not args.unfused_allreduce:
-                    peer_ar.gemv_sum(p.dtype, w, x_dev[p.k], p.n, out=o)  # matmul + exchange in one launch
-                    continue
+                if tp and p.split == "row" and peer_ar is not None and not args.unfused_allreduce and fused_ok.get(i, True):
+                    try:
+                        peer_ar.gemv_sum(p.dtype, w, x_dev[p.k], p.n, out=o)  # matmul + exchange in one launch
+                        continue
+                    except pkg.KernelLibraryError:
+                        fused_ok[i] = False  # the same on every rank (same shapes): two launches for this projection
                 ops.gemv(p.dtype, w, x_dev[p.k], p.n, out=o)
                 if tp and p.split == "row":
                     if peer_ar is not None:
