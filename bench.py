@@ -376,6 +376,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
     torch.cuda.set_device(local_rank)
     if world > 1:
+        # NCCL only carries the logits all-gather and the timing reductions here; without in-switch (NVLS) buffers no rank's
+        # memory stays bound to an NVLink multicast object when the processes leave
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pkg.library()
 
