@@ -14,8 +14,8 @@
 //   2. gemv_tc_i8_kernel: one persistent CTA per SM owns a contiguous run of weight rows and walks it in tiles of up
 //      to 128 rows (= TMEM lanes). Per stage of 256 k:
 //        warp 3       TMA (2-D tensor map over the packed bytes) brings the tile's 256-k chunk of every row;
-//        warps 4-11   unpack quants to int8 into a K-major 128-byte-swizzled A stage, and the rows' block scales
-//                     to f32 into a side buffer;
+//        warps 4-11   (two groups of four on alternate stages) unpack quants to int8 into a K-major
+//                     128-byte-swizzled A stage, and the rows' block scales to f32 into a side buffer;
 //        warp 0       TMA brings the activation tile (B operand) and its scales;
 //        warp 1       issues 8 tcgen05.mma kind::i8 (M = 128, N = 16 or 32, K = 32), one per 32-value block, each
 //                     into its own TMEM columns (no accumulation across blocks: scales differ);
