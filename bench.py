@@ -1,16 +1,21 @@
 #!/usr/bin/env python
 """Benchmark of the GGUF quantized-matmul decode path on B200.
 
-One "step" is one token's worth of quantized matmuls of a Llama-3-8B-shaped Q4_K_M model at batch 1: per layer
-attn_q/k/v, attn_output, ffn_gate/up/down, times 32 layers, plus the output head: 225 GEMVs over 4.88 GB of packed
-weights (every layer has its own weights, so each step streams far more than the 126 MB L2). Attention, norms and
-sampling are not part of the path and are not run. Weights are random well-formed GGUF blocks, activations ~N(0,1) bf16.
+One "step" is one token's worth of quantized matmuls of a Llama-3-shaped Q4_K_M model at batch 1: per layer
+attn_q/k/v, attn_output, ffn_gate/up/down, plus the output head. On one GPU that is the 8B shape (225 GEMVs over
+4.88 GB of packed weights); on N > 1 GPUs the 70B shape, tensor-parallel as the reference splits it (q/k/v, gate/up and
+the head by output rows; attn_output and ffn_down by input columns in whole superblocks, each followed by a sum
+all-reduce of the [1, hidden] partial output). Every layer has its own weights, so each step streams far more than the
+126 MB L2. Attention, norms and sampling are not part of the path and are not run. Weights are random well-formed GGUF
+blocks, activations ~N(0,1) bf16.
 
-  value     tok/s with inputs resident in HBM, timed with CUDA events over K steps (CUDA-graph replay of the step)
-  e2e       the same through the host-buffer call: every step copies the token's activations from pinned host memory
-            and reads the logits back
-  roofline  the dominant kernel (Q4_K GEMV, ffn_gate/up shape) timed alone over the 64 distinct gate/up weights
+  value        tok/s with inputs resident in HBM, timed with CUDA events over K steps (CUDA-graph replay of the step)
+  e2e          the same through the host-buffer call: every step copies the token's activations from pinned host memory
+               and reads the logits back
+  roofline     the dominant launch (ffn_gate + ffn_up) timed alone over all layers' distinct weights
   cpu_baseline / --impl reference   the CPU oracle (a C restatement of the reference's k_quants::matmul) on the host cores
+  reference_cuda   the reference's own CUDA kernels (generic dp4a / mma.sync, compiled for sm_100a from the reference
+               checkout into oracle/_ref) on the same chain and shapes, when that library was built
 
 Prints one JSON line on rank 0.
 """
@@ -37,8 +42,24 @@ def load_peaks():
     if os.path.exists(p):
         with open(p) as fh:
             d = json.load(fh)
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def host_threads() -> int:
+    """Host cores this process may use. Not OMP_NUM_THREADS: torch.distributed.run sets that to 1 for its children."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def workload_name(model, world: int) -> str:
+    """The same string in both arms (ours and --impl reference) at a given N."""
+    gemvs = model.layers * len(model.layer_projections()) + 1
+    gb = model.weight_bytes_per_token() / 1e9
+    tp = "" if world == 1 else f", tensor-parallel over {world} GPUs"
+    return f"{model.name} Q4_K_M decode matmul chain, batch 1{tp} ({gemvs} GEMVs, {gb:.2f} GB of weights per token)"
 
 
 class ClockSampler:
@@ -133,9 +154,19 @@ def time_launch_list(torch, stream, launches, reps):
     return e0.elapsed_time(e1) * 1000.0 / (reps * len(launches))
 
 
+def register_launch_order(ops, seq):
+    """seq: one (key weight, first weight, dtype, k, n) per launch, in stream order; the order is cyclic (the last
+    launch of a token is followed by the first of the next). Tells the library which matrix follows which."""
+    for i, (key, _, _, _, _) in enumerate(seq):
+        _, nxt, ndt, nk, nn = seq[(i + 1) % len(seq)]
+        ops.set_weight_successor(key, nxt, ndt, nk, nn)
+
+
 # DRAM bytes per launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum); the summaries are under profiles/
 NCU_TRAFFIC_GEMV_Q4K_4096_14336 = 33085184
 NCU_TRAFFIC_GROUP_GATE_UP = 66442752
+
+TYPE_TAGS = {"q4_k": "Q4K", "q6_k": "Q6K", "q8_0": "Q8_0"}
 
 
 def run_single(args):
@@ -147,7 +178,7 @@ def run_single(args):
     from inference_rs_b200 import ops
 
     tname, k, n, b = args.single[0], int(args.single[1]), int(args.single[2]), int(args.single[3])
-    dt = {"q4_k": pkg.GgmlDType.Q4K, "q6_k": pkg.GgmlDType.Q6K, "q8_0": pkg.GgmlDType.Q8_0}[tname]
+    dt = getattr(pkg.GgmlDType, TYPE_TAGS[tname])
     torch.cuda.set_device(0)
     gen = torch.Generator(device="cuda").manual_seed(7)
     wbytes = n * dt.row_bytes(k)
@@ -155,6 +186,8 @@ def run_single(args):
     ws = [random_blocks_device(torch, dt, n, k, gen) for _ in range(copies)]
     x = torch.randn(b, k, device="cuda", generator=gen).to(torch.bfloat16)
     out = torch.empty(b, n, dtype=torch.bfloat16, device="cuda")
+    if not args.no_prefetch and not args.tc:
+        register_launch_order(ops, [(w, w, dt, k, n) for w in ws])
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         if args.two_launch:
@@ -167,7 +200,7 @@ def run_single(args):
             outs2 = [torch.empty(b, n, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
 
             def mk(w):
-                return lambda: ops.gemv_group([dt, dt], [w, ws[0]], x, [n, n], outs=outs2)
+                return lambda: ops.gemv_group([dt, dt], [ws[0], w], x, [n, n], outs=outs2)
         elif args.tc:
             tc_ws = ops.gemv_tc_workspace(dt, k)
 
@@ -175,7 +208,7 @@ def run_single(args):
                 return lambda: ops.gemv_tc(dt, w, x, n, out=out, workspace=tc_ws)
         else:
             def mk(w):
-                return lambda: ops.gemv(dt, w, x, n, out=out)
+                return lambda: ops.gemv(dt, w, x, n, out=out, act_quant=args.act_quant)
         launches = [mk(w) for w in ws]
         if args.no_graph:
             for fn in launches:
@@ -191,13 +224,16 @@ def run_single(args):
             us = e0.elapsed_time(e1) * 1000.0 / (args.steps * len(launches))
         else:
             us = time_launch_list(torch, stream, launches, args.steps)
-    peak, src = load_peaks()
+    peak, _, src = load_peaks()
     alg = wbytes + b * k * 2 + b * n * 2
     if args.group2:
         alg = 2 * wbytes + b * k * 2 + 2 * b * n * 2
     print(json.dumps({"single": tname, "k": k, "n": n, "b": b, "copies": copies, "us_per_launch": us,
                       "GBps": alg / us / 1e3, "frac_of_" + src: alg / us / 1e3 / peak, "algorithmic_bytes": alg,
-                      "kernel": "gemv_tc" if args.tc else ("gemv_group x2" if args.group2 else "gemv"), "plan": None if (args.tc or b > 8) else ops.gemv_plan(dt, k, n, b), "device_status": list(pkg.kernel_library.device_status())}),
+                      "kernel": "gemv_tc" if args.tc else ("gemv_group x2" if args.group2 else "gemv"),
+                      "l2_prefetch_bytes": 0 if args.no_prefetch else ops.get_option("l2_prefetch_bytes"), "pdl": ops.get_option("pdl"),
+                      "plan": None if (args.tc or b > 8) else ops.gemv_plan(dt, k, n, b),
+                      "device_status": list(pkg.kernel_library.device_status())}),
           flush=True)
 
 
@@ -209,7 +245,7 @@ def run_gemm_single(args):
     from inference_rs_b200 import ops
 
     tname, k, n, m = args.gemm[0], int(args.gemm[1]), int(args.gemm[2]), int(args.gemm[3])
-    dt = {"q4_k": pkg.GgmlDType.Q4K, "q6_k": pkg.GgmlDType.Q6K, "q8_0": pkg.GgmlDType.Q8_0}[tname]
+    dt = getattr(pkg.GgmlDType, TYPE_TAGS[tname])
     torch.cuda.set_device(0)
     gen = torch.Generator(device="cuda").manual_seed(11)
     w = random_blocks_device(torch, dt, n, k, gen)
@@ -228,17 +264,14 @@ def run_gemm_single(args):
         stream.synchronize()
     us = e0.elapsed_time(e1) * 1000.0 / args.steps
     tflops = 2.0 * m * n * k / us / 1e6
-    peak = 1647.9
-    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(p):
-        peak = float(json.load(open(p))["bf16_tflops"])
+    _, peak, _ = load_peaks()
     print(json.dumps({"gemm": tname, "k": k, "n": n, "m": m, "us": us, "TFLOPs": tflops, "frac_of_measured_bf16": tflops / peak,
                       "device_status": list(pkg.kernel_library.device_status())}), flush=True)
 
 
 def cpu_chain_sample(model, threads, seconds_budget=12.0):
-    """Times the CPU oracle on one layer's projections plus the output head at batch 1 and scales to a token.
-    Returns (tok/s, description)."""
+    """Times the CPU oracle on one layer's projections plus a slice of the output head at batch 1 and scales to a
+    token. Returns (tok/s, description)."""
     import numpy as np
     from oracle import kquants as kq
     type_of = {"Q8_0": kq.Q8_0, "Q4K": kq.Q4_K, "Q6K": kq.Q6_K}
@@ -284,19 +317,20 @@ def cpu_chain_sample(model, threads, seconds_budget=12.0):
         best_layer, best_head = min(best_layer, tl), min(best_head, th)
         reps += 1
     tok_s = 1.0 / (best_layer * model.layers + best_head)
-    desc = (f"1 of {model.layers} layers (7 projections) + 1/8 of the output head at batch 1, best of {reps} passes, "
-            f"scaled to a token; scalar/auto-vectorised C port of k_quants::matmul, {threads} threads")
+    desc = (f"{model.name}: 1 of {model.layers} layers (7 projections, unsharded) + 1/8 of the output head at batch 1, best of {reps} "
+            f"passes, scaled to a token; scalar/auto-vectorised C port of k_quants::matmul, {threads} threads")
     return tok_s, desc
 
 
 def run_reference(args, rank, world):
-    """--impl reference: the reference's CPU path (oracle port; the Rust reference cannot be built here)."""
+    """--impl reference: the reference's CPU path on the host cores (the oracle port: the Rust reference cannot be built
+    here), on the same model as our arm runs at this N - the whole model on one host, as the CPU path has no tensor
+    parallelism."""
     if rank != 0:
         return
-    from oracle import kquants as kq
     from inference_rs_b200 import workloads
-    threads = kq.max_threads()
-    model = workloads.LLAMA3_8B
+    threads = host_threads()
+    model = workloads.LLAMA3_70B if world > 1 else workloads.LLAMA3_8B
     vals = []
     desc = ""
     t0 = time.perf_counter()
@@ -308,14 +342,166 @@ def run_reference(args, rank, world):
     value = max(vals)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
-        "config": {"workload": "llama3-8b Q4_K_M decode matmul chain, batch 1 (225 GEMVs, 4.88 GB of weights per token)"},
+        "config": {"workload": workload_name(model, world)},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t0,
     }
     print(json.dumps(line), flush=True)
+
+
+class Chain:
+    """One rank's share of a model's decode matmul chain: weights, activations, outputs and the step that launches it."""
+
+    def __init__(self, torch, pkg, ops, workloads, model, shards, seed, group=True, act_quant=0, weights_of=None):
+        self.torch, self.ops, self.model, self.shards = torch, ops, model, shards
+        self.act_quant = act_quant
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        self.projs = [workloads.shard(p, shards) for p in model.layer_projections()]
+        self.head = workloads.shard(model.output_projection(), shards)
+        if weights_of is not None:  # another chain's weights (same model and sharding)
+            self.layers, self.head_w = weights_of.layers, weights_of.head_w
+        else:
+            self.layers = [[random_blocks_device(torch, p.dtype, p.n, p.k, gen) for p in self.projs] for _ in range(model.layers)]
+            self.head_w = random_blocks_device(torch, self.head.dtype, self.head.n, self.head.k, gen)
+        self.ks = sorted({p.k for p in self.projs} | {self.head.k})
+        self.x_host = {k: torch.randn(1, k, generator=torch.Generator().manual_seed(k)).to(torch.bfloat16).pin_memory() for k in self.ks}
+        self.x_dev = {k: v.cuda() for k, v in self.x_host.items()}
+        self.outs = [[torch.empty(1, p.n, dtype=torch.bfloat16, device="cuda") for p in self.projs] for _ in range(model.layers)]
+        self.logits = torch.empty(1, self.head.n, dtype=torch.bfloat16, device="cuda")
+        self.bytes_per_step = model.layers * sum(p.weight_bytes for p in self.projs) + self.head.weight_bytes  # per GPU
+        # projections that read the same input go out in one launch: q/k/v, gate/up (the reference's fused_qkv / fused_glu
+        # matvec launches, crates/inference-quant/src/lib.rs:2441-2776); the grouped kernel quantizes to Q8_1 only
+        self.groups = []
+        if group and act_quant == 0:
+            names = [p.name for p in self.projs]
+            for members in (("attn_q", "attn_k", "attn_v"), ("ffn_gate", "ffn_up")):
+                self.groups.append([names.index(m) for m in members])
+        self.grouped = {i for g in self.groups for i in g}
+        self.launches_per_step = model.layers * (len(self.projs) - len(self.grouped) + len(self.groups)) + 1
+        self.gemvs_per_step = model.layers * len(self.projs) + 1
+
+    def launch_sequence(self):
+        """(key weight, first weight, dtype, k, n) per launch, in the order step() issues them."""
+        seq = []
+        for li in range(self.model.layers):
+            for g in self.groups:
+                first, last = g[0], g[-1]
+                seq.append((self.layers[li][last], self.layers[li][first], self.projs[first].dtype, self.projs[first].k, self.projs[first].n))
+            for i, p in enumerate(self.projs):
+                if i not in self.grouped:
+                    seq.append((self.layers[li][i], self.layers[li][i], p.dtype, p.k, p.n))
+        seq.append((self.head_w, self.head_w, self.head.dtype, self.head.k, self.head.n))
+        return seq
+
+    def step(self, row_parallel=None, after_head=None):
+        """row_parallel(i, p, w, x, out): launches projection i's matmul and its exchange (tensor parallel), or None."""
+        ops = self.ops
+        for li in range(self.model.layers):
+            for g in self.groups:
+                ops.gemv_group([self.projs[i].dtype for i in g], [self.layers[li][i] for i in g], self.x_dev[self.projs[g[0]].k],
+                               [self.projs[i].n for i in g], outs=[self.outs[li][i] for i in g])
+            for i, (p, w, o) in enumerate(zip(self.projs, self.layers[li], self.outs[li])):
+                if i in self.grouped:
+                    continue
+                if row_parallel is not None and p.split == "row":
+                    row_parallel(i, p, w, self.x_dev[p.k], o)
+                else:
+                    ops.gemv(p.dtype, w, self.x_dev[p.k], p.n, out=o, act_quant=self.act_quant)
+        ops.gemv(self.head.dtype, self.head_w, self.x_dev[self.head.k], self.head.n, out=self.logits, act_quant=self.act_quant)
+        if after_head is not None:
+            after_head()
+
+    def free(self):
+        self.ops.clear_weight_successors()
+        self.layers = self.head_w = self.outs = None
+
+
+def time_chain(torch, stream, step, steps, warmup, use_graph=True):
+    """ms per step of `step` (CUDA events on `stream`), after one eager run, capture and `warmup` replays."""
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        graph = None
+        if use_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+        run = graph.replay if graph is not None else step
+        for _ in range(warmup):
+            run()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            run()
+        e1.record(stream)
+        stream.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+
+def reference_cuda_numbers(torch, pkg, chain, stream, peak, bf16_peak, steps):
+    """The reference's own CUDA kernels on this GPU (oracle/_ref, built from the reference checkout): its decode chain
+    as its host would launch it - one Q8_1 quantize per distinct input, plain matvecs for q/k/v (mixed types), the
+    fused gate/up matvec, plain matvecs for attn_output, ffn_down and the head - and its prefill path (quantize + MMQ)
+    on a few shapes. Returns None when the library is not there."""
+    try:
+        from oracle import refkernels as rk
+        if not rk.available():
+            return None
+    except Exception as exc:  # missing file, unloadable library
+        return {"unavailable": f"{type(exc).__name__}: {exc}"}
+    model, projs = chain.model, chain.projs
+    names = [p.name for p in projs]
+    idx = {n: names.index(n) for n in names}
+    x = chain.x_dev
+    bf = torch.bfloat16
+
+    def step():
+        for li in range(model.layers):
+            w = chain.layers[li]
+            vy = rk.quantize_q8_1(x[projs[0].k])
+            for nme in ("attn_q", "attn_k", "attn_v"):
+                p = projs[idx[nme]]
+                rk.mmvq_plain(int(p.dtype), w[idx[nme]], vy, p.n, p.k, 1, bf)
+            p = projs[idx["attn_output"]]
+            rk.mmvq_plain(int(p.dtype), w[idx["attn_output"]], rk.quantize_q8_1(x[p.k]), p.n, p.k, 1, bf)
+            p = projs[idx["ffn_gate"]]
+            rk.fused_glu(int(p.dtype), w[idx["ffn_gate"]], w[idx["ffn_up"]], x[p.k], p.n)
+            p = projs[idx["ffn_down"]]
+            rk.mmvq_plain(int(p.dtype), w[idx["ffn_down"]], rk.quantize_q8_1(x[p.k]), p.n, p.k, 1, bf)
+        rk.mmvq_plain(int(chain.head.dtype), chain.head_w, rk.quantize_q8_1(x[chain.head.k]), chain.head.n, chain.head.k, 1, bf)
+
+    ms = time_chain(torch, stream, step, max(3, steps // 4), 3)
+    out = {"kernels": "reference mmvq_gguf dp4a matvecs + fused_glu, compiled for sm_100a with the reference's nvcc flags",
+           "decode_chain_tok_per_s": 1000.0 / ms, "decode_chain_ms": ms,
+           "decode_chain_hbm_frac_of_measured": chain.bytes_per_step / (ms * 1e-3) / 1e9 / peak}
+    # prefill: quantize + MMQ, a few shapes
+    pre = []
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    with torch.cuda.stream(stream):
+        for dt, k, n in ((pkg.GgmlDType.Q4K, 4096, 4096), (pkg.GgmlDType.Q4K, 14336, 4096), (pkg.GgmlDType.Q6K, 14336, 4096)):
+            wq = random_blocks_device(torch, dt, n, k, gen)
+            for m in (512, 2048, 8192):
+                xm = torch.randn(m, k, device="cuda", generator=gen).to(bf)
+                for _ in range(2):
+                    rk.mmq_forward(int(dt), wq, xm, n)
+                stream.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(5):
+                    rk.mmq_forward(int(dt), wq, xm, n)
+                e1.record(stream)
+                stream.synchronize()
+                us = e0.elapsed_time(e1) * 200.0
+                tf = 2.0 * m * n * k / us / 1e6
+                pre.append({"type": dt.name, "k": k, "n": n, "m": m, "us": round(us, 1), "TFLOPs": round(tf, 1),
+                            "frac_of_measured_bf16_peak": round(tf / bf16_peak, 3)})
+            del wq
+    out["prefill_mmq"] = pre
+    return out
 
 
 def main():
@@ -327,8 +513,11 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-group", action="store_true", help="one launch per projection instead of grouped q/k/v and gate/up")
+    ap.add_argument("--no-prefetch", action="store_true", help="do not register the launch order (no L2 prefetch of the next matrix)")
+    ap.add_argument("--quick", action="store_true", help="the headline numbers only (no prefill / small-batch / reference_cuda / tp_base keys)")
     ap.add_argument("--sweep", action="store_true", help="also time every shape of the decode sweep")
     ap.add_argument("--single", nargs=4, metavar=("TYPE", "K", "N", "B"), help="time one GEMV shape only (q4_k|q6_k|q8_0)")
+    ap.add_argument("--act-quant", type=int, default=0, help="--single: 0 = Q8_1 activations, 1 = the CPU path's format")
     ap.add_argument("--unfused-allreduce", action="store_true", help="N > 1: the peer-memory all-reduce as a launch of its own")
     ap.add_argument("--shard-of", type=int, default=0, help="N = 1 only: run one rank's share of the N-way 70B chain, no exchanges")
     ap.add_argument("--nccl-allreduce", action="store_true", help="N > 1: NCCL all-reduce instead of the peer-memory kernel")
@@ -339,7 +528,7 @@ def main():
     ap.add_argument("--two-launch", action="store_true", help="--single: quantize launcher + GEMV launcher instead of one launch")
     ap.add_argument("--pdl", type=int, default=None, help="programmatic dependent launch on/off")
     ap.add_argument("--stage-bytes", type=int, default=None, help="GEMV planner: target bytes per shared-memory stage")
-    ap.add_argument("--ctas-per-sm", type=int, default=None, help="GEMV planner: CTAs of one grid per SM (1 or 2)")
+    ap.add_argument("--prefetch-bytes", type=int, default=None, help="bytes of the next matrix each CTA asks L2 for")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -350,15 +539,13 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
+    from inference_rs_b200 import ops as _ops
     if args.pdl is not None:
-        from inference_rs_b200 import ops as _ops
         _ops.set_option("pdl", args.pdl)
-    if args.ctas_per_sm is not None:
-        from inference_rs_b200 import ops as _ops
-        _ops.set_option("gemv_ctas_per_sm", args.ctas_per_sm)
     if args.stage_bytes is not None:
-        from inference_rs_b200 import ops as _ops
         _ops.set_option("gemv_stage_bytes", args.stage_bytes)
+    if args.prefetch_bytes is not None:
+        _ops.set_option("l2_prefetch_bytes", args.prefetch_bytes)
     if args.single:
         run_single(args)
         return
@@ -376,46 +563,25 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        # NCCL only carries the logits all-gather and the timing reductions here; without in-switch (NVLS) buffers no rank's
-        # memory stays bound to an NVLink multicast object when the processes leave
+        # NCCL only carries the logits all-gather, the checks and the timing reductions here; without in-switch (NVLS)
+        # buffers no rank's memory stays bound to an NVLink multicast object when the processes leave
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pkg.library()
+    peak, bf16_peak, peak_src = load_peaks()
 
-    # one GPU: the Llama-3-8B-shaped chain. Several GPUs: the Llama-3-70B-shaped chain, tensor-parallel as the reference
-    # splits it (q/k/v, gate/up and the head by output rows; attn_output and ffn_down by input columns in whole
-    # superblocks, each followed by a sum all-reduce of the [1, hidden] partial output over NCCL)
     tp = world > 1
     # --shard-of N on one GPU: one rank's share of the N-way tensor-parallel 70B chain without the exchanges (what the
     # compute alone costs at those shard shapes)
     shards = args.shard_of if (args.shard_of and not tp) else world
     model = workloads.LLAMA3_70B if (tp or shards > 1) else workloads.LLAMA3_8B
-    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    full_projs = model.layer_projections()
-    projs = [workloads.shard(p, shards) for p in full_projs]
-    head = workloads.shard(model.output_projection(), shards)
-    layers = [[random_blocks_device(torch, p.dtype, p.n, p.k, gen) for p in projs] for _ in range(model.layers)]
-    head_w = random_blocks_device(torch, head.dtype, head.n, head.k, gen)
-    ks = sorted({p.k for p in projs} | {head.k})
-    x_host = {k: torch.randn(1, k, generator=torch.Generator().manual_seed(k)).to(torch.bfloat16).pin_memory() for k in ks}
-    x_dev = {k: v.cuda() for k, v in x_host.items()}
-    outs = [[torch.empty(1, p.n, dtype=torch.bfloat16, device="cuda") for p in projs] for _ in range(model.layers)]
-    logits = torch.empty(1, head.n, dtype=torch.bfloat16, device="cuda")
-    logits_all = torch.empty(world, head.n, dtype=torch.bfloat16, device="cuda") if tp else logits
+    chain = Chain(torch, pkg, ops, workloads, model, shards, 1234 + rank, group=not args.no_group)
+    if not args.no_prefetch:
+        register_launch_order(ops, chain.launch_sequence())
+    projs, head = chain.projs, chain.head
+    logits_all = torch.empty(world, head.n, dtype=torch.bfloat16, device="cuda") if tp else chain.logits
     logits_host = torch.empty(1, head.n * world, dtype=torch.bfloat16).pin_memory()
-    launches_per_step = model.layers * len(projs) + 1
-    bytes_per_step = model.layers * sum(p.weight_bytes for p in projs) + head.weight_bytes  # per GPU
     allreduces_per_step = model.layers * sum(1 for p in projs if p.split == "row") if tp else 0
-
-    # projections that read the same input go out in one launch: q/k/v, gate/up (the reference's fused_qkv / fused_glu
-    # matvec launches, crates/inference-quant/src/lib.rs:2441-2776)
-    groups = []
-    if not args.no_group:
-        names = [p.name for p in projs]
-        for members in (("attn_q", "attn_k", "attn_v"), ("ffn_gate", "ffn_up")):
-            groups.append([names.index(m) for m in members])
-    grouped = {i for g in groups for i in g}
-    launches_per_step = model.layers * (len(projs) - len(grouped) + len(groups)) + 1
 
     peer_ar = None
     if tp and not args.nccl_allreduce:
@@ -432,32 +598,59 @@ def main():
             peer_ar = None
     fused_ok = {}  # projection index -> the fused matmul + exchange launch takes this shape (found out on the first, eager step)
 
+    def row_parallel(i, p, w, x, o):
+        if peer_ar is not None and not args.unfused_allreduce and fused_ok.get(i, True):
+            try:
+                peer_ar.gemv_sum(p.dtype, w, x, p.n, out=o)  # matmul + exchange in one launch
+                return
+            except pkg.KernelLibraryError:
+                fused_ok[i] = False  # the same on every rank (same shapes): two launches for this projection
+        ops.gemv(p.dtype, w, x, p.n, out=o)
+        if peer_ar is not None:
+            peer_ar.sum_all_reduce_(o)
+        else:
+            dist.all_reduce(o)
+
+    def after_head():
+        dist.all_gather_into_tensor(logits_all, chain.logits)
+
     def step():
-        for li in range(model.layers):
-            for g in groups:
-                ops.gemv_group([projs[i].dtype for i in g], [layers[li][i] for i in g], x_dev[projs[g[0]].k],
-                               [projs[i].n for i in g], outs=[outs[li][i] for i in g])
-            for i, (p, w, o) in enumerate(zip(projs, layers[li], outs[li])):
-                if i in grouped:
-                    continue
-                if tp and p.split == "row" and peer_ar is not None and not args.unfused_allreduce and fused_ok.get(i, True):
-                    try:
-                        peer_ar.gemv_sum(p.dtype, w, x_dev[p.k], p.n, out=o)  # matmul + exchange in one launch
-                        continue
-                    except pkg.KernelLibraryError:
-                        fused_ok[i] = False  # the same on every rank (same shapes): two launches for this projection
-                ops.gemv(p.dtype, w, x_dev[p.k], p.n, out=o)
-                if tp and p.split == "row":
-                    if peer_ar is not None:
-                        peer_ar.sum_all_reduce_(o)
-                    else:
-                        dist.all_reduce(o)
-        ops.gemv(head.dtype, head_w, x_dev[head.k], head.n, out=logits)
-        if tp:
-            dist.all_gather_into_tensor(logits_all, logits)
+        chain.step(row_parallel if tp else None, after_head if tp else None)
 
     stream = torch.cuda.Stream()
     torch.cuda.synchronize()
+
+    # ---- tensor parallel: the exchange is checked on every rank count the bench runs at, before anything is timed: one
+    # row-parallel matmul per shape through the path the step uses, against ops.gemv + an f32 NCCL all-reduce, and the
+    # result must be the same bits on every rank
+    tp_check = None
+    if tp:
+        tp_check = "ok"
+        with torch.cuda.stream(stream):
+            for i, p in enumerate(projs):
+                if p.split != "row":
+                    continue
+                o = torch.empty(1, p.n, dtype=torch.bfloat16, device="cuda")
+                row_parallel(i, p, chain.layers[0][i], chain.x_dev[p.k], o)
+                part = ops.gemv(p.dtype, chain.layers[0][i], chain.x_dev[p.k], p.n).float()
+                stream.synchronize()
+                ref = part.clone()
+                dist.all_reduce(ref)
+                gathered = [torch.empty_like(o) for _ in range(world)]
+                dist.all_gather(gathered, o)
+                stream.synchronize()
+                same_bits = all(torch.equal(gathered[0], t) for t in gathered)
+                # partial outputs are rounded to bf16 before they are added (as the reference's all-reduce of bf16
+                # tensors does), the sum once more: (world + 1) roundings of 2^-9 relative to the largest term
+                tol = (world + 1) * 2.0 ** -9 * float(part.abs().max()) * world ** 0.5 + 2.0 ** -8 * float(ref.abs().max())
+                err = float((o.float() - ref).abs().max())
+                if not same_bits or not err <= tol:
+                    tp_check = f"FAILED at {p.name}: max err {err:.4g} (tolerance {tol:.4g}), identical bits on all ranks: {same_bits}"
+        flag = torch.tensor([1 if tp_check == "ok" else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0 and tp_check == "ok":
+            tp_check = "FAILED on another rank"
+
     with torch.cuda.stream(stream):
         step()  # first launch sets kernel attributes; must precede capture
         stream.synchronize()
@@ -505,8 +698,8 @@ def main():
 
         # ---- end to end: host buffers in, logits out, every step
         def e2e_step():
-            for k in ks:
-                x_dev[k].copy_(x_host[k], non_blocking=True)
+            for k in chain.ks:
+                chain.x_dev[k].copy_(chain.x_host[k], non_blocking=True)
             run_step()
             logits_host.view(-1)[: logits_all.numel()].copy_(logits_all.view(-1), non_blocking=True)
 
@@ -526,20 +719,22 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_ms = float(t.item())
         e2e_tok_s = 1000.0 * args.steps / e2e_ms
-        h2d = sum(v.numel() * v.element_size() for v in x_host.values())
+        h2d = sum(v.numel() * v.element_size() for v in chain.x_host.values())
         d2h = logits_host.numel() * logits_host.element_size()
 
         # ---- roofline of the dominant launch (largest share of the step's device time in the ncu launch list): the
         # ffn_gate + ffn_up GEMVs, one grouped launch per layer when grouping is on, timed alone over all layers'
-        # distinct weights (2 GB, far beyond L2)
+        # distinct weights (2 GB, far beyond L2). The launch order is re-registered for this loop (each layer's launch is
+        # followed by the next layer's) and put back afterwards.
         gate_idx = [i for i, p in enumerate(projs) if p.name in ("ffn_gate", "ffn_up")]
         gp = projs[gate_idx[0]]
         nl = min(model.layers, 32)
-        if not args.no_group and not tp and len(gate_idx) == 2:
+        if not args.no_group and len(gate_idx) == 2 and chain.groups:
             dom_kernel = "gemv_group_kernel<bf16, b=1> (ffn_gate + ffn_up, Q4_K)"
             dom_outs = [torch.empty(1, gp.n, dtype=torch.bfloat16, device="cuda") for _ in gate_idx]
-            dom_list = [(lambda li=li: ops.gemv_group([gp.dtype, gp.dtype], [layers[li][i] for i in gate_idx], x_dev[gp.k],
+            dom_list = [(lambda li=li: ops.gemv_group([gp.dtype, gp.dtype], [chain.layers[li][i] for i in gate_idx], chain.x_dev[gp.k],
                                                       [gp.n, gp.n], outs=dom_outs)) for li in range(nl)]
+            dom_seq = [(chain.layers[li][gate_idx[1]], chain.layers[li][gate_idx[0]], gp.dtype, gp.k, gp.n) for li in range(nl)]
             dom_bytes = 2 * gp.weight_bytes + gp.k * 2 + 2 * gp.n * 2
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape (ncu capture
             # summarised in profiles/gemv_group_q4k_gate_up.txt)
@@ -547,46 +742,69 @@ def main():
         else:
             dom_kernel = "gemv_staged_kernel<Q4_K, b=1, bf16>"
             dom_out = torch.empty(1, gp.n, dtype=torch.bfloat16, device="cuda")
-            dom_list = [(lambda w=layers[li][i]: ops.gemv(gp.dtype, w, x_dev[gp.k], gp.n, out=dom_out))
-                        for li in range(nl) for i in gate_idx[:1 if tp else 2]]
+            dom_w = [chain.layers[li][i] for li in range(nl) for i in gate_idx[:1 if tp else 2]]
+            dom_list = [(lambda w=w: ops.gemv(gp.dtype, w, chain.x_dev[gp.k], gp.n, out=dom_out)) for w in dom_w]
+            dom_seq = [(w, w, gp.dtype, gp.k, gp.n) for w in dom_w]
             dom_bytes = gp.weight_bytes + gp.k * 2 + gp.n * 2
             dom_traffic = NCU_TRAFFIC_GEMV_Q4K_4096_14336 if (gp.k, gp.n) == (4096, 14336) else None
+        if not args.no_prefetch:
+            register_launch_order(ops, dom_seq)
         dom_us = time_launch_list(torch, stream, dom_list, 10)
-        peak, peak_src = load_peaks()
+        if not args.no_prefetch:
+            register_launch_order(ops, chain.launch_sequence())
         achieved = dom_bytes / (dom_us * 1e-6) / 1e9
         clocks.__exit__(None, None, None)
 
+        extras = not tp and not args.quick and not args.shard_of
+
+        # ---- the element-wise-exact mode: the same chain with activations quantized to the CPU path's format (Q8_K /
+        # Q8_0) in the kernel prologue, one launch per projection (the grouped kernel quantizes to Q8_1 only)
+        cpu_format = None
+        if extras:
+            ops.clear_weight_successors()
+            exact = Chain(torch, pkg, ops, workloads, model, 1, 99, group=False, act_quant=1, weights_of=chain)
+            if not args.no_prefetch:
+                register_launch_order(ops, exact.launch_sequence())
+            ms_exact = time_chain(torch, stream, exact.step, max(3, args.steps // 4), 3)
+            cpu_format = {"value": 1000.0 / ms_exact, "unit": UNIT, "ms_per_step": ms_exact, "launches_per_step": exact.launches_per_step,
+                          "note": "act_quant=1: activations in the reference CPU path's Q8_K / Q8_0 format, element-wise within 1e-2 / 1e-3 of it"}
+            ops.clear_weight_successors()
+            if not args.no_prefetch:
+                register_launch_order(ops, chain.launch_sequence())
+
         prefill = None
-        if not tp:
+        if extras:
             prefill = []
-            bf16_peak = 1647.9
-            pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
-            if os.path.exists(pk):
-                bf16_peak = float(json.load(open(pk))["bf16_tflops"])
-            for dt, k, n in ((pkg.GgmlDType.Q4K, 4096, 4096), (pkg.GgmlDType.Q4K, 14336, 4096), (pkg.GgmlDType.Q6K, 14336, 4096)):
-                for m in (512, 2048, 8192):
+            gen = torch.Generator(device="cuda").manual_seed(76)
+            for dt in (pkg.GgmlDType.Q4K, pkg.GgmlDType.Q6K):
+                for (k, n) in workloads.SWEEP_SHAPES:
                     wq = random_blocks_device(torch, dt, n, k, gen)
-                    xm = torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16)
-                    ym = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
-                    for _ in range(3):
-                        ops.gemm(dt, wq, xm, n, out=ym)
-                    barrier()
-                    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    g0.record(stream)
-                    for _ in range(10):
-                        ops.gemm(dt, wq, xm, n, out=ym)
-                    g1.record(stream)
-                    barrier()
-                    us = g0.elapsed_time(g1) * 100.0
-                    tf = 2.0 * m * n * k / us / 1e6
-                    prefill.append({"type": dt.name, "k": k, "n": n, "m": m, "us": round(us, 1), "TFLOPs": round(tf, 1),
-                                    "frac_of_measured_bf16_peak": round(tf / bf16_peak, 3)})
-                    del wq, xm, ym
+                    for m in (512, 2048, 8192):
+                        xm = torch.randn(m, k, device="cuda", generator=gen).to(torch.bfloat16)
+                        ym = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+                        for _ in range(3):
+                            ops.gemm(dt, wq, xm, n, out=ym)
+                        barrier()
+                        reps = 10 if m * n * k < 2e12 else 4
+                        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        g0.record(stream)
+                        for _ in range(reps):
+                            ops.gemm(dt, wq, xm, n, out=ym)
+                        g1.record(stream)
+                        barrier()
+                        us = g0.elapsed_time(g1) * 1000.0 / reps
+                        tf = 2.0 * m * n * k / us / 1e6
+                        prefill.append({"type": dt.name, "k": k, "n": n, "m": m, "us": round(us, 1), "TFLOPs": round(tf, 1),
+                                        "frac_of_measured_bf16_peak": round(tf / bf16_peak, 3)})
+                        del xm, ym
+                    del wq
 
         small = None
-        if not tp:
+        if extras:
             # the decode sweep's batch 4 and 16 through the operator (QMatMul picks the kernel): weights-only GB/s
             small = []
+            gen = torch.Generator(device="cuda").manual_seed(77)
+            from inference_rs_b200 import qmatmul as _qm
             for dt, k, n in ((pkg.GgmlDType.Q4K, 4096, 6144), (pkg.GgmlDType.Q4K, 4096, 28672), (pkg.GgmlDType.Q4K, 14336, 4096),
                              (pkg.GgmlDType.Q6K, 14336, 4096), (pkg.GgmlDType.Q6K, 4096, 128256)):
                 wbytes = n * dt.row_bytes(k)
@@ -596,7 +814,6 @@ def main():
                     xb = torch.randn(b, k, device="cuda", generator=gen).to(torch.bfloat16)
                     qms[0].forward(xb)
                     us = time_launch_list(torch, stream, [(lambda q=q: q.forward(xb)) for q in qms], max(3, int(2e9 // (wbytes * copies))))
-                    from inference_rs_b200 import qmatmul as _qm
                     kern = ("gemv_tc" if _qm.prefers_tensor_core_rows(dt, b, n, k) else ("gemv" if b <= 8 else "gemm"))
                     small.append({"type": dt.name, "k": k, "n": n, "b": b, "kernel": kern, "us": round(us, 2),
                                   "GBps": round((wbytes + b * k * 2 + b * n * 2) / us / 1e3, 1),
@@ -606,11 +823,14 @@ def main():
         sweep = None
         if args.sweep:
             sweep = []
+            gen = torch.Generator(device="cuda").manual_seed(78)
             for dt in (pkg.GgmlDType.Q4K, pkg.GgmlDType.Q6K, pkg.GgmlDType.Q8_0):
                 for (k, n) in workloads.SWEEP_SHAPES:
                     wbytes = n * dt.row_bytes(k)
                     copies = max(2, min(8, int(600e6 // wbytes) + 1))
                     ws = [random_blocks_device(torch, dt, n, k, gen) for _ in range(copies)]
+                    if not args.no_prefetch:
+                        register_launch_order(ops, [(w, w, dt, k, n) for w in ws])
                     for b in (1, 4, 8):
                         xb = torch.randn(b, k, device="cuda", generator=gen).to(torch.bfloat16)
                         ob = torch.empty(b, n, dtype=torch.bfloat16, device="cuda")
@@ -621,24 +841,56 @@ def main():
                             continue
                         us = time_launch_list(torch, stream, [(lambda w=w: ops.gemv(dt, w, xb, n, out=ob)) for w in ws], iters)
                         sweep.append({"type": dt.name, "k": k, "n": n, "b": b, "us": round(us, 2),
-                                      "GBps": round((wbytes + b * k * 2 + b * n * 2) / us / 1e3, 1)})
+                                      "GBps": round((wbytes + b * k * 2 + b * n * 2) / us / 1e3, 1),
+                                      "frac_of_measured_hbm": round((wbytes + b * k * 2 + b * n * 2) / us / 1e3 / peak, 3)})
+                    for w in ws:
+                        ops.set_weight_successor(w, None)
                     del ws
+
+        ref_cuda = None
+        if extras:
+            try:
+                ref_cuda = reference_cuda_numbers(torch, pkg, chain, stream, peak, bf16_peak, args.steps)
+            except Exception as exc:
+                ref_cuda = {"unavailable": f"{type(exc).__name__}: {exc}"}
         status = pkg.kernel_library.device_status()
+
+    launches_per_step, bytes_per_step = chain.launches_per_step, chain.bytes_per_step
+
+    # ---- strong-scaling base for the tensor-parallel curve (one GPU only): the full 70B chain on this GPU and one rank's
+    # share of the 2- / 4- / 8-way split without any exchange (the compute-only floor of each N)
+    tp_base = None
+    if extras:
+        chain.free()
+        del chain
+        torch.cuda.empty_cache()
+        tp_base = []
+        for sh in (1, 2, 4, 8):
+            c70 = Chain(torch, pkg, ops, workloads, workloads.LLAMA3_70B, sh, 4321, group=True)
+            if not args.no_prefetch:
+                register_launch_order(ops, c70.launch_sequence())
+            ms70 = time_chain(torch, stream, c70.step, 10 if sh == 1 else 20, 3)
+            tp_base.append({"shard_of": sh, "ms_per_step": round(ms70, 4), "tok_per_s": round(1000.0 / ms70, 2),
+                            "GB_per_step": round(c70.bytes_per_step / 1e9, 3), "launches": c70.launches_per_step,
+                            "hbm_frac_of_measured": round(c70.bytes_per_step / (ms70 * 1e-3) / 1e9 / peak, 3)})
+            c70.free()
+            del c70
+            torch.cuda.empty_cache()
 
     line = {
         "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
         "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
-        "config": {"workload": (f"{model.name} Q4_K_M decode matmul chain, batch 1 ({model.layers * len(projs) + 1} GEMVs in {launches_per_step} launches, "
-                                f"{bytes_per_step / 1e9:.2f} GB of weights per token and GPU)"),
+        "config": {"workload": workload_name(model, world) if not args.shard_of else f"one rank's share of the {shards}-way split: " + workload_name(model, shards),
+                   "launches_per_step": launches_per_step,
+                   "weights_GB_per_token_and_gpu": round(bytes_per_step / 1e9, 3),
                    "l2": "inputs larger than L2: every step streams its GBs of distinct weights",
                    "parallelism": (f"tp{world}: column / row split, {allreduces_per_step} "
                                    f"{('peer-memory all-reduces fused into the row-parallel GEMVs (b200q_gemv_allreduce)' if not args.unfused_allreduce else 'peer-memory all-reduces (b200q_peer_allreduce)') if peer_ar is not None else 'NCCL all-reduces'} per token") if tp else "1 gpu",
                    "cuda_graph": graph is not None, "pdl": ops.get_option("pdl"),
+                   "l2_prefetch_bytes": 0 if args.no_prefetch else ops.get_option("l2_prefetch_bytes"),
                    "grouped_launches": not args.no_group},
         "weights_GBps_per_gpu": bytes_per_step * tok_s / 1e9,
-        "hbm_frac_of_measured": bytes_per_step * tok_s / 1e9 / peak,
-        "hbm_frac_of_nominal_8TBps": bytes_per_step * tok_s / 8e12,
         "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "kernel": dom_kernel, "shape": f"K={gp.k} N={gp.n}",
@@ -647,19 +899,28 @@ def main():
         "clocks": clocks.summary(),
         "device_status": list(status),
     }
+    line["hbm_frac_of_measured"] = line["weights_GBps_per_gpu"] / peak
+    line["hbm_frac_of_nominal_8TBps"] = line["weights_GBps_per_gpu"] / 8000.0
+    if tp_check is not None:
+        line["tp_check"] = tp_check
+    if cpu_format is not None:
+        line["cpu_format_activations"] = cpu_format
     if prefill is not None:
         line["prefill_gemm"] = prefill
     if small is not None:
         line["small_batch"] = small
     if sweep is not None:
         line["sweep"] = sweep
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        from oracle import kquants as kq
-        threads = kq.max_threads()
-        v, desc = cpu_chain_sample(model, threads)
-        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
+    if ref_cuda is not None:
+        line["reference_cuda"] = ref_cuda
+    if tp_base is not None:
+        line["tp_base"] = tp_base
+    if rank == 0 and not args.no_cpu_baseline:
+        v, desc = cpu_chain_sample(model, host_threads())
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": host_threads(), "kind": "port", "sample": desc}
     if rank == 0:
         print(json.dumps(line), flush=True)
+    failed = tp_check is not None and tp_check != "ok"
     if world > 1:
         # leave without tearing NCCL down: destroying a process group whose collectives were captured into a CUDA graph
         # can block at exit, and nothing is left to flush
@@ -667,7 +928,9 @@ def main():
         dist.barrier()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        os._exit(1 if failed else 0)
+    if failed:
+        raise SystemExit(1)
 
 
 if __name__ == "__main__":

@@ -96,7 +96,8 @@ const char* b200q_version(void);
 const char* b200q_last_error(void);
 
 /* Options: "pdl" (launch GEMVs and quantizers with programmatic stream serialization), "force_simple_gemv",
- * "gemv_stage_bytes". get also answers "sm_count" and "smem_optin". */
+ * "gemv_stage_bytes", "l2_prefetch_bytes" (see b200q_set_weight_successor; 0 switches the prefetch off). get also
+ * answers "sm_count" and "smem_optin". */
 int b200q_set_option(const char* name, int value);
 int b200q_get_option(const char* name, int* value);
 
@@ -122,6 +123,20 @@ int b200q_set_trace_buffer(void* dev, int records);
  * Host-side counterpart in the reference: fast_mmvq::plain (crates/inference-quant/src/gguf/fast_mmvq.rs:477-665). */
 int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
                int b_size, int act_quant, void* stream);
+
+/* Launch order hint, set once when a model is loaded: "the decode launch that follows the one on weight matrix `w`
+ * reads `next_w`" (GGUF type next_type, next_N rows of next_K values). Every decode GEMV launch on `w` - through part 1's
+ * launch_mmvq_gguf_*_plain symbols as well as b200q_gemv / b200q_gemv_group (keyed by the group's last matrix) - then
+ * has each CTA, once its last weight copy is issued, ask L2 (cp.async.bulk.prefetch.L2) for the first
+ * "l2_prefetch_bytes" (option, default 160 KB) of the row range the same CTA of the next launch will stream first, so
+ * that HBM keeps streaming through the tail of one launch and the gap before the next. A decoder's projections run in
+ * a fixed order, so the host registers the chain layer by layer; the hint only moves bytes into L2 early and never
+ * changes a result. next_w == NULL forgets `w`; b200q_clear_weight_successors forgets everything (call it before the
+ * weights are freed). The table is read-mostly: setting it while other threads launch is safe (a lock), but a launch
+ * racing with its own registration may or may not see it. No counterpart in the reference, whose launchers know
+ * nothing about the launch after them. */
+int b200q_set_weight_successor(const void* w, const void* next_w, int next_type, int next_K, int next_N);
+int b200q_clear_weight_successors(void);
 
 /* Grouped decode GEMV: nmat (1..4) weight matrices of GGUF types types[i] with N[i] rows and the same K, applied to the
  * same single activation row x [K] (element type `elem`) in ONE launch; output i goes to dsts[i] [N[i]] in x's type.

@@ -8,9 +8,9 @@
 #include "runtime.h"
 
 namespace b200q {
-int gemv_q4_k(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
-int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
-int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
+int gemv_q4_k(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
+int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
+int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
 void gemv_describe(int type, int K, int N, int b, int* out);
 int gemv_group(int elem, int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, const void* x,
                cudaStream_t s);
@@ -51,6 +51,9 @@ int b200q_set_option(const char* name, int value) {
         rt.tc_ksplit = value ? 1 : 0;
     } else if (!std::strcmp(name, "gemm_direct")) {
         rt.gemm_direct = value ? 1 : 0;
+    } else if (!std::strcmp(name, "l2_prefetch_bytes")) {
+        if (value < 0) return set_error(B200Q_ERR_INVALID, "l2_prefetch_bytes must be >= 0");
+        rt.l2_prefetch_bytes = value & ~15;
     } else if (!std::strcmp(name, "gemv_ctas_per_sm")) {
         if (value != 1 && value != 2) return set_error(B200Q_ERR_INVALID, "gemv_ctas_per_sm is 1 or 2");
         rt.gemv_ctas_per_sm = value;
@@ -68,6 +71,7 @@ int b200q_get_option(const char* name, int* value) {
     else if (!std::strcmp(name, "gemv_ctas_per_sm")) *value = rt.gemv_ctas_per_sm;
     else if (!std::strcmp(name, "gemm_direct")) *value = rt.gemm_direct;
     else if (!std::strcmp(name, "tc_ksplit")) *value = rt.tc_ksplit;
+    else if (!std::strcmp(name, "l2_prefetch_bytes")) *value = rt.l2_prefetch_bytes;
     else if (!std::strcmp(name, "sm_count")) *value = rt.sm_count;
     else if (!std::strcmp(name, "smem_optin")) *value = rt.smem_optin;
     else return set_error(B200Q_ERR_INVALID, "unknown option");
@@ -102,8 +106,8 @@ int b200q_set_trace_buffer(void* dev, int records) {
 // First non-zero status a void launcher produced since the last call (then cleared).
 int b200q_take_launch_status(void) { return take_launch_status(); }
 
-int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
-               int b_size, int act_quant, void* stream) {
+static int gemv_one_launch(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
+                           int b_size, int act_quant, const PeerExchange* px, void* stream) {
     if (act_quant != 0 && act_quant != 1) return set_error(B200Q_ERR_INVALID, "act_quant is 0 (Q8_1) or 1 (CPU path's format)");
     const int mode = act_quant == 0 ? 1 : 2;  // ACT_RAW_Q8_1 / ACT_RAW_CPU
     if (!w || !x || !dst) return set_error(B200Q_ERR_INVALID, "null pointer");
@@ -111,14 +115,39 @@ int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int 
     if (K <= 0 || K % type_block_elems(type) != 0) return set_error(B200Q_ERR_INVALID, "K is not a multiple of the block size");
     int rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (type == TYPE_Q4_K) rc = gemv_q4_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, mode, s);
-    else if (type == TYPE_Q6_K) rc = gemv_q6_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, mode, s);
-    else if (type == TYPE_Q8_0) rc = gemv_q8_0(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, mode, s);
+    if (type == TYPE_Q4_K) rc = gemv_q4_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, mode, px, s);
+    else if (type == TYPE_Q6_K) rc = gemv_q6_k(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, mode, px, s);
+    else if (type == TYPE_Q8_0) rc = gemv_q8_0(elem, w, x, dst, K, N, stride_x, stride_dst, b_size, mode, px, s);
     else return set_error(B200Q_ERR_UNSUPPORTED, "weight type is not Q8_0, Q4_K or Q6_K");
     take_launch_status();
     if (rc == B200Q_ERR_UNSUPPORTED)
         return set_error(rc, "no one-launch GEMV for this shape or alignment: quantize to Q8_1 and use launch_mmvq_gguf_*_plain");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemv failed");
+    return B200Q_OK;
+}
+
+int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int stride_x, int stride_dst,
+               int b_size, int act_quant, void* stream) {
+    return gemv_one_launch(type, elem, w, x, dst, K, N, stride_x, stride_dst, b_size, act_quant, nullptr, stream);
+}
+
+// "The launch after the one on `w` reads `next_w`" (a matrix of GGUF type next_type with next_N rows of next_K values);
+// next_w == NULL forgets w. Read by every decode GEMV launch on w from then on.
+int b200q_set_weight_successor(const void* w, const void* next_w, int next_type, int next_K, int next_N) {
+    if (!w) return set_error(B200Q_ERR_INVALID, "null pointer");
+    if (next_w == nullptr) {
+        set_weight_successor(w, nullptr);
+        return B200Q_OK;
+    }
+    if (type_block_bytes(next_type) == 0 || next_K <= 0 || next_N <= 0 || next_K % type_block_elems(next_type) != 0)
+        return set_error(B200Q_ERR_INVALID, "b200q_set_weight_successor: bad type or shape of the successor");
+    const WeightSuccessor succ{next_w, next_type, next_K, next_N};
+    set_weight_successor(w, &succ);
+    return B200Q_OK;
+}
+
+int b200q_clear_weight_successors(void) {
+    clear_weight_successors();
     return B200Q_OK;
 }
 
@@ -194,10 +223,7 @@ int b200q_gemv_allreduce(int type, int elem, const void* w, const void* x, void*
     PeerExchange px{};
     if (fill_peer_exchange(px, bufs, rank, world, capacity) != 0)
         return set_error(B200Q_ERR_INVALID, "b200q_gemv_allreduce: 1..8 ranks, 16-byte aligned buffers, capacity a multiple of 16");
-    set_pending_peer_exchange(world > 1 ? &px : nullptr);
-    const int rc = b200q_gemv(type, elem, w, x, dst, K, N, K, N, b_size, 0, stream);
-    set_pending_peer_exchange(nullptr);
-    return rc;
+    return gemv_one_launch(type, elem, w, x, dst, K, N, K, N, b_size, 0, world > 1 ? &px : nullptr, stream);
 }
 
 // out[10] = {staged, grid, smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,

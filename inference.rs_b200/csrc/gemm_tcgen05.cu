@@ -757,12 +757,10 @@ static int launch_gemm_staged_mt(const CUtensorMap& map, const GemmParams& p, cu
     constexpr int RAW_STRIDE = ((GEMM_BN * RawChunk<TYPE>::PITCH + 64) + 127) & ~127;
     const size_t smem = 1024 + (size_t)GEMM2_STAGES * (MT * GEMM_A_BYTES + GEMM_B_BYTES) + (size_t)GEMM2_RAW_STAGES * RAW_STRIDE +
                         sizeof(Gemm2Barriers);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static PerDeviceOnce configured;  // per instantiation and device
+    const cudaError_t attr_err =
+        configured.run([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
+    if (attr_err != cudaSuccess) return (int)attr_err;
     const int ntiles = ((p.N + GEMM_BN - 1) / GEMM_BN) * ((p.M + MT * GEMM_BM - 1) / (MT * GEMM_BM));
     const int sms = runtime_info().sm_count;
     kernel<<<ntiles < sms ? ntiles : sms, gemm2_threads<MT>(), smem, s>>>(map, p);
@@ -773,12 +771,10 @@ template <int TYPE, typename T, int MT>
 static int launch_gemm_mt(const CUtensorMap& map, const GemmParams& p, cudaStream_t s) {
     auto kernel = gemm_tcgen05_kernel<TYPE, T, MT>;
     const size_t smem = 1024 + (size_t)GEMM_STAGES * (MT * GEMM_A_BYTES + GEMM_B_BYTES) + sizeof(GemmBarriers);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static PerDeviceOnce configured;  // per instantiation and device
+    const cudaError_t attr_err =
+        configured.run([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
+    if (attr_err != cudaSuccess) return (int)attr_err;
     dim3 grid((unsigned)((p.N + GEMM_BN - 1) / GEMM_BN), (unsigned)((p.M + MT * GEMM_BM - 1) / (MT * GEMM_BM)), 1);
     kernel<<<grid, GEMM_THREADS, smem, s>>>(map, p);
     return (int)cudaGetLastError();

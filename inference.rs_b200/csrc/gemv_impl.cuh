@@ -35,6 +35,37 @@ constexpr int ACT_REC_BYTES = 80;  // i8 q[64]; f32 d[2]; f32 ds[2]
 
 enum ActMode : int { ACT_Q8_1 = 0, ACT_RAW_Q8_1 = 1, ACT_RAW_CPU = 2 };
 
+// The matrix the next launch on the stream will read (runtime.h: WeightSuccessor), cut the way that launch will cut
+// it: CTA c of that launch owns units [c * q + min(c, r), ...) of unit_bytes each. Each CTA of THIS launch asks L2 for
+// the first `bytes` of the range CTA c of the next launch will stream first. w == nullptr: nothing registered.
+struct NextPrefetch {
+    const uint8_t* w;
+    long long total_bytes;  // size of the successor's packed rows, rounded down to 16
+    int unit_bytes, units_per_cta, units_extra, grid;
+    int bytes;              // per CTA, multiple of 16
+};
+
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
+}
+
+// Called by the producer thread once its last weight copy is on its way: the requests queue behind this CTA's own
+// copies, so they run as those drain - through the tail of this grid and the launch gap after it.
+__device__ __forceinline__ void prefetch_successor(const NextPrefetch& n, int cta) {
+    if (n.w == nullptr || cta >= n.grid) return;
+    const long long unit0 = (long long)cta * n.units_per_cta + min(cta, n.units_extra);
+    const long long units = n.units_per_cta + (cta < n.units_extra ? 1 : 0);
+    const long long off = unit0 * n.unit_bytes;
+    long long len = units * n.unit_bytes;
+    if (off + len > n.total_bytes) len = n.total_bytes - off;
+    if (len > n.bytes) len = n.bytes;
+    len &= ~15LL;
+    for (long long o = 0; o < len; o += 16384) {
+        const long long chunk = len - o < 16384 ? len - o : 16384;
+        bulk_prefetch_l2(n.w + off + o, (uint32_t)chunk);
+    }
+}
+
 struct GemvParams {
     const uint8_t* w;   // packed weights, row-major blocks, 16-byte aligned, >= 16 readable bytes after the end
     const void* act;    // Q8_1 blocks [B][stride_act] (ACT_Q8_1) or raw rows [B][stride_act elements]
@@ -57,6 +88,7 @@ struct GemvParams {
     unsigned int* status;  // device status word
     unsigned long long* trace;  // optional: 8 timestamps (ns) written by the first and the last CTA, or nullptr
     PeerExchange px;     // px.world > 1: the last CTA to finish sums dst over the ranks in place (row-parallel matmul)
+    NextPrefetch next;   // the registered successor matrix, or w == nullptr
 };
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -584,6 +616,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
             mbar_arrive_expect_tx(&full[issued], bytes);
             bulk_copy_g2s(ring + (size_t)issued * p.stage_bytes, p.w + (size_t)r * p.row_bytes, bytes, &full[issued]);
         }
+        if (issued >= niter) prefetch_successor(p.next, cta);  // everything of this CTA is already on its way
     }
     for (int i = tid; i < counter_ints; i += GEMV_THREADS) counters[i] = 0;
     __syncthreads();
@@ -603,6 +636,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                 mbar_arrive_expect_tx(&full[s], bytes);
                 bulk_copy_g2s(ring + (size_t)s * p.stage_bytes, p.w + (size_t)r * p.row_bytes, bytes, &full[s]);
                 issued = it + 1;
+                if (issued == niter) prefetch_successor(p.next, cta);
             }
             if (!ok) {
                 // a consumer may have left; wait (bounded) until every copy already issued has landed so that no
@@ -790,6 +824,7 @@ struct GemvGroupParams {
     int nstages, stage_bytes, act_bytes, max_rows_per_stage;
     int use_pdl, act_vec;
     unsigned int* status;
+    NextPrefetch next;
 };
 
 // rows [row0, row1) of matrix m that CTA `cta` owns
@@ -914,6 +949,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
                     bulk_copy_g2s(ring + (size_t)s * p.stage_bytes, p.w[m] + (size_t)r * p.row_bytes[m], bytes, &full[s]);
                 }
             }
+            if (ok) prefetch_successor(p.next, cta);
             if (!ok) {
                 for (int q = max(0, g - S); q < g; ++q)
                     if (!mbar_wait_bounded(&full[q % S], (q / S) & 1)) {
@@ -1164,6 +1200,9 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     return plan;
 }
 
+// The successor registered for weight matrix `w`, cut as its own launch will cut it (see NextPrefetch).
+static inline NextPrefetch plan_next_prefetch(const void* w);
+
 template <typename Kern>
 static inline cudaError_t launch_gemv_kernel(Kern kernel, int grid, int block, size_t smem, cudaStream_t s, bool pdl,
                                              const GemvParams& p) {
@@ -1180,16 +1219,32 @@ static inline cudaError_t launch_gemv_kernel(Kern kernel, int grid, int block, s
     return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
+static inline NextPrefetch plan_next_prefetch(const void* w) {
+    NextPrefetch n{};
+    const RuntimeInfo& rt = runtime_info();
+    WeightSuccessor succ;
+    if (rt.l2_prefetch_bytes < 16 || !find_weight_successor(w, &succ)) return n;
+    if (type_block_bytes(succ.type) == 0 || succ.K <= 0 || succ.N <= 0 || succ.K % type_block_elems(succ.type) != 0) return n;
+    const GemvPlan next = plan_gemv(succ.type, succ.K, succ.N, 1, succ.w);
+    if (!next.staged) return n;
+    n.w = static_cast<const uint8_t*>(succ.w);
+    n.total_bytes = ((long long)succ.N * next.p.row_bytes) & ~15LL;
+    n.unit_bytes = next.p.row_align * next.p.row_bytes;
+    n.units_per_cta = next.p.units_per_cta;
+    n.units_extra = next.p.units_extra;
+    n.grid = next.grid;
+    n.bytes = rt.l2_prefetch_bytes & ~15;
+    return n;
+}
+
 template <int TYPE, int B, typename dst_t, int ACT, typename act_t, int NREG, bool AR>
 static inline int launch_staged_ar(const GemvPlan& plan, cudaStream_t s) {
     auto kernel = gemv_staged_kernel<TYPE, B, dst_t, ACT, act_t, NREG, AR>;
-    static bool configured = false;  // per instantiation; the attribute is set on the first launch
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             runtime_info().smem_optin - 1024);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static PerDeviceOnce configured;  // per instantiation
+    cudaError_t e = configured.run([&] {
+        return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, runtime_info().smem_optin - 1024);
+    });
+    if (e != cudaSuccess) return (int)e;
     return (int)launch_gemv_kernel(kernel, plan.grid, GEMV_THREADS, plan.smem, s, plan.p.use_pdl != 0, plan.p);
 }
 
@@ -1212,7 +1267,7 @@ static inline int launch_staged(const GemvPlan& plan, cudaStream_t s) {
 
 template <int TYPE, int B, typename dst_t>
 static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int K, int N, int stride_act, int stride_dst,
-                                int act_mode, cudaStream_t s) {
+                                int act_mode, const PeerExchange* px, cudaStream_t s) {
     GemvPlan plan = plan_gemv(TYPE, K, N, B, vx);
     plan.p.w = (const uint8_t*)vx;
     plan.p.act = act;
@@ -1222,7 +1277,8 @@ static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int 
     plan.p.status = status_ptr();
     plan.p.trace = trace_slot();
     plan.p.px.world = 0;
-    if (const PeerExchange* px = take_pending_peer_exchange()) {
+    plan.p.next = plan_next_prefetch(vx);
+    if (px != nullptr && px->world > 1) {
         // fused all-reduce: the staged kernel only, contiguous [B][N] output of whole 16-byte units within the capacity
         const long long bytes = (long long)B * N * (long long)sizeof(dst_t);
         if (!plan.staged || stride_dst != N || bytes % 16 != 0 || bytes > px->capacity || reinterpret_cast<uintptr_t>(dst) % 16 != 0)
@@ -1245,17 +1301,17 @@ static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int 
 
 template <int TYPE, typename dst_t>
 static inline int launch_gemv(const void* vx, const void* act, void* dst, int K, int N, int stride_act, int stride_dst,
-                              int b, int act_mode, cudaStream_t s) {
+                              int b, int act_mode, const PeerExchange* px, cudaStream_t s) {
     if (N <= 0 || K <= 0) return 0;
     switch (b) {
-        case 1: return launch_gemv_b<TYPE, 1, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, s);
-        case 2: return launch_gemv_b<TYPE, 2, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, s);
-        case 3: return launch_gemv_b<TYPE, 3, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, s);
-        case 4: return launch_gemv_b<TYPE, 4, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, s);
-        case 5: return launch_gemv_b<TYPE, 5, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, s);
-        case 6: return launch_gemv_b<TYPE, 6, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, s);
-        case 7: return launch_gemv_b<TYPE, 7, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, s);
-        case 8: return launch_gemv_b<TYPE, 8, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, s);
+        case 1: return launch_gemv_b<TYPE, 1, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, px, s);
+        case 2: return launch_gemv_b<TYPE, 2, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, px, s);
+        case 3: return launch_gemv_b<TYPE, 3, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, px, s);
+        case 4: return launch_gemv_b<TYPE, 4, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, px, s);
+        case 5: return launch_gemv_b<TYPE, 5, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, px, s);
+        case 6: return launch_gemv_b<TYPE, 6, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, px, s);
+        case 7: return launch_gemv_b<TYPE, 7, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, px, s);
+        case 8: return launch_gemv_b<TYPE, 8, dst_t>(vx, act, dst, K, N, stride_act, stride_dst, act_mode, px, s);
         default: return B200Q_ERR_UNSUPPORTED;
     }
 }
@@ -1275,6 +1331,7 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
     p.act_vec = (reinterpret_cast<uintptr_t>(x) % 16 == 0);
     p.use_pdl = rt.use_pdl;
     p.status = status_ptr();
+    p.next = plan_next_prefetch(ws[nmat - 1]);
     int grid = rt.sm_count, max_stage = 0, max_R = 0, wpr = 0, ipl = 0;
     for (int m = 0; m < nmat; ++m) {
         if (type_block_bytes(types[m]) == 0 || K % type_block_elems(types[m]) != 0) return B200Q_ERR_UNSUPPORTED;
@@ -1338,10 +1395,10 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
 // One weight type's dispatcher over the output element type; defined once per type in gemv_<type>.cu.
 template <int TYPE>
 static inline int gemv_type_dispatch(int dst_elem, const void* vx, const void* act, void* dst, int K, int N, int stride_act,
-                                     int stride_dst, int b, int act_mode, cudaStream_t s) {
-    if (dst_elem == ELEM_BF16) return launch_gemv<TYPE, __nv_bfloat16>(vx, act, dst, K, N, stride_act, stride_dst, b, act_mode, s);
-    if (dst_elem == ELEM_F16) return launch_gemv<TYPE, __half>(vx, act, dst, K, N, stride_act, stride_dst, b, act_mode, s);
-    if (dst_elem == ELEM_F32) return launch_gemv<TYPE, float>(vx, act, dst, K, N, stride_act, stride_dst, b, act_mode, s);
+                                     int stride_dst, int b, int act_mode, const PeerExchange* px, cudaStream_t s) {
+    if (dst_elem == ELEM_BF16) return launch_gemv<TYPE, __nv_bfloat16>(vx, act, dst, K, N, stride_act, stride_dst, b, act_mode, px, s);
+    if (dst_elem == ELEM_F16) return launch_gemv<TYPE, __half>(vx, act, dst, K, N, stride_act, stride_dst, b, act_mode, px, s);
+    if (dst_elem == ELEM_F32) return launch_gemv<TYPE, float>(vx, act, dst, K, N, stride_act, stride_dst, b, act_mode, px, s);
     return B200Q_ERR_UNSUPPORTED;
 }
 
@@ -1353,26 +1410,26 @@ static inline int gemv_type_dispatch(int dst_elem, const void* vx, const void* a
 #define B200Q_DEFINE_GEMV_TYPE(tag, TYPE)                                                                              \
     namespace b200q {                                                                                                  \
     int gemv_##tag(int dst_elem, const void* vx, const void* act, void* dst, int K, int N, int stride_act,             \
-                   int stride_dst, int b, int act_mode, cudaStream_t s) {                                              \
+                   int stride_dst, int b, int act_mode, const PeerExchange* px, cudaStream_t s) {                      \
         return note_launch_status(                                                                                     \
-            gemv_type_dispatch<TYPE>(dst_elem, vx, act, dst, K, N, stride_act, stride_dst, b, act_mode, s));           \
+            gemv_type_dispatch<TYPE>(dst_elem, vx, act, dst, K, N, stride_act, stride_dst, b, act_mode, px, s));       \
     }                                                                                                                  \
     }                                                                                                                  \
     extern "C" void launch_mmvq_gguf_##tag##_bf16_plain(const void* vx, const void* vy, void* dst, int ncols_x,        \
                                                         int nrows_x, int stride_col_y, int stride_col_dst, int b_size, \
                                                         void* stream) {                                                \
         b200q::gemv_##tag(b200q::ELEM_BF16, vx, vy, dst, ncols_x, nrows_x, stride_col_y, stride_col_dst, b_size,       \
-                          b200q::ACT_Q8_1, (cudaStream_t)stream);                                                      \
+                          b200q::ACT_Q8_1, nullptr, (cudaStream_t)stream);                                                      \
     }                                                                                                                  \
     extern "C" void launch_mmvq_gguf_##tag##_f16_plain(const void* vx, const void* vy, void* dst, int ncols_x,         \
                                                        int nrows_x, int stride_col_y, int stride_col_dst, int b_size,  \
                                                        void* stream) {                                                 \
         b200q::gemv_##tag(b200q::ELEM_F16, vx, vy, dst, ncols_x, nrows_x, stride_col_y, stride_col_dst, b_size,        \
-                          b200q::ACT_Q8_1, (cudaStream_t)stream);                                                      \
+                          b200q::ACT_Q8_1, nullptr, (cudaStream_t)stream);                                                      \
     }                                                                                                                  \
     extern "C" void launch_mmvq_gguf_##tag##_f32_plain(const void* vx, const void* vy, void* dst, int ncols_x,         \
                                                        int nrows_x, int stride_col_y, int stride_col_dst, int b_size,  \
                                                        void* stream) {                                                 \
         b200q::gemv_##tag(b200q::ELEM_F32, vx, vy, dst, ncols_x, nrows_x, stride_col_y, stride_col_dst, b_size,        \
-                          b200q::ACT_Q8_1, (cudaStream_t)stream);                                                      \
+                          b200q::ACT_Q8_1, nullptr, (cudaStream_t)stream);                                                      \
     }

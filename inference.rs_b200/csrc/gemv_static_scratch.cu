@@ -19,9 +19,10 @@ void launch_mmvq_gguf_quantize_q8_1_f32(const void*, void*, int, int, int, void*
 }
 
 namespace b200q {
-int gemv_q4_k(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
-int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
-int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int, cudaStream_t);
+struct PeerExchange;
+int gemv_q4_k(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
+int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
+int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
 int set_error(int code, const char* msg);
 
 // Largest problem the fixed scratch holds: 8 activation rows of 32768 values (padded), 36 bytes per 32 values.
@@ -81,9 +82,9 @@ extern "C" int b200q_gemv_static_scratch(int type, int elem, const void* w, cons
     if (e != cudaSuccess) return set_error((int)e, cudaGetErrorString(e));
     int rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (type == TYPE_Q4_K) rc = gemv_q4_k(elem, w, scratch, dst, K, N, k_padded / 32, stride_dst, b_size, 0, s);
-    else if (type == TYPE_Q6_K) rc = gemv_q6_k(elem, w, scratch, dst, K, N, k_padded / 32, stride_dst, b_size, 0, s);
-    else rc = gemv_q8_0(elem, w, scratch, dst, K, N, k_padded / 32, stride_dst, b_size, 0, s);
+    if (type == TYPE_Q4_K) rc = gemv_q4_k(elem, w, scratch, dst, K, N, k_padded / 32, stride_dst, b_size, 0, nullptr, s);
+    else if (type == TYPE_Q6_K) rc = gemv_q6_k(elem, w, scratch, dst, K, N, k_padded / 32, stride_dst, b_size, 0, nullptr, s);
+    else rc = gemv_q8_0(elem, w, scratch, dst, K, N, k_padded / 32, stride_dst, b_size, 0, nullptr, s);
     take_launch_status();
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemv failed");
     return B200Q_OK;

@@ -706,12 +706,10 @@ template <int TYPE, typename T, int TOK>
 static int launch_gemv_tc_i8_tok(const CUtensorMap& map_w, const CUtensorMap& map_x, const TcqParams& p, int grid, int smem_bytes,
                                  cudaStream_t s) {
     auto kernel = gemv_tc_i8_kernel<TYPE, T, TOK>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TCQ_SMEM_LIMIT);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static PerDeviceOnce configured;  // per instantiation and device
+    const cudaError_t attr_err =
+        configured.run([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TCQ_SMEM_LIMIT); });
+    if (attr_err != cudaSuccess) return (int)attr_err;
     kernel<<<grid, TCQ_THREADS, smem_bytes, s>>>(map_w, map_x, p);
     return (int)cudaGetLastError();
 }

@@ -3,12 +3,15 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <mutex>
+#include <shared_mutex>
+#include <unordered_map>
 
 namespace b200q {
 
 __device__ unsigned int g_status_word[4] = {0, 0, 0, 0};
 
-static RuntimeInfo g_rt = {0, 0, 0, 0, 0, 40 * 1024, 0, 1, 1};
+static RuntimeInfo g_rt = {0, 0, 0, 0, 0, 40 * 1024, 0, 1, 1, 160 * 1024};
 static std::atomic<int> g_launch_status{0};
 
 static void query_device() {
@@ -30,6 +33,7 @@ static void query_device() {
         int v = std::atoi(e);
         if (v >= 1024) g_rt.gemv_stage_target = v;
     }
+    if (const char* e = std::getenv("B200Q_L2_PREFETCH_BYTES")) g_rt.l2_prefetch_bytes = std::atoi(e) & ~15;
 }
 
 RuntimeInfo& runtime_info_mut() {
@@ -61,13 +65,6 @@ void set_trace_buffer(unsigned long long* dev, int records) {
     g_trace_records = records;
     g_trace_next = 0;
 }
-static thread_local const PeerExchange* t_pending_px = nullptr;
-void set_pending_peer_exchange(const PeerExchange* px) { t_pending_px = px; }
-const PeerExchange* take_pending_peer_exchange() {
-    const PeerExchange* px = t_pending_px;
-    t_pending_px = nullptr;
-    return px;
-}
 
 unsigned long long* trace_buffer(int* slots) {
     *slots = g_trace ? g_trace_records * 16 : 0;
@@ -77,6 +74,26 @@ unsigned long long* trace_slot() {
     if (g_trace == nullptr || g_trace_records <= 0) return nullptr;
     const int i = g_trace_next.fetch_add(1) % g_trace_records;
     return g_trace + (size_t)i * 16;
+}
+
+static std::shared_mutex g_succ_mutex;
+static std::unordered_map<const void*, WeightSuccessor> g_successors;
+void set_weight_successor(const void* w, const WeightSuccessor* next) {
+    std::unique_lock<std::shared_mutex> lock(g_succ_mutex);
+    if (next == nullptr || next->w == nullptr) g_successors.erase(w);
+    else g_successors[w] = *next;
+}
+void clear_weight_successors() {
+    std::unique_lock<std::shared_mutex> lock(g_succ_mutex);
+    g_successors.clear();
+}
+bool find_weight_successor(const void* w, WeightSuccessor* out) {
+    std::shared_lock<std::shared_mutex> lock(g_succ_mutex);
+    if (g_successors.empty()) return false;
+    auto it = g_successors.find(w);
+    if (it == g_successors.end()) return false;
+    *out = it->second;
+    return true;
 }
 
 int note_launch_status(int status) {

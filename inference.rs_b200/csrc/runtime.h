@@ -23,7 +23,20 @@ struct RuntimeInfo {
     int gemm_direct;       // 1: the GEMM reads packed weights straight from global memory (no shared-memory staging)
     int gemv_ctas_per_sm;  // CTAs of one GEMV grid per SM: 2, or 1 to leave the other slot to the next grid
     int tc_ksplit;         // small-batch tensor-core kernel: split K over CTAs for matrices with few rows (1, testing: 0)
+    int l2_prefetch_bytes; // decode GEMV: bytes of the registered successor matrix each CTA asks L2 to fetch (0 = off)
 };
+
+// "After a launch on weight matrix w, the next launch on this stream will read matrix next_w": registered once by the
+// host when it loads a model (the order of a decoder's projections is static), read by every GEMV launch. A CTA that
+// has issued its last weight copy asks L2 for the first bytes of its own row range of the successor, so HBM keeps
+// streaming through the tail of this launch and the gap before the next one.
+struct WeightSuccessor {
+    const void* w;
+    int type, K, N;
+};
+void set_weight_successor(const void* w, const WeightSuccessor* next);  // next == nullptr: forget w
+void clear_weight_successors();
+bool find_weight_successor(const void* w, WeightSuccessor* out);
 
 const RuntimeInfo& runtime_info();
 RuntimeInfo& runtime_info_mut();
@@ -33,11 +46,24 @@ void set_trace_buffer(unsigned long long* dev, int records);
 unsigned long long* trace_slot();
 unsigned long long* trace_buffer(int* slots);
 
-// The exchange buffers a fused matmul + all-reduce call hands to the next GEMV launch of this host thread (the launch
-// takes and clears it); nullptr otherwise.
-struct PeerExchange;
-void set_pending_peer_exchange(const PeerExchange* px);
-const PeerExchange* take_pending_peer_exchange();  // the whole buffer (16 slots per record), or nullptr
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (function, device) pair: launchers set it once per device
+// and kernel instantiation, on the first launch there (one static PerDeviceOnce per instantiation).
+struct PerDeviceOnce {
+    bool done[64] = {};
+    template <typename Fn> cudaError_t run(Fn&& fn) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= 64) return fn();
+        if (!done[dev]) {
+            e = fn();
+            if (e != cudaSuccess) return e;
+            done[dev] = true;
+        }
+        return cudaSuccess;
+    }
+};
+
 int note_launch_status(int status);  // remembers the first non-zero status; returns its argument
 int take_launch_status();            // returns and clears it
 

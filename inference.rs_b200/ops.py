@@ -149,6 +149,21 @@ def gemv_tc(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: tor
     return y
 
 
+def set_weight_successor(w: torch.Tensor, next_w: torch.Tensor | None, next_dtype: GgmlDType | None = None, next_k: int = 0,
+                         next_n: int = 0) -> None:
+    """`b200q_set_weight_successor`: the decode launch after the one on `w` will read `next_w` [next_n, next_k]; every
+    GEMV launch on `w` then prefetches the start of `next_w` into L2. ``next_w=None`` forgets `w`."""
+    if next_w is None:
+        kl.check(kl.library().b200q_set_weight_successor(w.data_ptr(), None, 0, 0, 0), "b200q_set_weight_successor")
+    else:
+        kl.check(kl.library().b200q_set_weight_successor(w.data_ptr(), next_w.data_ptr(), int(next_dtype), next_k, next_n),
+                 "b200q_set_weight_successor")
+
+
+def clear_weight_successors() -> None:
+    kl.check(kl.library().b200q_clear_weight_successors(), "b200q_clear_weight_successors")
+
+
 def gemv_plan(dtype: GgmlDType, k: int, n: int, b: int) -> dict:
     out = (C.c_int * 10)()
     kl.check(kl.library().b200q_gemv_plan(int(dtype), k, n, b, C.byref(out)), "b200q_gemv_plan")
