@@ -62,6 +62,15 @@ void launch_mmvq_gguf_q6_k_f16_plain(const void* vx, const void* vy, void* dst, 
 void launch_mmvq_gguf_q6_k_f32_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
                                      int stride_col_y, int stride_col_dst, int b_size, void* stream);
 
+/* Q8_0 weights against UNQUANTIZED activations, f32 accumulation: dst[j * nrows_x + row] = sum_k W[row][k] * y[j][k],
+ * y [b_size][ncols_x] contiguous rows and dst [b_size][nrows_x], both of the suffix's type; b_size 1..8 (larger values
+ * are treated as 8, as the reference's launcher does).
+ * Replaces crates/inference-quant/src/gguf/ffi.rs:1004-1021 (kernels/cuda/mmvq_gguf/mmvq_instance_q8_0.cu:14-140). */
+void launch_mmvq_gguf_q8_0_bf16_exact(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x, int b_size,
+                                      void* stream);
+void launch_mmvq_gguf_q8_0_f32_exact(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x, int b_size,
+                                     void* stream);
+
 /* Prefill activation quantizer: rows -> 144-byte blocks of 128 values, block index (k / 128) * ne1 + row.
  * D4 stores four f32 scales, DS4 four half2 (d, sum(x)). type_x: 0 = f32, 1 = f16, 30 = bf16. ne00 = row length,
  * s01 = row stride in elements, ne0 = padded row length (multiple of 128), ne1 = rows; only ne2 = ne3 = 1.
@@ -108,9 +117,11 @@ int b200q_reset_device_status(void);
 /* First non-zero status a void launcher of part 1 produced since the last call, then cleared. */
 int b200q_take_launch_status(void);
 
-/* Diagnostics. `dev` is device memory for records * 16 uint64; every following GEMV launch takes the next record
- * (wrapping) and its first / last CTA write %globaltimer nanoseconds {start, barriers ready, activations staged,
- * first stage landed, done} into slots [0..4] / [8..12]. records = 0 switches it off. */
+/* Diagnostics. `dev` is device memory for records * 32 uint64; every following GEMV launch takes the next record
+ * (wrapping) and its first / last CTA write %globaltimer nanoseconds into slots [0..15] / [16..31]: 0 start,
+ * 1 barriers ready, 2 activations staged, 3 first stage landed, 4 done, 5 first weight copy issued, 6 activations
+ * quantized, 7 activations in registers, 8 barriers initialised, 9 initial copies issued, 10 activation loads back,
+ * 11 first stage consumed. records = 0 switches it off. */
 int b200q_set_trace_buffer(void* dev, int records);
 
 /* One-launch decode GEMV on unquantized activations: x [b_size][stride_x] and dst [b_size][stride_dst] both of

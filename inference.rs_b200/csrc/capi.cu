@@ -95,9 +95,8 @@ int b200q_reset_device_status(void) {
     return B200Q_OK;
 }
 
-// Diagnostics: `dev` points at records * 16 u64 of device memory; every following GEMV launch takes the next record
-// and its first / last CTA write nanosecond timestamps {start, barriers ready, activations staged, first stage
-// landed, done} at [0..4] / [8..12]. records = 0 switches tracing off.
+// Diagnostics: `dev` points at records * 32 u64; every following GEMV launch takes the next record and its first / last CTA
+// write nanosecond timestamps into slots [0..15] / [16..31] (slot meanings: include/inferencequant_b200.h). records = 0: off.
 int b200q_set_trace_buffer(void* dev, int records) {
     set_trace_buffer(static_cast<unsigned long long*>(dev), dev ? records : 0);
     return B200Q_OK;

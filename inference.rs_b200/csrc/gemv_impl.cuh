@@ -86,7 +86,7 @@ struct GemvParams {
     int use_pdl;
     int act_vec;         // raw activations: rows are 16-byte aligned
     unsigned int* status;  // device status word
-    unsigned long long* trace;  // optional: 8 timestamps (ns) written by the first and the last CTA, or nullptr
+    unsigned long long* trace;  // optional: 16 timestamps (ns) written by the first and by the last CTA, or nullptr
     PeerExchange px;     // px.world > 1: the last CTA to finish sums dst over the ranks in place (row-parallel matmul)
     NextPrefetch next;   // the registered successor matrix, or w == nullptr
 };
@@ -96,10 +96,15 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+#define GEMV_TRACE_ANY(slot)                                                                               \
+    do {                                                                                                   \
+        if (p.trace != nullptr && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))                        \
+            p.trace[(blockIdx.x == 0 ? 0 : 16) + (slot)] = global_timer_ns();                              \
+    } while (0)
 #define GEMV_TRACE(slot)                                                                                   \
     do {                                                                                                   \
         if (p.trace != nullptr && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))            \
-            p.trace[(blockIdx.x == 0 ? 0 : 8) + (slot)] = global_timer_ns();                               \
+            p.trace[(blockIdx.x == 0 ? 0 : 16) + (slot)] = global_timer_ns();                               \
     } while (0)
 
 // ---------------------------------------------------------------------------------------------
@@ -606,9 +611,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], GEMV_CONSUMER_WARPS);
         }
+        GEMV_TRACE_ANY(8);
         mbar_init_fence();
-        if (p.trace != nullptr && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
-            p.trace[(blockIdx.x == 0 ? 0 : 8) + 5] = global_timer_ns();
+        GEMV_TRACE_ANY(5);
         for (; issued < niter && issued < S; ++issued) {
             const int r = row0 + issued * R;
             const int rows = min(R, row1 - r);
@@ -616,6 +621,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
             mbar_arrive_expect_tx(&full[issued], bytes);
             bulk_copy_g2s(ring + (size_t)issued * p.stage_bytes, p.w + (size_t)r * p.row_bytes, bytes, &full[issued]);
         }
+        GEMV_TRACE_ANY(9);
         if (issued >= niter) prefetch_successor(p.next, cta);  // everything of this CTA is already on its way
     }
     for (int i = tid; i < counter_ints; i += GEMV_THREADS) counters[i] = 0;
@@ -626,9 +632,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         // ---------------- producer: refills stages as the consumers release them ----------------
         if (lane == 0) {
             bool ok = true;
+            int s = 0;          // the refills start over at stage 0 (issued == S here whenever this loop runs)
+            uint32_t ph = 0;    // parity of the consumers' first release of each stage
             for (int it = issued; it < niter && ok; ++it) {
-                const int s = it % S;
-                ok = mbar_wait_bounded(&empty[s], ((it / S) - 1) & 1);
+                ok = mbar_wait_bounded(&empty[s], ph);
                 if (!ok) { record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, it); break; }
                 const int r = row0 + it * R;
                 const int rows = min(R, row1 - r);
@@ -637,6 +644,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                 bulk_copy_g2s(ring + (size_t)s * p.stage_bytes, p.w + (size_t)r * p.row_bytes, bytes, &full[s]);
                 issued = it + 1;
                 if (issued == niter) prefetch_successor(p.next, cta);
+                if (++s == S) {
+                    s = 0;
+                    ph ^= 1u;
+                }
             }
             if (!ok) {
                 // a consumer may have left; wait (bounded) until every copy already issued has landed so that no
@@ -653,6 +664,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
     }
 
     // ---------------- consumers ----------------
+    if (p.trace != nullptr && tid == 0) {  // when this thread's first activation load has come back
+        if constexpr (ACT == ACT_Q8_1) asm volatile("" ::"r"(pre.v[0]));
+        else asm volatile("" ::"r"(pre.raw[0][0]));
+        GEMV_TRACE(10);
+    }
     if constexpr (ACT == ACT_Q8_1)
         stage_acts_q8_1<B>(acts, reinterpret_cast<const uint8_t*>(p.act), p.K, p.stride_act, tid, GEMV_CONSUMER_THREADS, pre);
     else
@@ -690,9 +706,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
 
     GEMV_TRACE(7);
     bool alive = true;
+    // ring position and row rotation kept incrementally: the loop has no integer division
+    int s = 0;
+    uint32_t ph = 0;
+    int rot = 0;
+    const int rot_step = R % rows_per_pass;
     for (int it = 0; it < niter; ++it) {
-        const int s = it % S;
-        if (alive && !mbar_wait_bounded(&full[s], (it / S) & 1)) {
+        if (alive && !mbar_wait_bounded(&full[s], ph)) {
             record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, it);
             alive = false;  // keep arriving so that the others are not held up, but compute nothing
         }
@@ -702,28 +722,87 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         const int rows_here = min(R, row1 - rbase);
         // rows of consecutive stages go to consecutive warp groups, so a stage may hold fewer rows than one pass of
         // all warps without leaving the same warps idle every time
-        const int rot = (it * R) % rows_per_pass;
         const int my_slot = row_slot >= rot ? row_slot - rot : row_slot - rot + rows_per_pass;
-        for (int pass0 = 0; pass0 < rows_here; pass0 += rows_per_pass) {  // warp-uniform trip count
-            const int r_in = pass0 + my_slot;
-            const bool has_row = r_in < rows_here;
-            float acc[B];
+        if constexpr (NREG > 0) {
+            // Two rows per warp in flight (rows r and r + rows_per_pass of the stage): their loads, dot products and
+            // shuffle reductions are independent, so one row's latencies hide behind the other's work. Everything is
+            // computed unconditionally on clamped addresses and masked afterwards, which keeps it one basic block.
+            // (With two item slots per lane a row already gives two independent chains, and two rows would spill.)
+            constexpr int U = NREG == 1 ? 2 : 1;
+            for (int pass0 = 0; pass0 < rows_here; pass0 += U * rows_per_pass) {  // warp-uniform trip count
+                int r_in[U];
+                bool has_row[U];
+                float acc[U][B];
 #pragma unroll
-            for (int b = 0; b < B; ++b) acc[b] = 0.0f;
-            if (alive && has_row) {
-                const uint32_t row_addr = st + (uint32_t)r_in * (uint32_t)p.row_bytes;
-                if (NREG > 0) {
+                for (int u = 0; u < U; ++u) {
+                    r_in[u] = pass0 + my_slot + u * rows_per_pass;
+                    has_row[u] = r_in[u] < rows_here;
 #pragma unroll
-                    for (int j = 0; j < (NREG > 0 ? NREG : 1); ++j) {
-                        const int item = item0 + j * item_step;
-                        if (item < items) {
-                            Weights<TYPE> W;
-                            W.load(row_addr, item);
+                    for (int b = 0; b < B; ++b) acc[u][b] = 0.0f;
+                }
 #pragma unroll
-                            for (int b = 0; b < B; ++b) acc[b] += dot(W, areg[b][j]);
+                for (int j = 0; j < NREG; ++j) {
+                    const int item = item0 + j * item_step;
+                    const bool item_ok = item < items;
+                    const int item_c = item_ok ? item : 0;
+                    Weights<TYPE> W[U];
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+                        W[u].load(st + (uint32_t)(has_row[u] ? r_in[u] : 0) * (uint32_t)p.row_bytes, item_c);
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+#pragma unroll
+                        for (int b = 0; b < B; ++b) {
+                            const float d = dot(W[u], areg[b][j]);
+                            acc[u][b] += (alive && has_row[u] && item_ok) ? d : 0.0f;
+                        }
+                }
+                // reduce over the lanes that share the row
+#pragma unroll
+                for (int m = 16; m > 0; m >>= 1) {
+                    if (m < islots) {
+#pragma unroll
+                        for (int u = 0; u < U; ++u)
+#pragma unroll
+                            for (int b = 0; b < B; ++b) acc[u][b] += __shfl_xor_sync(0xffffffffu, acc[u][b], m);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (lane_i == 0 && has_row[u]) {
+                        if (WPR == 1) {
+#pragma unroll
+                            for (int b = 0; b < B; ++b) dst[(size_t)b * p.stride_dst + rbase + r_in[u]] = from_float<dst_t>(acc[u][b]);
+                        } else {
+                            // the last of the WPR warps to arrive adds the partial sums in slice order and writes the row
+                            float* part = partial + ((size_t)(s * R + r_in[u]) * WPR) * B;
+#pragma unroll
+                            for (int b = 0; b < B; ++b) part[wslice * B + b] = acc[u][b];
+                            __threadfence_block();
+                            const int arrived = atomicAdd(&counters[s * R + r_in[u]], 1);
+                            if (arrived == WPR - 1) {
+                                __threadfence_block();
+                                counters[s * R + r_in[u]] = 0;
+#pragma unroll
+                                for (int b = 0; b < B; ++b) {
+                                    float v = 0.0f;
+                                    for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w * B + b];
+                                    dst[(size_t)b * p.stride_dst + rbase + r_in[u]] = from_float<dst_t>(v);
+                                }
+                            }
                         }
                     }
-                } else {
+                }
+            }
+        } else {
+            for (int pass0 = 0; pass0 < rows_here; pass0 += rows_per_pass) {  // warp-uniform trip count
+                const int r_in = pass0 + my_slot;
+                const bool has_row = r_in < rows_here;
+                float acc[B];
+#pragma unroll
+                for (int b = 0; b < B; ++b) acc[b] = 0.0f;
+                if (alive && has_row) {
+                    const uint32_t row_addr = st + (uint32_t)r_in * (uint32_t)p.row_bytes;
                     for (int j = 0; j < IPL; ++j) {
                         const int item = item0 + j * item_step;
                         if (item < items) {
@@ -738,34 +817,34 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                         }
                     }
                 }
-            }
-            // reduce over the lanes that share the row
+                // reduce over the lanes that share the row
 #pragma unroll
-            for (int m = 16; m > 0; m >>= 1) {
-                if (m < islots) {
+                for (int m = 16; m > 0; m >>= 1) {
+                    if (m < islots) {
 #pragma unroll
-                    for (int b = 0; b < B; ++b) acc[b] += __shfl_xor_sync(0xffffffffu, acc[b], m);
+                        for (int b = 0; b < B; ++b) acc[b] += __shfl_xor_sync(0xffffffffu, acc[b], m);
+                    }
                 }
-            }
-            if (lane_i == 0 && has_row) {
-                if (WPR == 1) {
+                if (lane_i == 0 && has_row) {
+                    if (WPR == 1) {
 #pragma unroll
-                    for (int b = 0; b < B; ++b) dst[(size_t)b * p.stride_dst + rbase + r_in] = from_float<dst_t>(acc[b]);
-                } else {
-                    // the last of the WPR warps to arrive adds the partial sums in slice order and writes the row
-                    float* part = partial + ((size_t)(s * R + r_in) * WPR) * B;
+                        for (int b = 0; b < B; ++b) dst[(size_t)b * p.stride_dst + rbase + r_in] = from_float<dst_t>(acc[b]);
+                    } else {
+                        // the last of the WPR warps to arrive adds the partial sums in slice order and writes the row
+                        float* part = partial + ((size_t)(s * R + r_in) * WPR) * B;
 #pragma unroll
-                    for (int b = 0; b < B; ++b) part[wslice * B + b] = acc[b];
-                    __threadfence_block();
-                    const int arrived = atomicAdd(&counters[s * R + r_in], 1);
-                    if (arrived == WPR - 1) {
+                        for (int b = 0; b < B; ++b) part[wslice * B + b] = acc[b];
                         __threadfence_block();
-                        counters[s * R + r_in] = 0;
+                        const int arrived = atomicAdd(&counters[s * R + r_in], 1);
+                        if (arrived == WPR - 1) {
+                            __threadfence_block();
+                            counters[s * R + r_in] = 0;
 #pragma unroll
-                        for (int b = 0; b < B; ++b) {
-                            float v = 0.0f;
-                            for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w * B + b];
-                            dst[(size_t)b * p.stride_dst + rbase + r_in] = from_float<dst_t>(v);
+                            for (int b = 0; b < B; ++b) {
+                                float v = 0.0f;
+                                for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w * B + b];
+                                dst[(size_t)b * p.stride_dst + rbase + r_in] = from_float<dst_t>(v);
+                            }
                         }
                     }
                 }
@@ -773,6 +852,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
+        if (it == 0) GEMV_TRACE(11);
+        if (++s == S) {
+            s = 0;
+            ph ^= 1u;
+        }
+        rot += rot_step;
+        if (rot >= rows_per_pass) rot -= rows_per_pass;
     }
     if constexpr (AR) {
         // fused exchange: the CTA that finishes last (device-wide arrival counter in the exchange buffer) sums the
@@ -842,23 +928,67 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
                                                  int lane_i, int WPR, int wslice, int IPL, uint32_t acts_addr,
                                                  const ActPair (&areg)[NREG > 0 ? NREG : 1], float* part_base, int* cnt_base,
                                                  dst_t* dst, bool alive) {
-    for (int pass0 = 0; pass0 < rows_here; pass0 += rows_per_pass) {
-        const int r_in = pass0 + my_slot;
-        const bool has_row = r_in < rows_here;
-        float acc = 0.0f;
-        if (alive && has_row) {
-            const uint32_t row_addr = st + (uint32_t)r_in * (uint32_t)row_bytes;
-            if (NREG > 0) {
+    if constexpr (NREG > 0) {
+        // two rows per warp in flight, computed unconditionally on clamped addresses and masked (see gemv_staged_kernel)
+        constexpr int U = NREG == 1 ? 2 : 1;
+        for (int pass0 = 0; pass0 < rows_here; pass0 += U * rows_per_pass) {
+            int r_in[U];
+            bool has_row[U];
+            float acc[U];
 #pragma unroll
-                for (int j = 0; j < (NREG > 0 ? NREG : 1); ++j) {
-                    const int item = item0 + j * item_step;
-                    if (item < items) {
-                        Weights<TYPE> W;
-                        W.load(row_addr, item);
-                        acc += dot(W, areg[j]);
+            for (int u = 0; u < U; ++u) {
+                r_in[u] = pass0 + my_slot + u * rows_per_pass;
+                has_row[u] = r_in[u] < rows_here;
+                acc[u] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < NREG; ++j) {
+                const int item = item0 + j * item_step;
+                const bool item_ok = item < items;
+                const int item_c = item_ok ? item : 0;
+                Weights<TYPE> W[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) W[u].load(st + (uint32_t)(has_row[u] ? r_in[u] : 0) * (uint32_t)row_bytes, item_c);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const float d = dot(W[u], areg[j]);
+                    acc[u] += (alive && has_row[u] && item_ok) ? d : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1)
+                if (m < islots) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
+                }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (lane_i == 0 && has_row[u]) {
+                    if (WPR == 1) {
+                        dst[rbase + r_in[u]] = from_float<dst_t>(acc[u]);
+                    } else {
+                        float* part = part_base + (size_t)r_in[u] * WPR;
+                        part[wslice] = acc[u];
+                        __threadfence_block();
+                        const int arrived = atomicAdd(&cnt_base[r_in[u]], 1);
+                        if (arrived == WPR - 1) {
+                            __threadfence_block();
+                            cnt_base[r_in[u]] = 0;
+                            float v = 0.0f;
+                            for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w];
+                            dst[rbase + r_in[u]] = from_float<dst_t>(v);
+                        }
                     }
                 }
-            } else {
+            }
+        }
+    } else {
+        for (int pass0 = 0; pass0 < rows_here; pass0 += rows_per_pass) {
+            const int r_in = pass0 + my_slot;
+            const bool has_row = r_in < rows_here;
+            float acc = 0.0f;
+            if (alive && has_row) {
+                const uint32_t row_addr = st + (uint32_t)r_in * (uint32_t)row_bytes;
                 for (int j = 0; j < IPL; ++j) {
                     const int item = item0 + j * item_step;
                     if (item < items) {
@@ -870,24 +1000,24 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
                     }
                 }
             }
-        }
 #pragma unroll
-        for (int m = 16; m > 0; m >>= 1)
-            if (m < islots) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-        if (lane_i == 0 && has_row) {
-            if (WPR == 1) {
-                dst[rbase + r_in] = from_float<dst_t>(acc);
-            } else {
-                float* part = part_base + (size_t)r_in * WPR;
-                part[wslice] = acc;
-                __threadfence_block();
-                const int arrived = atomicAdd(&cnt_base[r_in], 1);
-                if (arrived == WPR - 1) {
+            for (int m = 16; m > 0; m >>= 1)
+                if (m < islots) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+            if (lane_i == 0 && has_row) {
+                if (WPR == 1) {
+                    dst[rbase + r_in] = from_float<dst_t>(acc);
+                } else {
+                    float* part = part_base + (size_t)r_in * WPR;
+                    part[wslice] = acc;
                     __threadfence_block();
-                    cnt_base[r_in] = 0;
-                    float v = 0.0f;
-                    for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w];
-                    dst[rbase + r_in] = from_float<dst_t>(v);
+                    const int arrived = atomicAdd(&cnt_base[r_in], 1);
+                    if (arrived == WPR - 1) {
+                        __threadfence_block();
+                        cnt_base[r_in] = 0;
+                        float v = 0.0f;
+                        for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w];
+                        dst[rbase + r_in] = from_float<dst_t>(v);
+                    }
                 }
             }
         }
@@ -933,20 +1063,25 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
         if (lane == 0) {
             bool ok = true;
             int g = 0;  // running stage number over all matrices
+            int s = 0;
+            uint32_t ph = 1;  // becomes the parity of the consumers' first release once the ring has gone round
             for (int m = 0; m < p.nmat && ok; ++m) {
                 int row0, row1;
                 group_rows(p, m, cta, row0, row1);
                 const int R = p.rows_per_stage[m];
                 for (int r = row0; r < row1 && ok; r += R, ++g) {
-                    const int s = g % S;
                     if (g >= S) {
-                        ok = mbar_wait_bounded(&empty[s], ((g / S) - 1) & 1);
+                        ok = mbar_wait_bounded(&empty[s], ph);
                         if (!ok) { record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, g); break; }
                     }
                     const int rows = min(R, row1 - r);
                     const uint32_t bytes = ((uint32_t)rows * (uint32_t)p.row_bytes[m] + 15u) & ~15u;
                     mbar_arrive_expect_tx(&full[s], bytes);
                     bulk_copy_g2s(ring + (size_t)s * p.stage_bytes, p.w[m] + (size_t)r * p.row_bytes[m], bytes, &full[s]);
+                    if (++s == S) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
                 }
             }
             if (ok) prefetch_successor(p.next, cta);
@@ -990,7 +1125,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
 
     bool alive = true;
     int g = 0;
-    int rot_rows = 0;  // rows handed out so far: rotates the row-to-warp assignment across stages
+    int s = 0;
+    uint32_t ph = 0;
+    int rot = 0;  // rows handed out so far modulo rows_per_pass: rotates the row-to-warp assignment across stages
     for (int m = 0; m < p.nmat; ++m) {
         int row0, row1;
         group_rows(p, m, cta, row0, row1);
@@ -998,16 +1135,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
         const int mtype = p.type[m];
         dst_t* dst = reinterpret_cast<dst_t*>(p.dst[m]);
         for (int r = row0; r < row1; r += R, ++g) {
-            const int s = g % S;
-            if (alive && !mbar_wait_bounded(&full[s], (g / S) & 1)) {
+            if (alive && !mbar_wait_bounded(&full[s], ph)) {
                 record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, g);
                 alive = false;
             }
             const uint32_t st = ring_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
             const int rows_here = min(R, row1 - r);
-            const int rot = rot_rows % rows_per_pass;
             const int my_slot = row_slot >= rot ? row_slot - rot : row_slot - rot + rows_per_pass;
-            rot_rows += rows_here;
+            rot += rows_here;
+            while (rot >= rows_per_pass) rot -= rows_per_pass;
             float* part_base = partial + (size_t)s * RMAX * WPR;
             int* cnt_base = counters + s * RMAX;
             if (mtype == TYPE_Q4_K)
@@ -1021,6 +1157,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
                                                          items, islots, lane_i, WPR, wslice, IPL, acts_addr, areg, part_base, cnt_base, dst, alive);
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
+            if (++s == S) {
+                s = 0;
+                ph ^= 1u;
+            }
         }
     }
 }
@@ -1162,8 +1302,14 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     const int rows_per_pass = nrg * rpw;
     // rows per stage: whole passes of all warps (every warp visits every stage in order, so a stage that feeds only
     // some warps would stall the others), about gemv_stage_target bytes, at least one pass
-    const int unit = rows_per_pass * p.row_align / gcd_int(rows_per_pass, p.row_align);
-    int R = rt.gemv_stage_target / (unit * p.row_bytes) * unit;
+    // register-resident activations: 40 registers per slot and activation row
+    plan.nreg = (B == 1 && ipl <= 2) ? ipl : ((B == 2 && ipl == 1) ? 1 : 0);
+    // with one register-resident slot a warp keeps two rows of a stage in flight (rows r and r + rows_per_pass), so a
+    // stage holds two passes
+    const int passes = plan.nreg == 1 ? 2 : 1;
+    const int unit0 = rows_per_pass * p.row_align / gcd_int(rows_per_pass, p.row_align);
+    const int unit = unit0 * passes;
+    int R = passes * rt.gemv_stage_target / (unit * p.row_bytes) * unit;
     if (R < unit) R = unit;
     p.rows_per_stage = R;
     p.warps_per_row = wpr;
@@ -1194,8 +1340,6 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     plan.grid = (int)grid;
     p.units_per_cta = (int)(units / grid);
     p.units_extra = (int)(units % grid);
-    // register-resident activations: 40 registers per slot and activation row
-    plan.nreg = (B == 1 && ipl <= 2) ? ipl : ((B == 2 && ipl == 1) ? 1 : 0);
     plan.staged = true;
     return plan;
 }

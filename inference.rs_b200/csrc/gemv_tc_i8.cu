@@ -96,6 +96,10 @@ struct TcqParams {
     unsigned int* status;
     unsigned long long* trace;  // optional: SM clock of CTA 0's pipeline events, [event 0..7][stage 0..trace_stages)
     int trace_stages;
+    // REF_ACTS kernels: the activations as the reference's mmvq_tc_quantize lays them out (tcq_ref_quantize_kernel
+    // below writes the same bytes): `ref_halves` halves of 8 rows, each K / 32 blocks of 288 bytes
+    const uint8_t* ref_acts;
+    int ref_halves;
 };
 
 #define TCQ_TRACE(event, g)                                                                          \
@@ -131,6 +135,81 @@ __global__ void __launch_bounds__(32 * TCQ_TOKENS) tcq_quantize_kernel(const src
     if (lane == 0) {
         const float dh = __half2float(__float2half_rn(d));
         ds[(size_t)kb * TCQ_TOKENS + row] = make_float2(dh, dh * (float)sum);
+    }
+}
+
+// The reference tier's own activation layout (crates/inference-quant/kernels/cuda/mmvq_gguf/mmvq_quantize.cu:148-190,
+// mmvq_tc_act.cuh:1-7), for hosts that call launch_mmvq_tc_quantize_* / launch_mmvq_tc_gguf_*_plain as a pair: the
+// rows in halves of 8, one half after the other; per half nb = gridDim.x blocks of 32 values: nb * 32 int2 (entry
+// 4r + t of a block = row r's values 4t..4t+3 then 16+4t..16+4t+3), then nb * 8 f16 scales d = amax / 127, then nb * 8
+// int16 sums of the quants q = roundf(x / d). One CTA per (block, half), one warp per row.
+constexpr int TCQ_REF_BLOCK_BYTES = 32 * 8 + 8 * 2 + 8 * 2;  // 288
+template <typename src_t>
+__global__ void __launch_bounds__(256) tcq_ref_quantize_kernel(const src_t* __restrict__ x, uint8_t* __restrict__ vy, int kx, int num_rows) {
+    const int ib = blockIdx.x, nb = gridDim.x, row = threadIdx.y, lane = threadIdx.x;
+    const int col = ib * 32 + lane;
+    const int input_row = blockIdx.y * 8 + row;
+    uint8_t* base = vy + (size_t)blockIdx.y * nb * TCQ_REF_BLOCK_BYTES;
+    const float xi = (input_row < num_rows && col < kx) ? to_float<src_t>(x[(size_t)input_row * kx + col]) : 0.0f;
+    const float amax = warp_max(fabsf(xi));
+    const float d = amax / 127.0f;
+    const int qi = amax == 0.0f ? 0 : (int)roundf(xi / d);
+    const int sum = __reduce_add_sync(0xffffffffu, qi);
+    __shared__ __align__(8) int8_t q[8][32];
+    q[row][lane] = (int8_t)qi;
+    if (lane == 0) {
+        reinterpret_cast<__half*>(base + (size_t)nb * 256)[ib * 8 + row] = __float2half_rn(d);
+        reinterpret_cast<int16_t*>(base + (size_t)nb * 256 + (size_t)nb * 16)[ib * 8 + row] = (int16_t)sum;
+    }
+    __syncthreads();
+    if (row == 0) {
+        const int r = lane >> 2, t = lane & 3;
+        reinterpret_cast<int2*>(base)[(size_t)ib * 32 + lane] =
+            make_int2(*reinterpret_cast<const int*>(&q[r][4 * t]), *reinterpret_cast<const int*>(&q[r][16 + 4 * t]));
+    }
+}
+
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+
+// One stage (256 k = 8 blocks) of the reference-layout activations -> the B-operand tile the MMAs read (XROWS rows of
+// 128 swizzled bytes per 128-k sub-tile; for Q6_K rows 0..15 carry the first 16 values of every block and rows 16..31
+// the last 16) plus float2 (d, d * sum) per (block, row). Rows the caller did not supply stay zero. By one warp.
+template <int TYPE>
+__device__ __forceinline__ void tcq_stage_ref_acts(const TcqParams& p, int kc, uint8_t* st, int lane) {
+    using TT = TcqType<TYPE>;
+    using L = TcqLayout<TYPE>;
+    const uint32_t st_addr = smem_u32(st);
+    for (int i = lane; i < L::X_BYTES / 16; i += 32) sts128(st_addr + 16 * i, 0u, 0u, 0u, 0u);
+    __syncwarp();
+    const int nb = p.K / 32;
+    const int r = lane >> 2, t = lane & 3;
+    for (int hf = 0; hf < p.ref_halves; ++hf) {
+        const uint8_t* base = p.ref_acts + (size_t)hf * nb * TCQ_REF_BLOCK_BYTES;
+        const int row = hf * 8 + r;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int2 frag = __ldg(reinterpret_cast<const int2*>(base) + (size_t)(8 * kc + j) * 32 + lane);
+            const uint32_t sub = st_addr + (uint32_t)(j >> 2) * (TT::XROWS * 128);
+            const int c = 2 * (j & 3);
+            if constexpr (TYPE == TYPE_Q6_K) {
+                sts32(b_chunk_addr(sub, row, c) + 4 * t, (uint32_t)frag.x);
+                sts32(b_chunk_addr(sub, TCQ_TOKENS + row, c + 1) + 4 * t, (uint32_t)frag.y);
+            } else {
+                sts32(b_chunk_addr(sub, row, c) + 4 * t, (uint32_t)frag.x);
+                sts32(b_chunk_addr(sub, row, c + 1) + 4 * t, (uint32_t)frag.y);
+            }
+        }
+        // scales and sums of the stage's 8 blocks x 8 rows: two entries per lane
+        const __half* ds = reinterpret_cast<const __half*>(base + (size_t)nb * 256);
+        const int16_t* ss = reinterpret_cast<const int16_t*>(base + (size_t)nb * 256 + (size_t)nb * 16);
+#pragma unroll
+        for (int e2 = 0; e2 < 2; ++e2) {
+            const int e = lane + 32 * e2, j = e >> 3, rr = e & 7;
+            const float dh = __half2float(ds[(8 * kc + j) * 8 + rr]);
+            const float sm = (float)(int)ss[(8 * kc + j) * 8 + rr];
+            float2* dst = reinterpret_cast<float2*>(st + TT::XROWS * TCQ_KC) + j * TCQ_TOKENS + hf * 8 + rr;
+            *dst = make_float2(dh, dh * sm);
+        }
     }
 }
 
@@ -316,7 +395,9 @@ struct TcqRing {
     }
 };
 
-template <int TYPE, typename dst_t, int TOK>
+// REF_ACTS: activations come in the reference tier's layout (p.ref_acts) and warp 0 re-lays them out per stage instead
+// of fetching ready tiles by TMA.
+template <int TYPE, typename dst_t, int TOK, bool REF_ACTS = false>
 __global__ void __launch_bounds__(TCQ_THREADS, 1)
     gemv_tc_i8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const TcqParams p) {
     using TT = TcqType<TYPE>;
@@ -384,7 +465,25 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
-    if (warp == 0) {
+    if (warp == 0 && REF_ACTS) {
+        // ---------------- activation tiles re-laid out from the reference tier's fragments, by the whole warp ----------------
+        TcqRing xr;
+        int kc = kc0;
+        for (int g = 0; g < nstages; ++g) {
+            bool ok = mbar_wait_bounded(&bars->x_empty[xr.i], xr.ph ^ 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, g);
+                break;
+            }
+            tcq_stage_ref_acts<TYPE>(p, kc, x_stages + (size_t)xr.i * L::X_BYTES, lane);
+            fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->x_full[xr.i]);
+            xr.next(XS);
+            if (++kc == kc1) kc = kc0;
+        }
+    } else if (warp == 0) {
         // ---------------- activation tiles (two XROWS x 128-byte boxes) and their scales ----------------
         if (lane == 0) {
             TcqRing xr;
@@ -702,10 +801,10 @@ size_t gemv_tc_workspace_bytes(int type, int K) {
     return ((tcq_quant_bytes(type, K) + 255) & ~(size_t)255) + TCQ_COUNTERS * sizeof(unsigned int) + TCQ_PARTIAL_BYTES;
 }
 
-template <int TYPE, typename T, int TOK>
+template <int TYPE, typename T, int TOK, bool REF_ACTS = false>
 static int launch_gemv_tc_i8_tok(const CUtensorMap& map_w, const CUtensorMap& map_x, const TcqParams& p, int grid, int smem_bytes,
                                  cudaStream_t s) {
-    auto kernel = gemv_tc_i8_kernel<TYPE, T, TOK>;
+    auto kernel = gemv_tc_i8_kernel<TYPE, T, TOK, REF_ACTS>;
     static PerDeviceOnce configured;  // per instantiation and device
     const cudaError_t attr_err =
         configured.run([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TCQ_SMEM_LIMIT); });

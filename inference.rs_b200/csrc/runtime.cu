@@ -67,13 +67,13 @@ void set_trace_buffer(unsigned long long* dev, int records) {
 }
 
 unsigned long long* trace_buffer(int* slots) {
-    *slots = g_trace ? g_trace_records * 16 : 0;
+    *slots = g_trace ? g_trace_records * 32 : 0;
     return g_trace;
 }
 unsigned long long* trace_slot() {
     if (g_trace == nullptr || g_trace_records <= 0) return nullptr;
     const int i = g_trace_next.fetch_add(1) % g_trace_records;
-    return g_trace + (size_t)i * 16;
+    return g_trace + (size_t)i * 32;
 }
 
 static std::shared_mutex g_succ_mutex;

@@ -41,7 +41,7 @@ bool find_weight_successor(const void* w, WeightSuccessor* out);
 const RuntimeInfo& runtime_info();
 RuntimeInfo& runtime_info_mut();
 unsigned int* status_ptr();          // device address of the status word of the current device (cached)
-// diagnostics: when a trace buffer is set, every GEMV launch gets the next 16-slot record of it (wrapping)
+// diagnostics: when a trace buffer is set, every GEMV launch gets the next 32-slot record of it (wrapping)
 void set_trace_buffer(unsigned long long* dev, int records);
 unsigned long long* trace_slot();
 unsigned long long* trace_buffer(int* slots);

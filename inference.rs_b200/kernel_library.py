@@ -30,6 +30,8 @@ for _e in ("bf16", "f16", "f32"):
     SYMBOLS[f"launch_mmvq_gguf_quantize_q8_1_{_e}"] = (_QUANT_ARGS, None)
     for _t in ("q8_0", "q4_k", "q6_k"):
         SYMBOLS[f"launch_mmvq_gguf_{_t}_{_e}_plain"] = (_PLAIN_ARGS, None)
+for _e in ("bf16", "f32"):
+    SYMBOLS[f"launch_mmvq_gguf_q8_0_{_e}_exact"] = ([_vp, _vp, _vp, _i32, _i32, _i32, _vp], None)
 for _l in ("D4", "DS4"):
     SYMBOLS[f"launch_mmq_quantize_q8_1_{_l}"] = (_MMQ_QUANT_ARGS, None)
 SYMBOLS.update({

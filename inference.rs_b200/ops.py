@@ -82,6 +82,24 @@ def mmvq_plain(dtype: GgmlDType, w: torch.Tensor, vy: torch.Tensor, n: int, k: i
     return dst
 
 
+def mmvq_exact_q8_0(w: torch.Tensor, x: torch.Tensor, n: int) -> torch.Tensor:
+    """`launch_mmvq_gguf_q8_0_{bf16,f32}_exact`: Q8_0 weights against unquantized activations x [b <= 8, k] (bf16 or
+    f32), f32 accumulation; returns [b, n] in x's type."""
+    _require_cuda(w, x)
+    b, k = x.shape
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"the exact Q8_0 matvec takes bf16 or f32 activations, not {x.dtype}")
+    if b > 8:
+        raise ValueError("the exact Q8_0 matvec takes at most 8 activation rows")
+    dst = torch.empty((b, n), dtype=x.dtype, device=x.device)
+    fn = getattr(kl.library(), f"launch_mmvq_gguf_q8_0_{ELEM_TAG[elem_of(x.dtype)]}_exact")
+    fn(w.data_ptr(), x.data_ptr(), dst.data_ptr(), k, n, b, _stream())
+    rc = kl.library().b200q_take_launch_status()
+    if rc:
+        raise kl.KernelLibraryError(f"launch_mmvq_gguf_q8_0_*_exact failed with status {rc}")
+    return dst
+
+
 ACT_QUANT_Q8_1, ACT_QUANT_CPU = 0, 1
 
 

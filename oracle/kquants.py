@@ -34,6 +34,7 @@ def lib() -> C.CDLL:
         L.orc_quantize_q8_1_cpu.argtypes = [vp, vp, i64]
         L.orc_quantize_q8_1_mmvq.argtypes = [vp, vp, i64, i64, i64]
         L.orc_quantize_q8_1_mmq.argtypes = [vp, vp, i64, i64, i64, i32]
+        L.orc_quantize_mmvq_tc.argtypes = [vp, vp, i64, i64]
         L.orc_quantize_q8_k.argtypes = [vp, vp, i64]
         L.orc_matmul.argtypes = [i32, i64, i64, i64, vp, vp, vp, i32]
         L.orc_matmul.restype = i32
@@ -118,6 +119,15 @@ def quantize_q8_1_mmvq(x, k_padded: int | None = None) -> np.ndarray:
         k_padded = (k + 511) // 512 * 512
     out = np.zeros((rows, k_padded // 32 * 36), dtype=np.uint8)
     lib().orc_quantize_q8_1_mmvq(_p(x), _p(out), k, k_padded, rows)
+    return out
+
+
+def quantize_mmvq_tc(x) -> np.ndarray:
+    """The tensor-core matvec tier's activation layout: uint8 ``[ceil(rows / 8) * ceil(k / 32) * 288]``."""
+    x = _f32(x)
+    rows, k = x.shape
+    out = np.zeros(((rows + 7) // 8) * ((k + 31) // 32) * 288, dtype=np.uint8)
+    lib().orc_quantize_mmvq_tc(_p(x), _p(out), k, rows)
     return out
 
 

@@ -233,6 +233,45 @@ void orc_quantize_q8_1_mmvq(const float *x, void *out, int64_t kx, int64_t kx_pa
     }
 }
 
+/* The tensor-core matvec tier's activation layout, `mmvq_tc_quantize`
+ * (crates/inference-quant/kernels/cuda/mmvq_gguf/mmvq_quantize.cu:148-190, layout mmvq_tc_act.cuh:1-7): the rows in
+ * halves of 8, one half after the other; per half and with nb = ceil(kx / 32) blocks: nb * 32 int2 fragments (entry
+ * 4r + t of a block holds row r's values 4t..4t+3 then 16+4t..16+4t+3), then nb * 8 f16 scales (d = amax / 127), then
+ * nb * 8 int16 block sums of the quants. q = roundf(x / d) (IEEE division here, as in orc_quantize_q8_1_mmvq); rows
+ * past `rows` and values past `kx` are zero. `out` holds ceil(rows / 8) * nb * 288 bytes. */
+void orc_quantize_mmvq_tc(const float *x, void *out, int64_t kx, int64_t rows) {
+    int64_t nb = (kx + 31) / 32;
+    int64_t halves = (rows + 7) / 8;
+    for (int64_t h = 0; h < halves; h++) {
+        uint8_t *base = (uint8_t *)out + h * nb * 288;
+        int8_t *qs = (int8_t *)base;
+        uint16_t *ds = (uint16_t *)(base + nb * 256);
+        int16_t *ss = (int16_t *)(base + nb * 256 + nb * 16);
+        for (int64_t b = 0; b < nb; b++) {
+            for (int r = 0; r < 8; r++) {
+                int64_t row = h * 8 + r;
+                float v[32];
+                float amax = 0.0f;
+                for (int j = 0; j < 32; j++) {
+                    int64_t col = 32 * b + j;
+                    v[j] = (row < rows && col < kx) ? x[row * kx + col] : 0.0f;
+                    amax = fmaxf(amax, fabsf(v[j]));
+                }
+                float d = amax / 127.0f;
+                int sum = 0;
+                for (int j = 0; j < 32; j++) {
+                    int8_t q = amax == 0.0f ? 0 : (int8_t)roundf(v[j] / d);
+                    sum += q;
+                    int t = (j & 15) >> 2;
+                    qs[b * 256 + (4 * r + t) * 8 + (j >= 16 ? 4 : 0) + (j & 3)] = q;
+                }
+                ds[b * 8 + r] = orc_f32_to_f16(d);
+                ss[b * 8 + r] = (int16_t)sum;
+            }
+        }
+    }
+}
+
 /* The prefill path's activation quantizer, `quantize_mmq_q8_1` (MQ:98-199): blocks of 128 values of one
  * token, 144 bytes: 16 bytes of scales then 128 int8. Block index ib = (k / 128) * rows + row.
  * layout 0 (D4): four f32 d; layout 1 (DS4): four half2 (d, sum of x). d_inv = 127 / amax,

@@ -97,8 +97,9 @@ def mmvq_plain(type_id: int, w, vy, n: int, k: int, b: int, dtype):
     """The dp4a decode matvec on Q8_1 blocks, b = 1..8 (launch_mmvq_gguf_<type>_<elem>_plain)."""
     import torch
     out = torch.empty(b, n, dtype=dtype, device=w.device)
+    stride_blocks = vy.numel() // 36 // vy.shape[0]  # Q8_1 blocks per activation row, whatever the tensor's shape
     getattr(lib(), f"launch_mmvq_gguf_{NAMES[type_id]}_{_elem(dtype)}_plain")(
-        w.data_ptr(), vy.data_ptr(), out.data_ptr(), k, n, vy.shape[1], n, b, _stream())
+        w.data_ptr(), vy.data_ptr(), out.data_ptr(), k, n, stride_blocks, n, b, _stream())
     return out
 
 
@@ -114,7 +115,7 @@ def fused_glu(type_id: int, w_gate, w_up, x, n: int, activation: str = "silu"):
     vy = quantize_q8_1(x)
     out = torch.empty(b, n, dtype=x.dtype, device=x.device)
     getattr(lib(), f"launch_mmvq_gguf_{NAMES[type_id]}_{_elem(x.dtype)}_fused_glu")(
-        w_gate.data_ptr(), w_up.data_ptr(), vy.data_ptr(), out.data_ptr(), k, n, vy.shape[1], n, b,
+        w_gate.data_ptr(), w_up.data_ptr(), vy.data_ptr(), out.data_ptr(), k, n, vy.numel() // 36 // b, n, b,
         GLU_ACTIVATIONS[activation], _stream())
     return out
 
@@ -127,13 +128,13 @@ def fused_qkv(type_id: int, wq, wk, wv, x, nq: int, nk: int, nv: int):
     outs = [torch.empty(b, n, dtype=x.dtype, device=x.device) for n in (nq, nk, nv)]
     getattr(lib(), f"launch_mmvq_gguf_{NAMES[type_id]}_{_elem(x.dtype)}_fused_qkv")(
         wq.data_ptr(), wk.data_ptr(), wv.data_ptr(), vy.data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(),
-        k, nq, nk, nv, vy.shape[1], b, _stream())
+        k, nq, nk, nv, vy.numel() // 36 // b, b, _stream())
     return outs
 
 
 def tc_scratch_bytes(k: int, b: int) -> int:
-    """fast_mmvq.rs:1898-1902: 272 bytes per 32-value block and 8-row half."""
-    return (k // 32) * 272 * ((b + 7) // 8)
+    """fast_mmvq.rs:1898-1902: 288 bytes per 32-value block and 8-row half."""
+    return (k // 32) * 288 * ((b + 7) // 8)
 
 
 def tc_quantize(x):

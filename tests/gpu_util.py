@@ -1,6 +1,8 @@
 """Helpers shared by the GPU parity tests: seeded inputs, oracle calls, tolerances."""
 from __future__ import annotations
 
+import functools
+
 import numpy as np
 import torch
 
@@ -28,6 +30,21 @@ def as_f32_numpy(x: torch.Tensor) -> np.ndarray:
     return x.detach().float().cpu().numpy()
 
 
+@functools.lru_cache(maxsize=3)
+def real_packed(type_id: int, n: int, k: int) -> np.ndarray:
+    """The baseline's weights for a shape: ~N(0, 0.02), seed = n * 100003 + k, packed by the oracle's quantizer (the
+    reference's default mode). Seconds per shape on the host cores, a minute for the 128256-row head; the last few
+    shapes are kept so that the batch sizes of one shape share the work."""
+    g = torch.Generator().manual_seed(n * 100003 + k)
+    out = np.empty((n, k // kq.BLOCK_ELEMS[type_id] * kq.BLOCK_BYTES[type_id]), dtype=np.uint8)
+    step = 16384  # rows at a time: bounds the f32 copy of the head to 256 MB
+    for r0 in range(0, n, step):
+        rows = min(step, n - r0)
+        w = (torch.randn(rows, k, generator=g) * 0.02).numpy()
+        out[r0:r0 + rows] = kq.quantize(type_id, w)
+    return out
+
+
 def random_packed(type_id: int, n: int, k: int, seed: int) -> np.ndarray:
     """Random but well-formed blocks (random quants and sub-scales, scales of the size N(0, 0.02) weights give):
     lets full-size shapes be tested without running the quantizer over hundreds of millions of weights."""
@@ -51,6 +68,13 @@ def random_packed(type_id: int, n: int, k: int, seed: int) -> np.ndarray:
 
 def elementwise_pass_rate(got: np.ndarray, ref: np.ndarray, rtol=1e-2, atol=1e-3) -> float:
     return float((np.abs(got - ref) <= atol + rtol * np.abs(ref)).mean())
+
+
+# The reference's CUDA path feeds its matvecs Q8_1 activations (a scale per 32 values), its CPU path Q8_K (a scale per
+# 256 values) for Q4_K / Q6_K weights; on ~N(0, 0.02) weights and ~N(0, 1) activations the two roundings alone leave
+# about 61 % of the outputs within 1e-3 + 1e-2 |ref| of each other (Q8_0 weights, whose CPU format is per 32 too: 99 %).
+# A kernel that computes the CUDA path's arithmetic exactly lands on these rates; well below them something else is off.
+Q8_1_VS_CPU_PASS_FLOOR = {kq.Q4_K: 0.55, kq.Q6_K: 0.55, kq.Q8_0: 0.98}
 
 
 def assert_device_ok():

@@ -3,7 +3,16 @@
   * against the same arithmetic in double (activations as given, weights dequantized by the oracle and rounded to the
     activation type as the kernel does): only f32 accumulation order and output rounding differ;
   * against the reference CPU path (Q8_K / Q8_0 activations): per tensor, max|d| <= 1e-3 + 1e-2 max|ref|. The kernel
-    keeps activations unquantized, so it is closer to the dense product than the CPU path is.
+    keeps activations unquantized, so it is closer to the dense product than the CPU path is;
+  * against the reference's own CUDA prefill path (oracle/_ref: its activation quantizer + MMQ tile GEMM, compiled
+    from the reference checkout), per tensor at the bound the reference's own CUDA tests use, max|d| <= 0.02 max|ref|
+    (crates/inference-quant/src/gguf/mod.rs:998-1037): that path quantizes the activations to int8 and multiplies block
+    scales in half precision (mmq_gguf.cuh:2207-2211), so it sits 1.2 - 1.6 % of the largest output away from this kernel,
+    which keeps activations in 16 bits and scales in f32 and is the closer of the two to the CPU path.
+
+Shapes of the baseline's prefill sweep use ~N(0, 0.02) weights packed by the oracle's quantizer. At M = 2048 and 8192
+the CPU comparisons run on a seeded sample of the token rows (output rows are independent; the oracle is scalar code)
+and every row is covered by comparing the large call with calls on 512-token slices, bit for bit.
 """
 import numpy as np
 import pytest
@@ -11,8 +20,10 @@ import torch
 
 from oracle import kquants as kq
 
+from oracle import refkernels as rk
+
 from inference_rs_b200 import ops
-from gpu_util import DT, TYPES, as_f32_numpy, assert_device_ok, random_packed, seeded_acts, seeded_weights
+from gpu_util import DT, TYPES, as_f32_numpy, assert_device_ok, random_packed, real_packed, seeded_acts, seeded_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -23,17 +34,26 @@ def rounded_weights(type_id, packed, k, dtype):
     return t.astype(np.float64)
 
 
-def run_gemm(type_id, m, n, k, dtype=torch.bfloat16, packed=None, seed=0, check_cpu=True):
-    real = packed is None
+def run_gemm(type_id, m, n, k, dtype=torch.bfloat16, packed=None, seed=0, check_cpu=True, real=None, sample_rows=None):
+    if real is None:
+        real = packed is None
     if packed is None:
         packed = kq.quantize(type_id, seeded_weights(n, k, 3000 + seed))
     x = seeded_acts(m, k, 4000 + seed, dtype)
     w_dev = ops.upload_weights(packed, DT[type_id])
-    y = ops.gemm(DT[type_id], w_dev, x.cuda(), n)
+    x_dev = x.cuda()
+    y = ops.gemm(DT[type_id], w_dev, x_dev, n)
     torch.cuda.synchronize()
     assert_device_ok()
-    got = as_f32_numpy(y).astype(np.float64)
-    xf = as_f32_numpy(x).astype(np.float64)
+    rows = np.arange(m)
+    if sample_rows is not None and sample_rows < m:
+        rows = np.sort(np.random.default_rng(seed).choice(m, size=sample_rows, replace=False))
+        # rows outside the sample: the same bits as calls on 512-token slices
+        for r0 in range(0, m, 512):
+            part = ops.gemm(DT[type_id], w_dev, x_dev[r0:r0 + 512].contiguous(), n)
+            assert torch.equal(part, y[r0:r0 + 512]), f"rows {r0}..{r0 + 512} differ from the slice run alone"
+    got = as_f32_numpy(y)[rows].astype(np.float64)
+    xf = as_f32_numpy(x)[rows].astype(np.float64)
     ref = xf @ rounded_weights(type_id, packed, k, dtype).T
     eps = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
     scale = np.abs(ref).max()
@@ -41,9 +61,13 @@ def run_gemm(type_id, m, n, k, dtype=torch.bfloat16, packed=None, seed=0, check_
     assert not bad.any(), (f"{kq.TYPE_NAMES[type_id]} m={m} n={n} k={k}: {bad.sum()} outputs off, worst {np.abs(got - ref).max():.3e} "
                            f"vs scale {scale:.3e}; first at {np.argwhere(bad)[:4].tolist()}")
     if check_cpu:
-        cpu = kq.matmul(type_id, as_f32_numpy(x), packed, n)
+        cpu = kq.matmul(type_id, as_f32_numpy(x)[rows], packed, n)
         rel = 1e-2 if real else 2e-2
         assert np.abs(got - cpu).max() <= 1e-3 + rel * np.abs(cpu).max()
+    if rk.available() and k % 256 == 0:
+        theirs = as_f32_numpy(rk.mmq_forward(type_id, w_dev, x_dev, n))[rows].astype(np.float64)
+        torch.cuda.synchronize()
+        assert np.abs(got - theirs).max() <= 2e-2 * np.abs(theirs).max(), "differs from the reference's MMQ"
 
 
 @pytest.mark.parametrize("type_id", TYPES)
@@ -60,12 +84,21 @@ def test_f16_activations(type_id):
 @pytest.mark.parametrize("type_id", [kq.Q4_K, kq.Q6_K])
 @pytest.mark.parametrize("k,n", [(4096, 4096), (14336, 4096), (4096, 6144)])
 def test_prefill_shapes_m512(type_id, k, n):
-    run_gemm(type_id, 512, n, k, packed=random_packed(type_id, n, k, seed=k + n), seed=1)
+    run_gemm(type_id, 512, n, k, packed=real_packed(type_id, n, k), seed=1, real=True)
 
 
-def test_two_subtiles_path_large_m():
-    # M = 2048 with enough tiles takes the 256-token CTA tile
-    run_gemm(kq.Q4_K, 2048, 4096, 4096, packed=random_packed(kq.Q4_K, 4096, 4096, seed=5), seed=2, check_cpu=False)
+@pytest.mark.parametrize("type_id", [kq.Q4_K, kq.Q6_K])
+@pytest.mark.parametrize("k,n", [(4096, 4096), (14336, 4096)])
+@pytest.mark.parametrize("m", [2048, 8192])
+def test_prefill_shapes_large_m(type_id, k, n, m):
+    # M = 2048 with enough tiles takes the 256-token CTA tile; M = 8192 is the compute-bound end of the sweep
+    run_gemm(type_id, m, n, k, packed=real_packed(type_id, n, k), seed=m, real=True, sample_rows=192)
+
+
+@pytest.mark.parametrize("type_id", [kq.Q4_K, kq.Q6_K])
+def test_prefill_wide_shapes(type_id):
+    # the gate+up shape (4096 x 28672) at 512 tokens, CPU path on a sample of the rows
+    run_gemm(type_id, 512, 28672, 4096, packed=real_packed(type_id, 28672, 4096), seed=3, real=True, sample_rows=96)
 
 
 def test_rows_are_independent():

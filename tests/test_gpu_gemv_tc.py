@@ -5,7 +5,9 @@ d = f16(amax / 127), q = roundf(x / d) (mmvq_gguf/mmvq_quantize.cu:157-190), exa
 block scales applied in f32. Gates:
   * against that arithmetic in double (weights dequantized by the oracle times d * q): only the f32 scale products,
     their summation order and the output rounding differ;
-  * per tensor against the reference CPU path (Q8_K / Q8_0 activations): max|d| <= 1e-3 + 1e-2 max|ref|.
+  * per tensor against the reference CPU path (Q8_K / Q8_0 activations): max|d| <= 1e-3 + 1e-2 max|ref|;
+  * against the reference's own tensor-core matvec (oracle/_ref: launch_mmvq_tc_quantize_* +
+    launch_mmvq_tc_gguf_{q4_k,q6_k}_*_plain, compiled from the reference checkout), the same arithmetic.
 """
 import numpy as np
 import pytest
@@ -13,9 +15,12 @@ import torch
 
 from oracle import kquants as kq
 
+from oracle import refkernels as rk
+
 from inference_rs_b200 import kernel_library as kl
 from inference_rs_b200 import ops
-from gpu_util import DT, TYPES, as_f32_numpy, assert_device_ok, random_packed, seeded_acts, seeded_weights
+from gpu_util import (DT, Q8_1_VS_CPU_PASS_FLOOR, TYPES, as_f32_numpy, assert_device_ok, elementwise_pass_rate, random_packed,
+                      real_packed, seeded_acts, seeded_weights)
 
 pytestmark = pytest.mark.gpu
 
@@ -41,8 +46,9 @@ def requantized(x32):
     return (dh * q.astype(np.float64)).reshape(m, k)
 
 
-def run_tc(type_id, m, n, k, dtype=torch.bfloat16, packed=None, seed=0, check_cpu=True, scale=1.0):
-    real = packed is None
+def run_tc(type_id, m, n, k, dtype=torch.bfloat16, packed=None, seed=0, check_cpu=True, scale=1.0, real=None):
+    if real is None:
+        real = packed is None
     if packed is None:
         packed = kq.quantize(type_id, seeded_weights(n, k, 5000 + seed))
     x = (seeded_acts(m, k, 6000 + seed, torch.float32) * scale).to(dtype)
@@ -64,6 +70,16 @@ def run_tc(type_id, m, n, k, dtype=torch.bfloat16, packed=None, seed=0, check_cp
         # noise, which for short rows and hundreds of thousands of outputs reaches the 1 % line by itself
         rel = 1e-2 if (real and k >= 1024) else 2e-2
         assert np.abs(got - cpu).max() <= 1e-3 + rel * np.abs(cpu).max()
+        if real and k >= 1024 and m * n >= 4096:
+            assert elementwise_pass_rate(got, cpu) >= Q8_1_VS_CPU_PASS_FLOOR[type_id]
+    if rk.available() and type_id != kq.Q8_0 and scale == 1.0:
+        # the reference's tier on the same inputs (it has no Q8_0 instance): f32 scale products in another order
+        xd = x.cuda().contiguous()
+        theirs = as_f32_numpy(rk.tc_plain(type_id, w_dev, rk.tc_quantize(xd), n, k, m, dtype)).astype(np.float64)
+        torch.cuda.synchronize()
+        # (two separately rounded outputs may sit one unit of the output type apart: 2 eps)
+        off = np.abs(got - theirs) > 1e-4 * size + 2 * EPS[dtype] * 1.01 * np.abs(ref)
+        assert not off.any(), f"{off.sum()} outputs differ from the reference's tensor-core matvec, worst {np.abs(got - theirs).max():.3e} vs {size:.3e}"
     return y
 
 
@@ -82,11 +98,13 @@ def test_other_activation_types(type_id, dtype):
     run_tc(type_id, 7, 512, k_for(type_id, 768), dtype=dtype)
 
 
-@pytest.mark.parametrize("type_id", [kq.Q4_K, kq.Q6_K])
-@pytest.mark.parametrize("k,n", [(4096, 4096), (14336, 4096), (4096, 14336)])
-@pytest.mark.parametrize("m", [4, 16])
-def test_decode_shapes(type_id, k, n, m):
-    run_tc(type_id, m, n, k, packed=random_packed(type_id, n, k, seed=k + n), seed=m)
+@pytest.mark.parametrize("type_id", TYPES)
+@pytest.mark.parametrize("k,n", [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096), (4096, 128256)])
+def test_decode_sweep_shapes_batch_4_and_16(type_id, k, n):
+    """BASELINE config 2 at batch 4 and 16 on all five shapes and three types, weights ~N(0, 0.02) packed by the oracle."""
+    packed = real_packed(type_id, n, k)
+    for m in (4, 16):
+        run_tc(type_id, m, n, k, packed=packed, seed=m, real=True)
 
 
 def test_zero_rows_and_large_magnitudes():
