@@ -62,6 +62,31 @@ void launch_mmvq_gguf_q6_k_f16_plain(const void* vx, const void* vy, void* dst, 
 void launch_mmvq_gguf_q6_k_f32_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x,
                                      int stride_col_y, int stride_col_dst, int b_size, void* stream);
 
+/* Small-batch tensor-core matvec, as the reference's host drives it (fast_mmvq::tiled_plain,
+ * crates/inference-quant/src/gguf/fast_mmvq.rs:2049-2126): launch_mmvq_tc_quantize_<elem> lays num_rows (1..16) rows
+ * x [num_rows][kx] out in the tier's activation format - the rows in halves of 8, per half and 32-value block 32 int2
+ * fragments, then the 8 rows' f16 scales, then their int16 sums: 288 bytes per block and half, the host's scratch
+ * (fast_mmvq.rs:94,1898-1902) - and launch_mmvq_tc_gguf_<type>_<elem>_plain computes
+ * dst[j * stride_col_dst + row] = sum_k W[row][k] * x[j][k] for j < b_size from it. `cfg` picks among the reference
+ * kernel's own launch shapes and is ignored here. Needs ncols_x a multiple of 256.
+ * Replaces crates/inference-quant/src/gguf/ffi.rs:631-652,954-998 (kernels/cuda/mmvq_gguf/mmvq_quantize.cu:148-190,
+ * mmvq_tc_k.cuh:221-388). */
+void launch_mmvq_tc_quantize_bf16(const void* x, void* vy, int kx, int num_rows, void* stream);
+void launch_mmvq_tc_quantize_f16(const void* x, void* vy, int kx, int num_rows, void* stream);
+void launch_mmvq_tc_quantize_f32(const void* x, void* vy, int kx, int num_rows, void* stream);
+void launch_mmvq_tc_gguf_q4_k_bf16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x, int stride_col_dst,
+                                         int b_size, int cfg, void* stream);
+void launch_mmvq_tc_gguf_q4_k_f16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x, int stride_col_dst,
+                                        int b_size, int cfg, void* stream);
+void launch_mmvq_tc_gguf_q4_k_f32_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x, int stride_col_dst,
+                                        int b_size, int cfg, void* stream);
+void launch_mmvq_tc_gguf_q6_k_bf16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x, int stride_col_dst,
+                                         int b_size, int cfg, void* stream);
+void launch_mmvq_tc_gguf_q6_k_f16_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x, int stride_col_dst,
+                                        int b_size, int cfg, void* stream);
+void launch_mmvq_tc_gguf_q6_k_f32_plain(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x, int stride_col_dst,
+                                        int b_size, int cfg, void* stream);
+
 /* Q8_0 weights against UNQUANTIZED activations, f32 accumulation: dst[j * nrows_x + row] = sum_k W[row][k] * y[j][k],
  * y [b_size][ncols_x] contiguous rows and dst [b_size][nrows_x], both of the suffix's type; b_size 1..8 (larger values
  * are treated as 8, as the reference's launcher does).
@@ -81,6 +106,24 @@ void launch_mmq_quantize_q8_1_D4(const void* x, const int32_t* ids, void* vy, in
 void launch_mmq_quantize_q8_1_DS4(const void* x, const int32_t* ids, void* vy, int type_x, int64_t ne00, int64_t s01,
                                   int64_t s02, int64_t s03, int64_t ne0, int64_t ne1, int64_t ne2, int64_t ne3,
                                   void* stream);
+
+/* Prefill matmul on activations quantized by launch_mmq_quantize_q8_1_{D4,DS4}: dst[token * stride_col_dst + row] =
+ * sum_k W[row][k] * (d q)[token][k] for token < ncols_y, row < nrows_x. x: packed weights, stride_row_x blocks per row;
+ * y: the 144-byte activation blocks (D4 for Q8_0 and Q6_K weights, DS4 for Q4_K: the reference's host pairs them so,
+ * crates/inference-quant/src/gguf/fast_mmq.rs:167-190); type_dst: 0 = f32, 1 = f16, 30 = bf16. tmp_fixup (the
+ * reference kernel's stream-k scratch), cc, nsm, smpbo and warp_size are accepted and not used. On tcgen05 tensor
+ * cores when ncols_x is a multiple of 256 and the packed rows are 16-byte aligned, a plain kernel otherwise.
+ * Replaces crates/inference-quant/src/gguf/ffi.rs:911-927 (kernels/cuda/mmq_gguf/mmq_gguf.cuh:3632-3875, host side
+ * fast_mmq.rs:489-512). */
+void launch_mmq_gguf_q8_0(void* tmp_fixup, const void* x, const void* y, void* dst, int64_t ncols_x, int64_t nrows_x,
+                          int64_t ncols_y, int64_t stride_row_x, int64_t stride_col_dst, int cc, int nsm, int64_t smpbo,
+                          int warp_size, int type_dst, void* stream);
+void launch_mmq_gguf_q4_k(void* tmp_fixup, const void* x, const void* y, void* dst, int64_t ncols_x, int64_t nrows_x,
+                          int64_t ncols_y, int64_t stride_row_x, int64_t stride_col_dst, int cc, int nsm, int64_t smpbo,
+                          int warp_size, int type_dst, void* stream);
+void launch_mmq_gguf_q6_k(void* tmp_fixup, const void* x, const void* y, void* dst, int64_t ncols_x, int64_t nrows_x,
+                          int64_t ncols_y, int64_t stride_row_x, int64_t stride_col_dst, int cc, int nsm, int64_t smpbo,
+                          int warp_size, int type_dst, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------
  * Part 2: status-returning API
@@ -121,7 +164,7 @@ int b200q_take_launch_status(void);
  * (wrapping) and its first / last CTA write %globaltimer nanoseconds into slots [0..15] / [16..31]: 0 start,
  * 1 barriers ready, 2 activations staged, 3 first stage landed, 4 done, 5 first weight copy issued, 6 activations
  * quantized, 7 activations in registers, 8 barriers initialised, 9 initial copies issued, 10 activation loads back,
- * 11 first stage consumed. records = 0 switches it off. */
+ * 11 first stage consumed, 12 / 13 second stage landed / consumed, 14 / 15 third stage. records = 0 switches it off. */
 int b200q_set_trace_buffer(void* dev, int records);
 
 /* One-launch decode GEMV on unquantized activations: x [b_size][stride_x] and dst [b_size][stride_dst] both of
@@ -201,7 +244,8 @@ int b200q_gemv_tc(int type, int elem, const void* w, const void* x, void* y, int
  * crates/inference-quant/src/distributed/mod.rs:516-670; distributed/layers.rs:814-1190). Every rank calls it with the
  * same n and elem; out = sum over ranks of in, added in rank order in f32, so all ranks hold identical bits; in == out
  * is allowed. `bufs` is a host array of `world` device pointers: every rank's exchange buffer as mapped in THIS
- * process (bufs[rank] is the local one), each b200q_peer_allreduce_buffer_bytes(capacity) = 1024 + 4 capacity bytes, zeroed once before
+ * process (bufs[rank] is the local one), each b200q_peer_allreduce_buffer_bytes(capacity) bytes (about 32 capacity: an inbox
+ * per source rank, half and slot), zeroed once before
  * the first call and otherwise touched only by this function; capacity (bytes, multiple of 16) bounds n * sizeof(elem).
  * Needs 16-byte aligned in / out and n * sizeof(elem) a multiple of 16; world <= 8. Device-side sequence numbers only:
  * captured calls can be replayed. A rank that never arrives makes the others give up after about a second, set the
@@ -220,6 +264,22 @@ int b200q_peer_allreduce(const void* const* bufs, int rank, int world, long long
  * no staged kernel for the shape (then: the two separate calls). world == 1 is a plain b200q_gemv. */
 int b200q_gemv_allreduce(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int b_size,
                          const void* const* bufs, int rank, int world, long long capacity, void* stream);
+
+/* Weight quantizers on the device: n f32 values at x (device memory; n a multiple of the type's block: 32 for Q8_0,
+ * 256 otherwise) -> packed blocks at out, byte for byte what the reference's CPU quantizer writes in its default mode
+ * without an importance matrix (QTensor::quantize, crates/inference-tensor/src/quantized/mod.rs:903-918; Q8_0
+ * quantized/mod.rs:43-56, Q4_K k_quants.rs:1949-2015 with utils.rs:268-361, Q6_K k_quants.rs:2590-2646 with
+ * utils.rs:135-264). The reference has device quantizers for Q6_K and Q8_0 only
+ * (crates/inference-quant/kernels/cuda/gguf_quantize/k_quantize_instance_ggufq.cu:203-242) and runs Q4_K on the host. */
+int b200q_quantize(int type, const void* x, void* out, long long n, void* stream);
+
+/* Packed rows back to values of element type `elem`: b200q_dequantize all nrows rows of K values (to_float,
+ * k_quants.rs:905-921,2096-2123,2649-2680); b200q_get_rows the rows ids[0..n_ids) of a table of nrows_w rows (the
+ * quantized embedding gather, crates/inference-tensor/src/quantized/cuda.rs:151-242; ids are device int32). An id
+ * outside the table gives a row of zeros and code 6 in the device status word. */
+int b200q_dequantize(int type, int elem, const void* w, void* out, long long nrows, int K, void* stream);
+int b200q_get_rows(int type, int elem, const void* w, const int32_t* ids, void* out, long long n_ids, int K, long long nrows_w,
+                   void* stream);
 
 /* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,
  *        item slots per lane, register-resident slots} */

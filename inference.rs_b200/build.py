@@ -25,6 +25,11 @@ NVCC_FLAGS = [
 ]
 
 
+# per-file additions: the weight quantizers repeat the reference's scale searches operation for operation, which rules out
+# contracting a multiply and an add into one fused operation
+EXTRA_FLAGS = {"quantize_weights.cu": ["-fmad=false"]}
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.exists(cand):
@@ -44,6 +49,7 @@ def _headers_digest() -> str:
                 h.update(f.encode())
                 h.update(fh.read())
     h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(repr(sorted(EXTRA_FLAGS.items())).encode())
     return h.hexdigest()
 
 
@@ -53,7 +59,7 @@ def _stamp(src: str, hdr: str) -> str:
 
 
 def _compile(nvcc: str, src: str, obj: str, extra: list[str]) -> tuple[str, str]:
-    cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", src, "-o", obj]
+    cmd = [nvcc, *NVCC_FLAGS, *EXTRA_FLAGS.get(os.path.basename(src), []), *extra, "-c", src, "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{res.stdout}\n{res.stderr}")

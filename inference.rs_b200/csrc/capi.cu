@@ -18,6 +18,9 @@ int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int
 int gemv_tc_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace, cudaStream_t s);
 size_t gemv_tc_workspace_bytes(int type, int K);
 long long peer_allreduce_buffer_bytes(long long capacity);
+int quantize_weights(int type, const float* x, void* out, long long n, cudaStream_t s);
+int dequantize_rows(int type, int elem, const void* w, const int* ids, void* out, long long nrows_out, int K, long long nrows_w,
+                    cudaStream_t s);
 int fill_peer_exchange(PeerExchange& px, const void* const* bufs, int rank, int world, long long capacity);
 int peer_allreduce(const void* const* bufs, int rank, int world, long long capacity, int elem, const void* in, void* out, long long n,
                    cudaStream_t s);
@@ -169,7 +172,8 @@ int b200q_gemm(int type, int elem, const void* w, const void* x, void* y, int M,
     if (elem != ELEM_BF16 && elem != ELEM_F16) return set_error(B200Q_ERR_UNSUPPORTED, "b200q_gemm takes bf16 or f16 activations");
     const int rc = gemm_dispatch(type, elem, w, x, y, M, N, K, ldx, ldy, (cudaStream_t)stream);
     if (rc == B200Q_ERR_UNSUPPORTED)
-        return set_error(rc, "b200q_gemm needs K a multiple of 64 and of the block size, 16-byte aligned activation rows and Q4_K weights");
+        return set_error(rc, "b200q_gemm needs K a multiple of 64 and of the weight type's block size, x 16-byte aligned with ldx * 2 a "
+                             "multiple of 16, weights 2-byte aligned (Q4_K: 16-byte), and a driver that provides cuTensorMapEncodeTiled");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "gemm failed");
     return B200Q_OK;
 }
@@ -223,6 +227,35 @@ int b200q_gemv_allreduce(int type, int elem, const void* w, const void* x, void*
     if (fill_peer_exchange(px, bufs, rank, world, capacity) != 0)
         return set_error(B200Q_ERR_INVALID, "b200q_gemv_allreduce: 1..8 ranks, 16-byte aligned buffers, capacity a multiple of 16");
     return gemv_one_launch(type, elem, w, x, dst, K, N, K, N, b_size, 0, world > 1 ? &px : nullptr, stream);
+}
+
+// f32 values on the device -> packed blocks, byte for byte the reference CPU quantizer's (default mode).
+int b200q_quantize(int type, const void* x, void* out, long long n, void* stream) {
+    if (!x || !out) return set_error(B200Q_ERR_INVALID, "null pointer");
+    const int rc = quantize_weights(type, static_cast<const float*>(x), out, n, (cudaStream_t)stream);
+    if (rc == B200Q_ERR_UNSUPPORTED) return set_error(rc, "weight type is not Q8_0, Q4_K or Q6_K");
+    if (rc == B200Q_ERR_INVALID) return set_error(rc, "the number of values is not a multiple of the block size");
+    if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "quantize failed");
+    return B200Q_OK;
+}
+
+// Packed rows -> values of element type `elem`: all rows (to_float), or the rows `ids` names (embedding gather).
+int b200q_dequantize(int type, int elem, const void* w, void* out, long long nrows, int K, void* stream) {
+    if (!w || !out) return set_error(B200Q_ERR_INVALID, "null pointer");
+    const int rc = dequantize_rows(type, elem, w, nullptr, out, nrows, K, nrows, (cudaStream_t)stream);
+    if (rc == B200Q_ERR_UNSUPPORTED) return set_error(rc, "weight type is not Q8_0, Q4_K or Q6_K");
+    if (rc == B200Q_ERR_INVALID) return set_error(rc, "b200q_dequantize: K must be a multiple of the block size, elem f32 / f16 / bf16");
+    if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "dequantize failed");
+    return B200Q_OK;
+}
+
+int b200q_get_rows(int type, int elem, const void* w, const int32_t* ids, void* out, long long n_ids, int K, long long nrows_w, void* stream) {
+    if (!w || !out || !ids) return set_error(B200Q_ERR_INVALID, "null pointer");
+    const int rc = dequantize_rows(type, elem, w, ids, out, n_ids, K, nrows_w, (cudaStream_t)stream);
+    if (rc == B200Q_ERR_UNSUPPORTED) return set_error(rc, "weight type is not Q8_0, Q4_K or Q6_K");
+    if (rc == B200Q_ERR_INVALID) return set_error(rc, "b200q_get_rows: K must be a multiple of the block size, elem f32 / f16 / bf16");
+    if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "get_rows failed");
+    return B200Q_OK;
 }
 
 // out[10] = {staged, grid, smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,

@@ -44,6 +44,7 @@ enum DeviceStatus : unsigned int {
     STATUS_WAIT_MMA_TIMEOUT = 3,    // the epilogue gave up waiting for the tensor core
     STATUS_WAIT_DRAIN_TIMEOUT = 4,  // copies still in flight at exit did not land in time
     STATUS_WAIT_PEER_TIMEOUT = 5,   // a peer rank's flag did not arrive in time
+    STATUS_BAD_ROW_ID = 6,          // a row gather was given an id outside the table (that output row is zero)
 };
 
 // The word lives in one translation unit (runtime.cu); kernels receive its device address as a parameter

@@ -37,6 +37,11 @@ struct GemmParams {
     int ldy;
     int row_bytes;
     unsigned int* status;
+    // AQ kernels: activations arrive already quantized, as the reference's prefill quantizer lays them out (144-byte
+    // blocks of 128 values of one token: 16 bytes of scales, then 128 int8; block (k / 128) * M + token;
+    // crates/inference-quant/kernels/cuda/mmq_gguf/mmq_gguf.cuh:70-89, mmq_quantize.cu:126-131)
+    const uint8_t* aq;
+    int aq_ds4;  // scales are four half2 (d, sum) instead of four f32 d
 };
 
 template <typename T> struct ElemFormat;  // tcgen05 kind::f16 operand format code
@@ -486,10 +491,38 @@ template <> struct RawDequant<TYPE_Q6_K> {
 //   warp 0  TMA producer of the activations       warps 4-11           dequantization
 //   warp 1  tcgen05.mma issuer                    warps 12-(11 + 4 MT) epilogue
 //   warp 2  TMEM allocation                       warp 3               packed-row copies
-template <int MT> constexpr int gemm2_threads() { return 32 * (4 + GEMM_DEQ_WARPS + 4 * MT); }
+//   AQ: warps (12 + 4 MT) .. (11 + 8 MT) expand quantized activations (d * q from the reference's 144-byte blocks) into
+//   the A stages instead of warp 0's TMA loads; OutT is the output type (the operands stay 16-bit).
+template <int MT, bool AQ = false> constexpr int gemm2_threads() { return 32 * (4 + GEMM_DEQ_WARPS + 4 * MT + (AQ ? 4 * MT : 0)); }
 
-template <int TYPE, typename T, int MT>
-__global__ void __launch_bounds__(gemm2_threads<MT>(), 1) gemm_tcgen05_staged_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+// 32 accumulator columns of one token row -> global memory in OutT
+template <typename OutT>
+__device__ __forceinline__ void store_row32(OutT* yrow, int col0, int N, bool vec_ok, const uint32_t (&acc)[32]) {
+    if (vec_ok && col0 + 32 <= N) {
+        if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<uint4*>(yrow + col0 + 4 * q) = make_uint4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack2<OutT>(__uint_as_float(acc[8 * q]), __uint_as_float(acc[8 * q + 1]));
+                o.y = pack2<OutT>(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3]));
+                o.z = pack2<OutT>(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5]));
+                o.w = pack2<OutT>(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7]));
+                *reinterpret_cast<uint4*>(yrow + col0 + 8 * q) = o;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) yrow[col0 + j] = from_float<OutT>(__uint_as_float(acc[j]));
+    }
+}
+
+template <int TYPE, typename T, int MT, bool AQ = false, typename OutT = T>
+__global__ void __launch_bounds__(gemm2_threads<MT, AQ>(), 1) gemm_tcgen05_staged_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
     using RC = RawChunk<TYPE>;
     constexpr int RAW_BYTES = GEMM_BN * RC::PITCH + 64;  // + slack: reads may run a few bytes past the last row's slot
     extern __shared__ uint8_t gemm_smem_raw[];
@@ -510,7 +543,7 @@ __global__ void __launch_bounds__(gemm2_threads<MT>(), 1) gemm_tcgen05_staged_ke
 
     if (tid == 0) {
         for (int s = 0; s < GEMM2_STAGES; ++s) {
-            mbar_init(&bars->full_a[s], 1);
+            mbar_init(&bars->full_a[s], AQ ? 4 * MT : 1);
             mbar_init(&bars->full_b[s], GEMM_DEQ_WARPS);
             mbar_init(&bars->empty[s], 1);
         }
@@ -532,7 +565,7 @@ __global__ void __launch_bounds__(gemm2_threads<MT>(), 1) gemm_tcgen05_staged_ke
 
     if (warp == 0) {
         // ---------------- TMA producer of the activations ----------------
-        if (lane == 0) {
+        if (lane == 0 && !AQ) {
             int kbg = 0;  // k-blocks issued so far, over all tiles
             bool ok = true;
             for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
@@ -694,12 +727,12 @@ __global__ void __launch_bounds__(gemm2_threads<MT>(), 1) gemm_tcgen05_staged_ke
                 if (lane == 0) mbar_arrive(&bars->raw_empty[rs]);  // this warp has read the chunk
             }
         }
-    } else if (warp >= 4 + GEMM_DEQ_WARPS) {
+    } else if (warp >= 4 + GEMM_DEQ_WARPS && warp < 4 + GEMM_DEQ_WARPS + 4 * MT) {
         // ---------------- epilogue: one warp per 32 token rows of a sub-tile ----------------
         const int e = warp - (4 + GEMM_DEQ_WARPS);
         const int t = e >> 2;
         const int quarter = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4)
-        const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && ((size_t)p.ldy * sizeof(T) % 16 == 0);
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(p.y) % 16 == 0) && ((size_t)p.ldy * sizeof(OutT) % 16 == 0);
         bool ok = true;
         int ti = 0;
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++ti) {
@@ -714,33 +747,65 @@ __global__ void __launch_bounds__(gemm2_threads<MT>(), 1) gemm_tcgen05_staged_ke
             if (!ok) break;
             tc_fence_after();
             const int row = m0 + t * GEMM_BM + quarter * 32 + lane;
-            T* yrow = reinterpret_cast<T*>(p.y) + (size_t)row * p.ldy;
+            OutT* yrow = reinterpret_cast<OutT*>(p.y) + (size_t)row * p.ldy;
 #pragma unroll 1
             for (int c = 0; c < GEMM_BN / 32; ++c) {
                 uint32_t acc[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BUF_COLS + t * GEMM_BN + c * 32, acc);
-                const int col0 = n0 + c * 32;
-                if (row < p.M) {
-                    if (vec_ok && col0 + 32 <= p.N) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint4 o;
-                            o.x = pack2<T>(__uint_as_float(acc[8 * q]), __uint_as_float(acc[8 * q + 1]));
-                            o.y = pack2<T>(__uint_as_float(acc[8 * q + 2]), __uint_as_float(acc[8 * q + 3]));
-                            o.z = pack2<T>(__uint_as_float(acc[8 * q + 4]), __uint_as_float(acc[8 * q + 5]));
-                            o.w = pack2<T>(__uint_as_float(acc[8 * q + 6]), __uint_as_float(acc[8 * q + 7]));
-                            *reinterpret_cast<uint4*>(yrow + col0 + 8 * q) = o;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.N) yrow[col0 + j] = from_float<T>(__uint_as_float(acc[j]));
-                    }
-                }
+                if (row < p.M) store_row32<OutT>(yrow, n0 + c * 32, p.N, vec_ok, acc);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->tmem_empty[buf]);  // the accumulators are in registers or stored: reuse the buffer
+        }
+    } else if (AQ && warp >= 4 + GEMM_DEQ_WARPS + 4 * MT) {
+        // ---------------- quantized activations -> A stages: thread = token row of the tile, both 32-k halves of a k-block.
+        // d * q is formed in f32 and rounded once to the operand type, as the dequantized weights are. ----------------
+        const int c = tid - 32 * (4 + GEMM_DEQ_WARPS + 4 * MT);
+        const int t = c >> 7, r = c & (GEMM_BM - 1);
+        bool ok = true;
+        int kbg = 0;
+        for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            const int m0 = (tile / nx) * (MT * GEMM_BM);
+            const int token = m0 + t * GEMM_BM + r;
+            const bool token_ok = token < p.M;
+            for (int kb = 0; kb < nkb; ++kb, ++kbg) {
+                const int s = kbg % GEMM2_STAGES;
+                // the block of 128 k this k-block lies in; loads go out before the wait for the stage
+                const uint8_t* blk = p.aq + ((size_t)(kb >> 1) * p.M + (token_ok ? token : 0)) * MMQ_BLOCK_BYTES;
+                const uint4 sc = __ldg(reinterpret_cast<const uint4*>(blk));
+                uint4 qv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qv[i] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 64 * (kb & 1)) + i);
+                const bool free_now = mbar_try_wait(&bars->empty[s], ((kbg / GEMM2_STAGES) & 1) ^ 1);
+                if (!free_now && !mbar_wait_bounded(&bars->empty[s], ((kbg / GEMM2_STAGES) & 1) ^ 1)) {
+                    record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, 5000 + kbg);
+                    ok = false;
+                }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
+                const uint32_t a_addr = smem_u32(a_stages + (size_t)(s * MT + t) * GEMM_A_BYTES);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t sw = scw[2 * (kb & 1) + h];
+                    const float d = token_ok ? (p.aq_ds4 ? half_bits_to_float(sw) : __uint_as_float(sw)) : 0.0f;
+                    const uint32_t w8[8] = {qv[2 * h].x, qv[2 * h].y, qv[2 * h].z, qv[2 * h].w, qv[2 * h + 1].x, qv[2 * h + 1].y, qv[2 * h + 1].z, qv[2 * h + 1].w};
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t u = w8[i] ^ 0x80808080u;  // q + 128 as unsigned bytes
+                        v[4 * i + 0] = d * (byte_as_magic<0>(u) - 8388736.0f);  // 2^23 + 128
+                        v[4 * i + 1] = d * (byte_as_magic<1>(u) - 8388736.0f);
+                        v[4 * i + 2] = d * (byte_as_magic<2>(u) - 8388736.0f);
+                        v[4 * i + 3] = d * (byte_as_magic<3>(u) - 8388736.0f);
+                    }
+                    store_unit<T>(a_addr, r, h, v);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->full_a[s]);
+            }
         }
     }
     tc_fence_before();
@@ -748,12 +813,77 @@ __global__ void __launch_bounds__(gemm2_threads<MT>(), 1) gemm_tcgen05_staged_ke
     if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// Prefill matmul on quantized activations for shapes the tile kernel does not take (K not a multiple of 256, packed
+// rows that are not a multiple of 16 bytes, unaligned weights): a warp per weight row and 8 tokens, 32-value blocks over
+// the lanes, integer dot products per block with the block scales applied in f32 - the reference MMQ's arithmetic.
+template <int TYPE, typename OutT>
+__global__ void __launch_bounds__(256) mmq_simple_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ aq, OutT* __restrict__ y,
+                                                         int M, int N, int K, int ldy, int row_bytes, int ds4) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int tok0 = blockIdx.y * 8;
+    if (row >= N) return;
+    const uint8_t* rp = w + (size_t)row * row_bytes;
+    float acc[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) acc[t] = 0.0f;
+    for (int kb = lane; kb < K / 32; kb += 32) {
+        int wq[32];
+        float s0 = 0.0f, s1 = 0.0f, mn = 0.0f;  // Q4_K: s0 = d sc, mn = dmin m; Q6_K: s0, s1 = d sc of the two halves; Q8_0: s0 = d
+        if (TYPE == TYPE_Q8_0) {
+            const uint8_t* b = rp + (size_t)kb * Q8_0_BYTES;
+            s0 = half_bits_to_float((uint32_t)b[0] | ((uint32_t)b[1] << 8));
+            for (int l = 0; l < 32; ++l) wq[l] = (int)(int8_t)b[2 + l];
+        } else if (TYPE == TYPE_Q4_K) {
+            const int j = kb & 7;
+            const uint8_t* sb = rp + (size_t)(kb >> 3) * Q4_K_BYTES;
+            const uint8_t* q = sb + 4;
+            int sc, m;
+            if (j < 4) { sc = q[j] & 63; m = q[j + 4] & 63; }
+            else { sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4); m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+            s0 = half_bits_to_float((uint32_t)sb[0] | ((uint32_t)sb[1] << 8)) * (float)sc;
+            mn = half_bits_to_float((uint32_t)sb[2] | ((uint32_t)sb[3] << 8)) * (float)m;
+            const uint8_t* qs = sb + 16 + 32 * (j >> 1);
+            for (int l = 0; l < 32; ++l) wq[l] = (j & 1) ? (qs[l] >> 4) : (qs[l] & 0xF);
+        } else {
+            const int n = (kb >> 2) & 1, qd = kb & 3;
+            const uint8_t* sb = rp + (size_t)(kb >> 3) * Q6_K_BYTES;
+            const uint8_t* ql = sb + 64 * n + 32 * (qd & 1);
+            const uint8_t* qh = sb + 128 + 32 * n;
+            for (int l = 0; l < 32; ++l) {
+                const int lo = (qd & 2) ? (ql[l] >> 4) : (ql[l] & 0xF);
+                wq[l] = (lo | (((qh[l] >> (2 * qd)) & 3) << 4)) - 32;
+            }
+            const float d = half_bits_to_float((uint32_t)sb[208] | ((uint32_t)sb[209] << 8));
+            s0 = d * (float)(int)(int8_t)sb[192 + 8 * n + 2 * qd];
+            s1 = d * (float)(int)(int8_t)sb[192 + 8 * n + 2 * qd + 1];
+        }
+        for (int t = 0; t < 8; ++t) {
+            const int token = tok0 + t;
+            if (token >= M) break;
+            const uint8_t* blk = aq + ((size_t)(kb >> 2) * M + token) * MMQ_BLOCK_BYTES;
+            const int8_t* aqv = reinterpret_cast<const int8_t*>(blk + 16 + 32 * (kb & 3));
+            const float xd = ds4 ? half_bits_to_float(reinterpret_cast<const uint32_t*>(blk)[kb & 3]) : reinterpret_cast<const float*>(blk)[kb & 3];
+            int d0 = 0, d1 = 0, sum = 0;
+            for (int l = 0; l < 16; ++l) { d0 += wq[l] * (int)aqv[l]; sum += (int)aqv[l]; }
+            for (int l = 16; l < 32; ++l) { d1 += wq[l] * (int)aqv[l]; sum += (int)aqv[l]; }
+            if (TYPE == TYPE_Q6_K) acc[t] += xd * (s0 * (float)d0 + s1 * (float)d1);
+            else if (TYPE == TYPE_Q4_K) acc[t] += s0 * (xd * (float)(d0 + d1)) - mn * (xd * (float)sum);
+            else acc[t] += s0 * (xd * (float)(d0 + d1));
+        }
+    }
+    for (int t = 0; t < 8; ++t) {
+        const float v = warp_sum(acc[t]);
+        if (lane == 0 && tok0 + t < M) y[(size_t)(tok0 + t) * ldy + row] = from_float<OutT>(v);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
-template <int TYPE, typename T, int MT>
+template <int TYPE, typename T, int MT, bool AQ = false, typename OutT = T>
 static int launch_gemm_staged_mt(const CUtensorMap& map, const GemmParams& p, cudaStream_t s) {
-    auto kernel = gemm_tcgen05_staged_kernel<TYPE, T, MT>;
+    auto kernel = gemm_tcgen05_staged_kernel<TYPE, T, MT, AQ, OutT>;
     constexpr int RAW_STRIDE = ((GEMM_BN * RawChunk<TYPE>::PITCH + 64) + 127) & ~127;
     const size_t smem = 1024 + (size_t)GEMM2_STAGES * (MT * GEMM_A_BYTES + GEMM_B_BYTES) + (size_t)GEMM2_RAW_STAGES * RAW_STRIDE +
                         sizeof(Gemm2Barriers);
@@ -763,7 +893,7 @@ static int launch_gemm_staged_mt(const CUtensorMap& map, const GemmParams& p, cu
     if (attr_err != cudaSuccess) return (int)attr_err;
     const int ntiles = ((p.N + GEMM_BN - 1) / GEMM_BN) * ((p.M + MT * GEMM_BM - 1) / (MT * GEMM_BM));
     const int sms = runtime_info().sm_count;
-    kernel<<<ntiles < sms ? ntiles : sms, gemm2_threads<MT>(), smem, s>>>(map, p);
+    kernel<<<ntiles < sms ? ntiles : sms, gemm2_threads<MT, AQ>(), smem, s>>>(map, p);
     return (int)cudaGetLastError();
 }
 
@@ -812,6 +942,54 @@ static int launch_gemm_t(const void* w, const void* x, void* y, int M, int N, in
     return two ? launch_gemm_mt<TYPE, T, 2>(map, p, s) : launch_gemm_mt<TYPE, T, 1>(map, p, s);
 }
 
+// The reference's prefill launcher (crates/inference-quant/src/gguf/ffi.rs:911-927, called from fast_mmq.rs:489-512):
+// y[token * stride_col_dst + row] = sum_k W[row][k] * (d q)[token][k] with the activations already quantized by
+// launch_mmq_quantize_q8_1_{D4,DS4} into 144-byte blocks. The tile kernel expands d * q into its A stages (operands in
+// bf16, f32 accumulation); shapes it does not take go to mmq_simple_kernel. tmp_fixup (the reference's stream-k
+// scratch) is not needed.
+template <int TYPE, typename OutT>
+static int launch_mmq_t(const void* w, const void* aq, void* y, long long K, long long N, long long M, long long stride_row_x,
+                        long long ldy, int ds4, cudaStream_t s) {
+    if (M <= 0 || N <= 0) return 0;
+    const int be = type_block_elems(TYPE), bb = type_block_bytes(TYPE);
+    if (K <= 0 || K % be != 0 || K > (1LL << 30) || N > (1LL << 30) || M > (1LL << 30) || ldy > (1LL << 30))
+        return B200Q_ERR_UNSUPPORTED;
+    GemmParams p{};
+    p.w = static_cast<const uint8_t*>(w);
+    p.y = y;
+    p.M = (int)M;
+    p.N = (int)N;
+    p.K = (int)K;
+    p.ldy = (int)ldy;
+    p.row_bytes = (int)(stride_row_x * bb);
+    p.status = status_ptr();
+    p.aq = static_cast<const uint8_t*>(aq);
+    p.aq_ds4 = ds4;
+    const bool tile_ok = K % 256 == 0 && stride_row_x == K / be && p.row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(aq) % 16 == 0;
+    if (!tile_ok) {
+        if (reinterpret_cast<uintptr_t>(aq) % 4 != 0) return B200Q_ERR_UNSUPPORTED;
+        const dim3 grid((unsigned)((N + 7) / 8), (unsigned)((M + 7) / 8), 1);
+        mmq_simple_kernel<TYPE, OutT><<<grid, 256, 0, s>>>(p.w, p.aq, static_cast<OutT*>(y), p.M, p.N, p.K, p.ldy, p.row_bytes, ds4);
+        return (int)cudaGetLastError();
+    }
+    CUtensorMap unused_map{};  // the AQ kernels take no tensor map for the activations
+    const long long tiles2 = (long long)((N + GEMM_BN - 1) / GEMM_BN) * ((M + 2 * GEMM_BM - 1) / (2 * GEMM_BM));
+    const bool two = M > GEMM_BM && tiles2 >= runtime_info().sm_count;
+    return two ? launch_gemm_staged_mt<TYPE, __nv_bfloat16, 2, true, OutT>(unused_map, p, s)
+               : launch_gemm_staged_mt<TYPE, __nv_bfloat16, 1, true, OutT>(unused_map, p, s);
+}
+
+template <int TYPE>
+static int launch_mmq(const void* w, const void* aq, void* y, long long K, long long N, long long M, long long stride_row_x, long long ldy,
+                      int ds4, int type_dst, cudaStream_t s) {
+    // the reference's element codes (crates/inference-quant/src/gguf/fast_mmq.rs:671-676): 0 = f32, 1 = f16, 30 = bf16
+    if (type_dst == 0) return launch_mmq_t<TYPE, float>(w, aq, y, K, N, M, stride_row_x, ldy, ds4, s);
+    if (type_dst == 1) return launch_mmq_t<TYPE, __half>(w, aq, y, K, N, M, stride_row_x, ldy, ds4, s);
+    if (type_dst == 30) return launch_mmq_t<TYPE, __nv_bfloat16>(w, aq, y, K, N, M, stride_row_x, ldy, ds4, s);
+    return B200Q_ERR_INVALID;
+}
+
 int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % GEMM_BK != 0 || K % type_block_elems(type) != 0) return B200Q_ERR_UNSUPPORTED;
@@ -832,3 +1010,19 @@ int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int
 }
 
 }  // namespace b200q
+
+// The reference's symbols; void, asynchronous, allocation-free. The activation scale layout follows the weight type as in
+// the reference's host (fast_mmq.rs:167-190): Q8_0 and Q6_K blocks carry four f32 d (D4), Q4_K blocks four half2 (d, sum)
+// (DS4). cc, nsm, smpbo and warp_size describe the device to the reference's kernel and are not needed here.
+#define B200Q_MMQ_LAUNCHER(tag, TYPE, DS4)                                                                                          \
+    extern "C" void launch_mmq_gguf_##tag(void* tmp_fixup, const void* x, const void* y, void* dst, int64_t ncols_x, int64_t nrows_x, \
+                                          int64_t ncols_y, int64_t stride_row_x, int64_t stride_col_dst, int cc, int nsm,            \
+                                          int64_t smpbo, int warp_size, int type_dst, void* stream) {                                \
+        (void)tmp_fixup; (void)cc; (void)nsm; (void)smpbo; (void)warp_size;                                                          \
+        b200q::note_launch_status(b200q::launch_mmq<TYPE>(x, y, dst, ncols_x, nrows_x, ncols_y, stride_row_x, stride_col_dst, DS4,    \
+                                                          type_dst, (cudaStream_t)stream));                                          \
+    }
+B200Q_MMQ_LAUNCHER(q8_0, b200q::TYPE_Q8_0, 0)
+B200Q_MMQ_LAUNCHER(q4_k, b200q::TYPE_Q4_K, 1)
+B200Q_MMQ_LAUNCHER(q6_k, b200q::TYPE_Q6_K, 0)
+#undef B200Q_MMQ_LAUNCHER

@@ -75,7 +75,11 @@ struct GemvParams {
     int stride_dst;
     int row_bytes;
     int rows_per_stage;  // R: rows one stage holds (multiple of row_align and of the number of row groups)
+    int first_rows;      // rows of the CTA's very first stage (<= R): a smaller one lands sooner, and nothing can be
+                         // computed before it has
     int warps_per_row;   // WPR: power of two <= 16; 16 / WPR row groups work on different rows at once
+    int log2_wpr;        // shifts instead of divisions in the kernel: WPR = 1 << log2_wpr,
+    int log2_islots;     // islots (lanes that share a row inside a warp: items rounded up to a power of two, <= 32)
     int items_per_lane;  // IPL: item slots of one lane: item = (warp % WPR) * 32 + lane + j * 32 * WPR, j < IPL
     int row_align;       // rows per 16-byte-aligned unit of the byte stream
     int units_per_cta;   // CTA c owns units [c * q + min(c, r), ...) with q = units_per_cta, r = units_extra
@@ -218,7 +222,7 @@ template <int ACT, typename act_t> struct ActPrefetch {
         for (int u = 0; u < PRE_UNITS; ++u) {
             const int i = tid + u * GEMV_CONSUMER_THREADS;
             if (i < B * chunks) {
-                const int b = i / chunks, c = i - b * chunks;
+                const int b = B == 1 ? 0 : i / chunks, c = i - b * chunks;  // (no division on the single-row path)
                 const act_t* src = reinterpret_cast<const act_t*>(act) + (size_t)b * stride_elems + 8 * c;
                 if (vec) {
 #pragma unroll
@@ -263,6 +267,10 @@ B200Q_PREFETCH_GET16(ACT_RAW_CPU, __half, __half22float2, __half2)
 B200Q_PREFETCH_GET16(ACT_RAW_Q8_1, __nv_bfloat16, __bfloat1622float2, __nv_bfloat162)
 B200Q_PREFETCH_GET16(ACT_RAW_CPU, __nv_bfloat16, __bfloat1622float2, __nv_bfloat162)
 
+// roundf(v / d) with the IEEE division, kept out of line: the quantizer below needs it for the few values whose quotient
+// lies next to a rounding boundary, and eight inlined copies would sit in every launch's instruction stream
+static __device__ __noinline__ int round_div_exact(float v, float d) { return (int)roundf(v / d); }
+
 // From raw rows, quantized here. Each thread takes 8 consecutive values, so 4 lanes share a 32-value block and a warp
 // covers 256 values.
 //   ACT_RAW_Q8_1: the decode quantizer's arithmetic (d = amax / 127 rounded to f16, q = roundf(x / d)): identical to
@@ -278,17 +286,26 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
     const int nrec = K / 64;
     const int lane = tid & 31;
     constexpr bool PER_256 = (MODE == ACT_RAW_CPU) && (TYPE != TYPE_Q8_0);
-    const unsigned gmask = PER_256 ? 0xffffffffu : (0xFu << (lane & 28));
+    // The shuffles below name the whole warp: a shuffle whose mask differs between the lanes of one instruction is
+    // carried out one mask after the other and costs hundreds of cycles a piece, four times per chunk. So the loop's
+    // trip count is the same for all lanes of a warp (lanes past the end work on zeros and store nothing).
+    constexpr unsigned gmask = 0xffffffffu;
+    const int total = B * chunks;
     int u = 0;  // which of this thread's chunks
-    for (int i = tid; i < B * chunks; i += nthreads, ++u) {
+    for (int i = tid; i - lane < total; i += nthreads, ++u) {
+        const bool valid = i < total;
         // integer divisions are dozens of dependent instructions on a path every launch runs exactly once
-        const int b = B == 1 ? 0 : i / chunks, c = B == 1 ? i : i - b * chunks;
+        const int b = B == 1 ? 0 : (valid ? i / chunks : 0), c = B == 1 ? i : i - b * chunks;
         float v[8];
         if (u == 0) pre.get(0, v);
         else if (u == 1) pre.get(1, v);
         else if (u == 2) pre.get(2, v);
         else if (u == 3) pre.get(3, v);
-        else load8<src_t>(x + (size_t)b * stride_elems + 8 * c, vec, v);
+        else if (valid) load8<src_t>(x + (size_t)b * stride_elems + 8 * c, vec, v);
+        if (!valid) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+        }
         int q[8];
         float d_used;
         if (PER_256) {
@@ -320,7 +337,12 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
             for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
             amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
-            const float d = amax / 127.0f;
+            // amax / 127 correctly rounded without the division routine: multiply by the rounded reciprocal, then one
+            // residual correction (exact for every finite amax whose quotient is a normal number; smaller ones take the
+            // division, which then also matches)
+            float d = amax * 0.007874015718698502f;
+            d = fmaf(fmaf(-127.0f, d, amax), 0.007874015718698502f, d);
+            if (amax < 1e-30f) d = amax / 127.0f;
             if (MODE == ACT_RAW_CPU) {
                 const float id = d != 0.0f ? 1.0f / d : 0.0f;
 #pragma unroll
@@ -329,15 +351,22 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
                 // roundf(x / d) without eight IEEE divisions: one exact reciprocal, a residual-corrected quotient
                 // (accurate to a couple of ulp), and the exact division only where that quotient lies within 1e-3
                 // of a rounding boundary, so the result is always the one the quantize launcher computes
-                const float rcp = amax == 0.0f ? 0.0f : 1.0f / d;
+                // (the reciprocal only seeds the quotient, so the approximate one does; |q| <= 127.5, so the magic-number
+                // rounding applies)
+                const float rcp = amax == 0.0f ? 0.0f : __frcp_rn(d);
+                unsigned near_half = 0u;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float q0 = v[j] * rcp;
                     const float q1 = fmaf(fmaf(-d, q0, v[j]), rcp, q0);
-                    const float qr = rintf(q1);
-                    int qi = (int)qr;
-                    if (fabsf(q1 - qr) > 0.499f) qi = (int)roundf(v[j] / d);
-                    q[j] = amax == 0.0f ? 0 : qi;
+                    const float qr = (q1 + 12582912.0f) - 12582912.0f;  // nearest integer
+                    q[j] = amax == 0.0f ? 0 : (int)qr;
+                    near_half |= (fabsf(q1 - qr) > 0.499f) ? (1u << j) : 0u;
+                }
+                if (near_half != 0u && amax != 0.0f) {  // rare: decided by the division itself, out of line
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if ((near_half >> j) & 1u) q[j] = round_div_exact(v[j], d);
                 }
             }
             d_used = __half2float(__float2half_rn(d));
@@ -351,6 +380,7 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
                             ((uint32_t)(q[3] & 0xff) << 24);
         const uint32_t w1 = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) |
                             ((uint32_t)(q[7] & 0xff) << 24);
+        if (!valid) continue;
         uint8_t* rec = acts + ((size_t)b * nrec + (c >> 3)) * ACT_REC_BYTES;
         const int h = (c >> 2) & 1;
         *reinterpret_cast<uint2*>(rec + 32 * h + 8 * (c & 3)) = make_uint2(w0, w1);
@@ -408,13 +438,12 @@ template <> struct Weights<TYPE_Q4_K> {
             w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
         }
         // 6-bit scales and mins (crates/inference-tensor/src/quantized/utils.rs:119-129), four at a time
-        if (h == 0) {
-            sc4 = hdr.y & 0x3f3f3f3fu;
-            m4 = hdr.z & 0x3f3f3f3fu;
-        } else {
-            sc4 = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
-            m4 = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
-        }
+        // (both forms computed and selected: h alternates between neighbouring lanes, and a branch would split every warp)
+        const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, m_lo = hdr.z & 0x3f3f3f3fu;
+        const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+        const uint32_t m_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+        sc4 = h == 0 ? sc_lo : sc_hi;
+        m4 = h == 0 ? m_lo : m_hi;
         d = half_bits_to_float(hdr.x);
         dmin = half_bits_to_float(hdr.x >> 16);
     }
@@ -584,14 +613,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     GEMV_TRACE(0);
-    if (p.use_pdl) {
-        grid_launch_dependents();  // the next grid may start its own set-up now
-        if (warp != GEMV_CONSUMER_WARPS) grid_dependency_wait();  // activations come from the previous grid
-    }
-    // the first activation loads go out before anything else: issued after the weight stream has started they
-    // would queue behind megabytes of bulk copies
+    // Under programmatic dependent launch this grid may start while the previous one is still running (on the SMs that
+    // grid has left): barrier set-up and the weight stream do not depend on it and go ahead; only the consumers wait
+    // for it - after the CTA-wide barrier below, so that they do not hold the producer back - before they touch the
+    // activations it wrote.
+    if (p.use_pdl) grid_launch_dependents();  // and the grid after this one may start its own set-up
+    // Without it, the first activation loads go out before anything else: issued after the weight stream has started
+    // they would queue behind megabytes of bulk copies.
     ActPrefetch<ACT, act_t> pre;
-    if (warp != GEMV_CONSUMER_WARPS) pre.issue(p.act, B, p.K, p.stride_act, p.act_vec != 0, tid);
+    if (!p.use_pdl && warp != GEMV_CONSUMER_WARPS) pre.issue(p.act, B, p.K, p.stride_act, p.act_vec != 0, tid);
 
     // this CTA's rows: a contiguous run of 16-byte-aligned units, sizes differing by at most one unit
     const int cta = blockIdx.x;
@@ -599,13 +629,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
     const int row0 = unit0 * p.row_align;
     int row1 = (unit0 + p.units_per_cta + (cta < p.units_extra ? 1 : 0)) * p.row_align;
     if (row1 > p.N) row1 = p.N;
-    const int nrows = row1 > row0 ? row1 - row0 : 0;
-    const int niter = (nrows + R - 1) / R;
+    if (row1 < row0) row1 = row0;  // the stages of this CTA are the row offsets row0, row0 + R, ... below row1
 
     // The producer thread sets the barriers up and starts the weight stream at once; weights never depend on the
     // previous grid, so under programmatic dependent launch this runs while that grid is still computing.
     const bool is_producer = (warp == GEMV_CONSUMER_WARPS);
     int issued = 0;
+    int next_row = row0;  // producer: first row not yet requested
     if (is_producer && lane == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&full[s], 1);
@@ -613,20 +643,24 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         }
         GEMV_TRACE_ANY(8);
         mbar_init_fence();
+    }
+    for (int i = tid; i < counter_ints; i += GEMV_THREADS) counters[i] = 0;
+    __syncthreads();  // barriers initialised: the consumers go on to their activations, the producer to its copies
+    GEMV_TRACE(1);
+    if (is_producer && lane == 0) {
         GEMV_TRACE_ANY(5);
-        for (; issued < niter && issued < S; ++issued) {
-            const int r = row0 + issued * R;
-            const int rows = min(R, row1 - r);
+        int r = row0;
+        for (; r < row1 && issued < S; ++issued) {
+            const int rows = min(issued == 0 ? p.first_rows : R, row1 - r);
             const uint32_t bytes = ((uint32_t)rows * (uint32_t)p.row_bytes + 15u) & ~15u;
             mbar_arrive_expect_tx(&full[issued], bytes);
             bulk_copy_g2s(ring + (size_t)issued * p.stage_bytes, p.w + (size_t)r * p.row_bytes, bytes, &full[issued]);
+            r += rows;
         }
+        next_row = r;
         GEMV_TRACE_ANY(9);
-        if (issued >= niter) prefetch_successor(p.next, cta);  // everything of this CTA is already on its way
+        if (r >= row1) prefetch_successor(p.next, cta);  // everything of this CTA is already on its way
     }
-    for (int i = tid; i < counter_ints; i += GEMV_THREADS) counters[i] = 0;
-    __syncthreads();
-    GEMV_TRACE(1);
 
     if (is_producer) {
         // ---------------- producer: refills stages as the consumers release them ----------------
@@ -634,16 +668,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
             bool ok = true;
             int s = 0;          // the refills start over at stage 0 (issued == S here whenever this loop runs)
             uint32_t ph = 0;    // parity of the consumers' first release of each stage
-            for (int it = issued; it < niter && ok; ++it) {
+            for (int it = issued, r = next_row; r < row1 && ok; ++it, r += R) {
                 ok = mbar_wait_bounded(&empty[s], ph);
                 if (!ok) { record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, it); break; }
-                const int r = row0 + it * R;
                 const int rows = min(R, row1 - r);
                 const uint32_t bytes = ((uint32_t)rows * (uint32_t)p.row_bytes + 15u) & ~15u;
                 mbar_arrive_expect_tx(&full[s], bytes);
                 bulk_copy_g2s(ring + (size_t)s * p.stage_bytes, p.w + (size_t)r * p.row_bytes, bytes, &full[s]);
                 issued = it + 1;
-                if (issued == niter) prefetch_successor(p.next, cta);
+                if (r + R >= row1) prefetch_successor(p.next, cta);
                 if (++s == S) {
                     s = 0;
                     ph ^= 1u;
@@ -664,6 +697,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
     }
 
     // ---------------- consumers ----------------
+    if (p.use_pdl) {
+        grid_dependency_wait();  // the previous grid has finished and its stores are visible
+        pre.issue(p.act, B, p.K, p.stride_act, p.act_vec != 0, tid);
+    }
     if (p.trace != nullptr && tid == 0) {  // when this thread's first activation load has come back
         if constexpr (ACT == ACT_Q8_1) asm volatile("" ::"r"(pre.v[0]));
         else asm volatile("" ::"r"(pre.raw[0][0]));
@@ -680,12 +717,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
 
     const int nrec = p.K / 64;
     const int items = p.K / 128;
-    int islots = 32;                       // lanes that share one row inside a warp
-    while (islots > 1 && (islots >> 1) >= items) islots >>= 1;
-    const int rpw = 32 / islots;           // rows a warp works on at once
-    const int lane_i = lane & (islots - 1), lane_r = lane / islots;
-    const int nrg = GEMV_CONSUMER_WARPS / WPR;  // warp groups working on different rows
-    const int wgroup = warp / WPR, wslice = warp % WPR;
+    const int islots = 1 << p.log2_islots;  // lanes that share one row inside a warp
+    const int rpw = 32 >> p.log2_islots;    // rows a warp works on at once
+    const int lane_i = lane & (islots - 1), lane_r = lane >> p.log2_islots;
+    const int nrg = GEMV_CONSUMER_WARPS >> p.log2_wpr;  // warp groups working on different rows
+    const int wgroup = warp >> p.log2_wpr, wslice = warp & (WPR - 1);
     const int row_slot = wgroup * rpw + lane_r;  // this lane's row within a pass of nrg * rpw rows
     const int rows_per_pass = nrg * rpw;
     const int item0 = wslice * 32 + lane_i;
@@ -704,22 +740,45 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                 if (item0 + j * item_step < items) areg[b][j].load(acts_addr + b * act_row_bytes, item0 + j * item_step);
     }
 
+    // Row-parallel matmul with the exchange fused in: every output is pushed, as it is produced, into this rank's inbox
+    // in EVERY rank's exchange buffer (plain peer stores over NVLink, the own buffer included); the last CTA to finish
+    // then only raises the flags, waits for the peers' and adds the inboxes of the local buffer (peer_allreduce.cuh).
+    unsigned int ar_epoch = 0;
+    long long ar_inbox = 0;
+    if constexpr (AR) {
+        // the call number: one more than the finished calls (written by the last CTA of the previous launch, which this
+        // grid was ordered after - by the stream, or by grid_dependency_wait above under programmatic launch)
+        ar_epoch = *reinterpret_cast<volatile unsigned int*>(p.px.bufs[p.px.rank] + PAR_EPOCH_OFFSET + 4 * PAR_FUSED_BLOCK) + 1u;
+        ar_inbox = par_fused_inbox_offset(p.px.capacity, ar_epoch & 1u, p.px.rank);
+    }
+    auto store_out = [&](int b, int row, float v) {
+        if constexpr (AR) {
+            const dst_t o = from_float<dst_t>(v);
+            const size_t at = (size_t)ar_inbox + ((size_t)b * p.N + row) * sizeof(dst_t);
+            for (int r = 0; r < p.px.world; ++r) *reinterpret_cast<dst_t*>(p.px.bufs[r] + at) = o;
+        } else {
+            dst[(size_t)b * p.stride_dst + row] = from_float<dst_t>(v);
+        }
+    };
     GEMV_TRACE(7);
     bool alive = true;
     // ring position and row rotation kept incrementally: the loop has no integer division
     int s = 0;
     uint32_t ph = 0;
     int rot = 0;
-    const int rot_step = R % rows_per_pass;
-    for (int it = 0; it < niter; ++it) {
+    int rot_step = R;  // R mod rows_per_pass (R is at most a few passes)
+    while (rot_step >= rows_per_pass) rot_step -= rows_per_pass;
+    int first_rot_step = p.first_rows;
+    while (first_rot_step >= rows_per_pass) first_rot_step -= rows_per_pass;
+    for (int it = 0, rbase = row0; rbase < row1; rbase += (it == 0 ? p.first_rows : R), ++it) {
         if (alive && !mbar_wait_bounded(&full[s], ph)) {
             record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, it);
             alive = false;  // keep arriving so that the others are not held up, but compute nothing
         }
         if (it == 0) GEMV_TRACE(3);
+        else if (it <= 2) GEMV_TRACE(10 + 2 * it);  // 12, 14: stages 1 and 2 landed
         const uint32_t st = ring_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
-        const int rbase = row0 + it * R;
-        const int rows_here = min(R, row1 - rbase);
+        const int rows_here = min(it == 0 ? p.first_rows : R, row1 - rbase);
         // rows of consecutive stages go to consecutive warp groups, so a stage may hold fewer rows than one pass of
         // all warps without leaving the same warps idle every time
         const int my_slot = row_slot >= rot ? row_slot - rot : row_slot - rot + rows_per_pass;
@@ -772,7 +831,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                     if (lane_i == 0 && has_row[u]) {
                         if (WPR == 1) {
 #pragma unroll
-                            for (int b = 0; b < B; ++b) dst[(size_t)b * p.stride_dst + rbase + r_in[u]] = from_float<dst_t>(acc[u][b]);
+                            for (int b = 0; b < B; ++b) store_out(b, rbase + r_in[u], acc[u][b]);
                         } else {
                             // the last of the WPR warps to arrive adds the partial sums in slice order and writes the row
                             float* part = partial + ((size_t)(s * R + r_in[u]) * WPR) * B;
@@ -787,7 +846,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                                 for (int b = 0; b < B; ++b) {
                                     float v = 0.0f;
                                     for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w * B + b];
-                                    dst[(size_t)b * p.stride_dst + rbase + r_in[u]] = from_float<dst_t>(v);
+                                    store_out(b, rbase + r_in[u], v);
                                 }
                             }
                         }
@@ -828,7 +887,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                 if (lane_i == 0 && has_row) {
                     if (WPR == 1) {
 #pragma unroll
-                        for (int b = 0; b < B; ++b) dst[(size_t)b * p.stride_dst + rbase + r_in] = from_float<dst_t>(acc[b]);
+                        for (int b = 0; b < B; ++b) store_out(b, rbase + r_in, acc[b]);
                     } else {
                         // the last of the WPR warps to arrive adds the partial sums in slice order and writes the row
                         float* part = partial + ((size_t)(s * R + r_in) * WPR) * B;
@@ -843,7 +902,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                             for (int b = 0; b < B; ++b) {
                                 float v = 0.0f;
                                 for (int w = 0; w < WPR; ++w) v += reinterpret_cast<volatile float*>(part)[w * B + b];
-                                dst[(size_t)b * p.stride_dst + rbase + r_in] = from_float<dst_t>(v);
+                                store_out(b, rbase + r_in, v);
                             }
                         }
                     }
@@ -853,18 +912,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
         if (it == 0) GEMV_TRACE(11);
+        else if (it <= 2) GEMV_TRACE(11 + 2 * it);  // 13, 15: stages 1 and 2 consumed
         if (++s == S) {
             s = 0;
             ph ^= 1u;
         }
-        rot += rot_step;
+        rot += it == 0 ? first_rot_step : rot_step;
         if (rot >= rows_per_pass) rot -= rows_per_pass;
     }
     if constexpr (AR) {
-        // fused exchange: the CTA that finishes last (device-wide arrival counter in the exchange buffer) sums the
-        // output over the ranks through peer memory, in place; no second launch, no second trip through the host queue
+        // the CTA that finishes last (device-wide arrival counter in the exchange buffer) completes the exchange: no
+        // second launch, no second trip through the host queue, one NVLink crossing on the critical path
         __shared__ unsigned int s_px[3];
-        __threadfence();  // this CTA's outputs, before it is counted
+        __threadfence_system();  // this thread's pushes, at every rank, before the CTA is counted
         named_bar_sync(1, GEMV_CONSUMER_THREADS);
         if (tid == 0) {
             unsigned int* counter = reinterpret_cast<unsigned int*>(p.px.bufs[p.px.rank] + PAR_COUNTER_OFFSET);
@@ -874,10 +934,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         }
         named_bar_sync(1, GEMV_CONSUMER_THREADS);
         if (s_px[2]) {
-            __threadfence();
+            __threadfence_system();  // the other CTAs' pushes, ordered before theirs counts, before this rank's flags go up
             const long long units = (long long)B * p.N * (long long)sizeof(dst_t) / 16;
-            peer_allreduce_slice<dst_t, true>(p.px, PAR_HEADER_BYTES + 2 * (size_t)p.px.capacity, PAR_FUSED_BLOCK, p.dst, p.dst, 0, units, tid,
-                                              GEMV_CONSUMER_THREADS, p.status, s_px);
+            peer_signal_wait_reduce<dst_t, true>(p.px, PAR_FUSED_BLOCK, ar_epoch, par_fused_inbox_offset(p.px.capacity, ar_epoch & 1u, 0),
+                                                 p.px.capacity, p.dst, units, tid, GEMV_CONSUMER_THREADS, p.status, s_px);
+            if (tid == 0)
+                *reinterpret_cast<volatile unsigned int*>(p.px.bufs[p.px.rank] + PAR_EPOCH_OFFSET + 4 * PAR_FUSED_BLOCK) = ar_epoch;
         }
     }
     GEMV_TRACE(4);
@@ -906,8 +968,9 @@ struct GemvGroupParams {
     int nmat;
     const void* act;  // one raw activation row of K values
     int K;
-    int warps_per_row, items_per_lane;
+    int warps_per_row, items_per_lane, log2_wpr, log2_islots;
     int nstages, stage_bytes, act_bytes, max_rows_per_stage;
+    int first_rows[GEMV_GROUP_MAX];  // rows of the first stage of each matrix; < rows_per_stage only for the first matrix
     int use_pdl, act_vec;
     unsigned int* status;
     NextPrefetch next;
@@ -1040,12 +1103,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x;
-    if (p.use_pdl) {
-        grid_launch_dependents();
-        if (warp != GEMV_CONSUMER_WARPS) grid_dependency_wait();
-    }
+    // programmatic dependent launch: as in gemv_staged_kernel, only the consumers wait for the previous grid, and only
+    // after the CTA-wide barrier, so that the producer starts the weight stream at once
+    if (p.use_pdl) grid_launch_dependents();
     ActPrefetch<ACT, act_t> pre;
-    if (warp != GEMV_CONSUMER_WARPS) pre.issue(p.act, 1, p.K, p.K, p.act_vec != 0, tid);
+    if (!p.use_pdl && warp != GEMV_CONSUMER_WARPS) pre.issue(p.act, 1, p.K, p.K, p.act_vec != 0, tid);
 
     const bool is_producer = (warp == GEMV_CONSUMER_WARPS);
     if (is_producer && lane == 0) {
@@ -1069,12 +1131,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
                 int row0, row1;
                 group_rows(p, m, cta, row0, row1);
                 const int R = p.rows_per_stage[m];
-                for (int r = row0; r < row1 && ok; r += R, ++g) {
+                for (int r = row0; r < row1 && ok; r += (r == row0 ? p.first_rows[m] : R), ++g) {
                     if (g >= S) {
                         ok = mbar_wait_bounded(&empty[s], ph);
                         if (!ok) { record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, g); break; }
                     }
-                    const int rows = min(R, row1 - r);
+                    const int rows = min(r == row0 ? p.first_rows[m] : R, row1 - r);
                     const uint32_t bytes = ((uint32_t)rows * (uint32_t)p.row_bytes[m] + 15u) & ~15u;
                     mbar_arrive_expect_tx(&full[s], bytes);
                     bulk_copy_g2s(ring + (size_t)s * p.stage_bytes, p.w[m] + (size_t)r * p.row_bytes[m], bytes, &full[s]);
@@ -1097,18 +1159,21 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
     }
 
     // ---------------- consumers ----------------
+    if (p.use_pdl) {
+        grid_dependency_wait();
+        pre.issue(p.act, 1, p.K, p.K, p.act_vec != 0, tid);
+    }
     // the activation row is quantized once for all matrices
     stage_acts_raw<1, act_t, TYPE_Q4_K, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.K, p.act_vec != 0, tid,
                                              GEMV_CONSUMER_THREADS, pre);
     named_bar_sync(1, GEMV_CONSUMER_THREADS);
 
     const int items = p.K / 128;
-    int islots = 32;
-    while (islots > 1 && (islots >> 1) >= items) islots >>= 1;
-    const int rpw = 32 / islots;
-    const int lane_i = lane & (islots - 1), lane_r = lane / islots;
-    const int nrg = GEMV_CONSUMER_WARPS / WPR;
-    const int wgroup = warp / WPR, wslice = warp % WPR;
+    const int islots = 1 << p.log2_islots;
+    const int rpw = 32 >> p.log2_islots;
+    const int lane_i = lane & (islots - 1), lane_r = lane >> p.log2_islots;
+    const int nrg = GEMV_CONSUMER_WARPS >> p.log2_wpr;
+    const int wgroup = warp >> p.log2_wpr, wslice = warp & (WPR - 1);
     const int row_slot = wgroup * rpw + lane_r;
     const int rows_per_pass = nrg * rpw;
     const int item0 = wslice * 32 + lane_i;
@@ -1134,13 +1199,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
         const int R = p.rows_per_stage[m];
         const int mtype = p.type[m];
         dst_t* dst = reinterpret_cast<dst_t*>(p.dst[m]);
-        for (int r = row0; r < row1; r += R, ++g) {
+        for (int r = row0; r < row1; r += (r == row0 ? p.first_rows[m] : R), ++g) {
             if (alive && !mbar_wait_bounded(&full[s], ph)) {
                 record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, g);
                 alive = false;
             }
             const uint32_t st = ring_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
-            const int rows_here = min(R, row1 - r);
+            const int rows_here = min(r == row0 ? p.first_rows[m] : R, row1 - r);
             const int my_slot = row_slot >= rot ? row_slot - rot : row_slot - rot + rows_per_pass;
             rot += rows_here;
             while (rot >= rows_per_pass) rot -= rows_per_pass;
@@ -1314,6 +1379,10 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     p.rows_per_stage = R;
     p.warps_per_row = wpr;
     p.items_per_lane = ipl;
+    p.log2_wpr = 0;
+    while ((1 << p.log2_wpr) < wpr) ++p.log2_wpr;
+    p.log2_islots = 0;
+    while ((1 << p.log2_islots) < islots) ++p.log2_islots;
     p.stage_bytes = (R * p.row_bytes + 16 + 127) & ~127;
     const int budget = rt.smem_optin - 1024;  // one CTA per SM; 1 KB per CTA is reserved by the system
     int S = 0;
@@ -1333,6 +1402,9 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     }
     if (S < 2) return plan;  // does not fit: simple kernel
     p.nstages = S;
+    R = p.rows_per_stage;
+    // first stage: one pass of all warps where a stage holds two, so that the first rows land in half the time
+    p.first_rows = (passes == 2 && R % 2 == 0 && (R / 2) % unit0 == 0) ? R / 2 : R;
     const long long units = (N + p.row_align - 1) / p.row_align;
     long long grid = rt.sm_count;
     if (grid > units) grid = units;
@@ -1482,7 +1554,7 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
         if (reinterpret_cast<uintptr_t>(ws[m]) % 16 != 0 || Ns[m] <= 0) return B200Q_ERR_UNSUPPORTED;
         const GemvPlan one = plan_gemv(types[m], K, Ns[m], 1, ws[m]);
         if (!one.staged) return B200Q_ERR_UNSUPPORTED;
-        if (m == 0) { wpr = one.p.warps_per_row; ipl = one.p.items_per_lane; }
+        if (m == 0) { wpr = one.p.warps_per_row; ipl = one.p.items_per_lane; p.log2_wpr = one.p.log2_wpr; p.log2_islots = one.p.log2_islots; }
         if (one.p.warps_per_row != wpr || one.p.items_per_lane != ipl) return B200Q_ERR_UNSUPPORTED;  // same K: cannot differ
         p.w[m] = static_cast<const uint8_t*>(ws[m]);
         p.dst[m] = dsts[m];
@@ -1490,6 +1562,7 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
         p.type[m] = types[m];
         p.row_bytes[m] = one.p.row_bytes;
         p.rows_per_stage[m] = one.p.rows_per_stage;
+        p.first_rows[m] = m == 0 ? one.p.first_rows : one.p.rows_per_stage;
         p.row_align[m] = one.p.row_align;
         if (one.p.stage_bytes > max_stage) max_stage = one.p.stage_bytes;
         if (one.p.rows_per_stage > max_R) max_R = one.p.rows_per_stage;

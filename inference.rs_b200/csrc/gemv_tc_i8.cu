@@ -813,37 +813,17 @@ static int launch_gemv_tc_i8_tok(const CUtensorMap& map_w, const CUtensorMap& ma
     return (int)cudaGetLastError();
 }
 
-template <int TYPE, typename T>
-static int launch_gemv_tc_i8(const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace, cudaStream_t s) {
+// Row split, K split and ring depths for a shape; fills p.{ksplit, tile_rows, rows_per_cta, rows_extra, a_stages,
+// raw_stages}. Returns 0 or B200Q_ERR_UNSUPPORTED.
+template <int TYPE>
+static int tcq_plan(TcqParams& p, int N, int K, bool allow_ksplit, int& grid, int& smem_bytes) {
     using TT = TcqType<TYPE>;
     using L = TcqLayout<TYPE>;
-    EncodeTiledFn encode = encode_tiled_fn();
-    if (encode == nullptr) return B200Q_ERR_UNSUPPORTED;
-    int8_t* q = static_cast<int8_t*>(workspace);
-    float2* ds = reinterpret_cast<float2*>(q + (size_t)TT::XROWS * K);
-
-    TcqParams p{};
-    p.y = y;
-    p.ds = reinterpret_cast<const uint8_t*>(ds);
-    p.M = M;
-    p.N = N;
-    p.K = K;
-    p.ldy = ldy;
-    p.status = status_ptr();
-    {
-        int slots = 0;
-        p.trace = trace_buffer(&slots);
-        p.trace_stages = slots / 8;
-    }
-    uint8_t* after = static_cast<uint8_t*>(workspace) + ((tcq_quant_bytes(TYPE, K) + 255) & ~(size_t)255);
-    p.counters = reinterpret_cast<unsigned int*>(after);
-    p.partial = reinterpret_cast<float*>(after + TCQ_COUNTERS * sizeof(unsigned int));
     const int sms = runtime_info().sm_count < TCQ_MAX_CTAS ? runtime_info().sm_count : TCQ_MAX_CTAS;
     const int nkc = K / TCQ_KC;
     const int row_tiles = (N + TCQ_ROWS - 1) / TCQ_ROWS;
-    int grid;
     p.ksplit = 1;
-    if (2 * row_tiles <= sms && nkc >= 4 && runtime_info().tc_ksplit) {
+    if (allow_ksplit && 2 * row_tiles <= sms && nkc >= 4 && runtime_info().tc_ksplit) {
         // few rows: full-height tiles, K shared out so that most SMs get a unit of at least two stages
         int ks = sms / row_tiles;
         if (ks > nkc / 2) ks = nkc / 2;
@@ -871,21 +851,58 @@ static int launch_gemv_tc_i8(const void* w, const void* x, void* y, int M, int N
     p.raw_stages = (room - p.a_stages * a_bytes) / raw_bytes;
     if (p.raw_stages > 8) p.raw_stages = 8;
     if (p.raw_stages < 2) return B200Q_ERR_UNSUPPORTED;
-    const int smem_bytes = L::FIXED + p.a_stages * a_bytes + p.raw_stages * raw_bytes;
+    smem_bytes = L::FIXED + p.a_stages * a_bytes + p.raw_stages * raw_bytes;
+    return 0;
+}
 
+// 2-D tensor map over the packed weight bytes: boxes of tile_rows x one 256-k chunk
+template <int TYPE>
+static int tcq_encode_w(CUtensorMap& map_w, const void* w, int N, int K, int tile_rows) {
+    using TT = TcqType<TYPE>;
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (encode == nullptr) return B200Q_ERR_UNSUPPORTED;
     const int row_bytes = K / type_block_elems(TYPE) * type_block_bytes(TYPE);
-    CUtensorMap map_w, map_x;
+    const bool u16 = TYPE == TYPE_Q8_0;  // a 272-byte chunk is more than 256 one-byte elements
+    const cuuint64_t dims[2] = {(cuuint64_t)(u16 ? row_bytes / 2 : row_bytes), (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)(u16 ? TT::PITCH / 2 : TT::PITCH), (cuuint32_t)tile_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&map_w, u16 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : B200Q_ERR_INVALID;
+}
+
+template <int TYPE, typename T>
+static int launch_gemv_tc_i8(const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace, cudaStream_t s) {
+    using TT = TcqType<TYPE>;
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (encode == nullptr) return B200Q_ERR_UNSUPPORTED;
+    int8_t* q = static_cast<int8_t*>(workspace);
+    float2* ds = reinterpret_cast<float2*>(q + (size_t)TT::XROWS * K);
+
+    TcqParams p{};
+    p.y = y;
+    p.ds = reinterpret_cast<const uint8_t*>(ds);
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.ldy = ldy;
+    p.status = status_ptr();
     {
-        const bool u16 = TYPE == TYPE_Q8_0;  // a 272-byte chunk is more than 256 one-byte elements
-        const cuuint64_t dims[2] = {(cuuint64_t)(u16 ? row_bytes / 2 : row_bytes), (cuuint64_t)N};
-        const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-        const cuuint32_t box[2] = {(cuuint32_t)(u16 ? TT::PITCH / 2 : TT::PITCH), (cuuint32_t)p.tile_rows};
-        const cuuint32_t estr[2] = {1, 1};
-        CUresult r = encode(&map_w, u16 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), dims, strides,
-                            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return B200Q_ERR_INVALID;
+        int slots = 0;
+        p.trace = trace_buffer(&slots);
+        p.trace_stages = slots / 8;
     }
+    uint8_t* after = static_cast<uint8_t*>(workspace) + ((tcq_quant_bytes(TYPE, K) + 255) & ~(size_t)255);
+    p.counters = reinterpret_cast<unsigned int*>(after);
+    p.partial = reinterpret_cast<float*>(after + TCQ_COUNTERS * sizeof(unsigned int));
+    int grid = 0, smem_bytes = 0;
+    int rc = tcq_plan<TYPE>(p, N, K, true, grid, smem_bytes);
+    if (rc != 0) return rc;
+    CUtensorMap map_w, map_x;
+    rc = tcq_encode_w<TYPE>(map_w, w, N, K, p.tile_rows);
+    if (rc != 0) return rc;
     {
         const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)TT::XROWS};
         const cuuint64_t strides[1] = {(cuuint64_t)K};
@@ -903,6 +920,115 @@ static int launch_gemv_tc_i8(const void* w, const void* x, void* y, int M, int N
     if (M <= 4) return launch_gemv_tc_i8_tok<TYPE, T, 4>(map_w, map_x, p, grid, smem_bytes, s);
     if (M <= 8) return launch_gemv_tc_i8_tok<TYPE, T, 8>(map_w, map_x, p, grid, smem_bytes, s);
     return launch_gemv_tc_i8_tok<TYPE, T, 16>(map_w, map_x, p, grid, smem_bytes, s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The reference tier's own pair of launchers (crates/inference-quant/src/gguf/ffi.rs:631-652,954-998): the host
+// quantizes with launch_mmvq_tc_quantize_<elem> into ITS scratch (288 bytes per 32-value block and 8-row half,
+// fast_mmvq.rs:94,1898-1902) and hands that to launch_mmvq_tc_gguf_<type>_<elem>_plain. The matvec is the kernel
+// above with REF_ACTS: one warp re-lays the fragments out stage by stage, so nothing beyond the host's scratch is
+// needed; without a workspace for partial outputs the split along K is off. Shapes the TMA path cannot take (packed
+// rows that are not a multiple of 16 bytes, unaligned weights) go to a plain one-warp-per-row kernel on the same layout.
+// ---------------------------------------------------------------------------------------------
+template <int TYPE, typename dst_t>
+__global__ void __launch_bounds__(256) gemv_tc_ref_simple_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ acts,
+                                                                 dst_t* __restrict__ dst, int K, int N, int stride_dst, int M) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= N) return;
+    const int nb = K / 32;
+    const uint8_t* rp = w + (size_t)row * (K / 256) * type_block_bytes(TYPE);
+    float acc[TCQ_TOKENS];
+#pragma unroll
+    for (int t = 0; t < TCQ_TOKENS; ++t) acc[t] = 0.0f;
+    for (int kb = lane; kb < nb; kb += 32) {
+        int wq[32];
+        float s0 = 0.0f, s1 = 0.0f, mn = 0.0f;  // Q4_K: s0 = d * sc, mn = dmin * m; Q6_K: s0, s1 = d * sc of the two halves
+        const int sblk = kb >> 3;
+        if (TYPE == TYPE_Q4_K) {
+            const int j = kb & 7;
+            const uint8_t* sb = rp + (size_t)sblk * Q4_K_BYTES;
+            const uint8_t* q = sb + 4;
+            int sc, m;
+            if (j < 4) { sc = q[j] & 63; m = q[j + 4] & 63; }
+            else { sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4); m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+            s0 = half_bits_to_float((uint32_t)sb[0] | ((uint32_t)sb[1] << 8)) * (float)sc;
+            mn = half_bits_to_float((uint32_t)sb[2] | ((uint32_t)sb[3] << 8)) * (float)m;
+            const uint8_t* qs = sb + 16 + 32 * (j >> 1);
+            for (int l = 0; l < 32; ++l) wq[l] = (j & 1) ? (qs[l] >> 4) : (qs[l] & 0xF);
+        } else {
+            const int n = (kb >> 2) & 1, qd = kb & 3;
+            const uint8_t* sb = rp + (size_t)sblk * Q6_K_BYTES;
+            const uint8_t* ql = sb + 64 * n + 32 * (qd & 1);
+            const uint8_t* qh = sb + 128 + 32 * n;
+            for (int l = 0; l < 32; ++l) {
+                const int lo = (qd & 2) ? (ql[l] >> 4) : (ql[l] & 0xF);
+                wq[l] = (lo | (((qh[l] >> (2 * qd)) & 3) << 4)) - 32;
+            }
+            const float d = half_bits_to_float((uint32_t)sb[208] | ((uint32_t)sb[209] << 8));
+            s0 = d * (float)(int)(int8_t)sb[192 + 8 * n + 2 * qd];
+            s1 = d * (float)(int)(int8_t)sb[192 + 8 * n + 2 * qd + 1];
+        }
+        for (int t = 0; t < M; ++t) {
+            const uint8_t* base = acts + (size_t)(t >> 3) * nb * TCQ_REF_BLOCK_BYTES;
+            const int r = t & 7;
+            const int8_t* frag = reinterpret_cast<const int8_t*>(base) + (size_t)kb * 256 + (4 * r) * 8;
+            const float xd = __half2float(reinterpret_cast<const __half*>(base + (size_t)nb * 256)[kb * 8 + r]);
+            int d0 = 0, d1 = 0;
+            for (int l = 0; l < 16; ++l) d0 += wq[l] * (int)frag[(l >> 2) * 8 + (l & 3)];
+            for (int l = 16; l < 32; ++l) d1 += wq[l] * (int)frag[((l - 16) >> 2) * 8 + 4 + (l & 3)];
+            if (TYPE == TYPE_Q4_K) {
+                const int sum = (int)reinterpret_cast<const int16_t*>(base + (size_t)nb * 256 + (size_t)nb * 16)[kb * 8 + r];
+                acc[t] += s0 * (xd * (float)(d0 + d1)) - mn * (xd * (float)sum);
+            } else {
+                acc[t] += xd * (s0 * (float)d0 + s1 * (float)d1);
+            }
+        }
+    }
+    for (int t = 0; t < M; ++t) {
+        const float v = warp_sum(acc[t]);
+        if (lane == 0) dst[(size_t)t * stride_dst + row] = from_float<dst_t>(v);
+    }
+}
+
+template <typename T>
+static int launch_tcq_ref_quantize(const void* x, void* vy, int kx, int num_rows, cudaStream_t s) {
+    if (kx <= 0 || num_rows <= 0) return 0;
+    const dim3 grid((unsigned)((kx + 31) / 32), (unsigned)((num_rows + 7) / 8), 1);
+    tcq_ref_quantize_kernel<T><<<grid, dim3(32, 8, 1), 0, s>>>(static_cast<const T*>(x), static_cast<uint8_t*>(vy), kx, num_rows);
+    return (int)cudaGetLastError();
+}
+
+template <int TYPE, typename T>
+static int launch_gemv_tc_ref(const void* w, const void* vy, void* dst, int K, int N, int stride_col_dst, int b, cudaStream_t s) {
+    if (N <= 0 || K <= 0 || b <= 0) return 0;
+    if (b > TCQ_TOKENS || K % TCQ_KC != 0) return B200Q_ERR_UNSUPPORTED;
+    const int row_bytes = K / 256 * type_block_bytes(TYPE);
+    const bool tma_ok = reinterpret_cast<uintptr_t>(w) % 16 == 0 && row_bytes % 16 == 0 && encode_tiled_fn() != nullptr;
+    if (!tma_ok) {
+        gemv_tc_ref_simple_kernel<TYPE, T><<<(N + 7) / 8, 256, 0, s>>>(static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(vy),
+                                                                      static_cast<T*>(dst), K, N, stride_col_dst, b);
+        return (int)cudaGetLastError();
+    }
+    TcqParams p{};
+    p.y = dst;
+    p.M = b;
+    p.N = N;
+    p.K = K;
+    p.ldy = stride_col_dst;
+    p.status = status_ptr();
+    p.ref_acts = static_cast<const uint8_t*>(vy);
+    p.ref_halves = (b + 7) / 8;
+    int grid = 0, smem_bytes = 0;
+    int rc = tcq_plan<TYPE>(p, N, K, false, grid, smem_bytes);
+    if (rc != 0) return rc;
+    CUtensorMap map_w;
+    rc = tcq_encode_w<TYPE>(map_w, w, N, K, p.tile_rows);
+    if (rc != 0) return rc;
+    // (the activation map parameter is not read by the REF_ACTS kernels)
+    if (b <= 4) return launch_gemv_tc_i8_tok<TYPE, T, 4, true>(map_w, map_w, p, grid, smem_bytes, s);
+    if (b <= 8) return launch_gemv_tc_i8_tok<TYPE, T, 8, true>(map_w, map_w, p, grid, smem_bytes, s);
+    return launch_gemv_tc_i8_tok<TYPE, T, 16, true>(map_w, map_w, p, grid, smem_bytes, s);
 }
 
 int gemv_tc_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace,
@@ -927,3 +1053,30 @@ int gemv_tc_dispatch(int type, int elem, const void* w, const void* x, void* y, 
 }
 
 }  // namespace b200q
+
+// The reference's symbols; void, asynchronous, allocation-free. `cfg` selects among the reference kernel's own launch
+// shapes (mmvq_tc_k.cuh:352-375) and has no meaning for this kernel.
+#define B200Q_TC_QUANTIZE(tag, T)                                                                                          \
+    extern "C" void launch_mmvq_tc_quantize_##tag(const void* x, void* vy, int kx, int num_rows, void* stream) {          \
+        b200q::note_launch_status(b200q::launch_tcq_ref_quantize<T>(x, vy, kx, num_rows, (cudaStream_t)stream));           \
+    }
+B200Q_TC_QUANTIZE(bf16, __nv_bfloat16)
+B200Q_TC_QUANTIZE(f16, __half)
+B200Q_TC_QUANTIZE(f32, float)
+#undef B200Q_TC_QUANTIZE
+
+#define B200Q_TC_PLAIN(type_tag, TYPE, tag, T)                                                                             \
+    extern "C" void launch_mmvq_tc_gguf_##type_tag##_##tag##_plain(const void* vx, const void* vy, void* dst, int ncols_x,  \
+                                                                   int nrows_x, int stride_col_dst, int b_size, int cfg,   \
+                                                                   void* stream) {                                         \
+        (void)cfg;                                                                                                         \
+        b200q::note_launch_status(                                                                                         \
+            b200q::launch_gemv_tc_ref<TYPE, T>(vx, vy, dst, ncols_x, nrows_x, stride_col_dst, b_size, (cudaStream_t)stream)); \
+    }
+B200Q_TC_PLAIN(q4_k, b200q::TYPE_Q4_K, bf16, __nv_bfloat16)
+B200Q_TC_PLAIN(q4_k, b200q::TYPE_Q4_K, f16, __half)
+B200Q_TC_PLAIN(q4_k, b200q::TYPE_Q4_K, f32, float)
+B200Q_TC_PLAIN(q6_k, b200q::TYPE_Q6_K, bf16, __nv_bfloat16)
+B200Q_TC_PLAIN(q6_k, b200q::TYPE_Q6_K, f16, __half)
+B200Q_TC_PLAIN(q6_k, b200q::TYPE_Q6_K, f32, float)
+#undef B200Q_TC_PLAIN

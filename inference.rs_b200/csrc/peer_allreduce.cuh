@@ -12,12 +12,12 @@ constexpr int PAR_EPOCH_OFFSET = 768;
 constexpr int PAR_THREADS = 512;
 
 constexpr int PAR_COUNTER_OFFSET = 832;  // arrival counter of the CTAs of a fused matmul + all-reduce launch
-constexpr int PAR_FUSED_BLOCK = 7;       // flag / epoch slot of the fused path (stand-alone calls use blocks 0..6)
+constexpr int PAR_FUSED_BLOCK = 7;       // flag / epoch slot of the fused path (stand-alone calls use slots 0..6)
 
 // The ranks' exchange buffers as mapped in this process; world <= 1 means "no exchange".
 struct PeerExchange {
     uint8_t* bufs[PAR_MAX_WORLD];  // bufs[rank] is the local one
-    long long capacity;            // bytes of one staging half
+    long long capacity;            // largest vector in bytes
     int rank, world;
 };
 
@@ -89,37 +89,45 @@ template <> struct Vec16<__nv_bfloat16> {
     }
 };
 
-// One slice [u0, u1) (16-byte units) of the vector, by `nthreads` threads of one CTA (tid < nthreads; all of them must
-// call). `staging` = byte offset of the two staging halves in every rank's buffer, `slot` = which flag / epoch slot.
-// NAMED: the threads are a subset of the CTA that meets on named barrier 1; else the whole CTA (__syncthreads).
-// `scratch` = two words of shared memory. Returns false (on all threads) if a peer did not arrive in time.
+// ---- buffer layout (every rank's buffer is the same; `capacity` = largest vector in bytes, a multiple of 16) ----
+//   [0, 512)      arrive[slot 0..7][source rank 0..15]  u32, written by the peers
+//   768           epoch[slot 0..7]                       u32, local
+//   832           arrival counter of the CTAs of a fused matmul + all-reduce launch
+//   [1024, ...)   inboxes: for stand-alone slot i < 7, half h, source rank r: slot_cap bytes at
+//                 1024 + ((i * 2 + h) * 8 + r) * slot_cap, slot_cap = ceil16(capacity / 7): slot i always carries bytes
+//                 [i * slot_cap, (i + 1) * slot_cap) of a vector, whatever the vector's length, so a slot's inboxes
+//                 only ever meet that slot's own earlier calls;
+//                 then the fused launches' inboxes (slot 7): capacity bytes at fused_base + (h * 8 + r) * capacity.
+__host__ __device__ inline long long par_slot_cap(long long capacity) { return ((capacity + PAR_MAX_BLOCKS - 1) / PAR_MAX_BLOCKS + 15) & ~15LL; }
+__host__ __device__ inline long long par_inbox_offset(long long capacity, int slot, unsigned int half, int src) {
+    return PAR_HEADER_BYTES + (((long long)slot * 2 + half) * PAR_MAX_WORLD + src) * par_slot_cap(capacity);
+}
+__host__ __device__ inline long long par_fused_base(long long capacity) {
+    return PAR_HEADER_BYTES + (long long)PAR_MAX_BLOCKS * 2 * PAR_MAX_WORLD * par_slot_cap(capacity);
+}
+__host__ __device__ inline long long par_fused_inbox_offset(long long capacity, unsigned int half, int src) {
+    return par_fused_base(capacity) + ((long long)half * PAR_MAX_WORLD + src) * capacity;
+}
+__host__ __device__ inline long long par_buffer_bytes(long long capacity) { return par_fused_base(capacity) + 2LL * PAR_MAX_WORLD * capacity; }
+
+__device__ __forceinline__ void st_global_16(void* p, const uint4& v) {
+    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Second half of an exchange, by `nthreads` threads of one CTA (tid < nthreads; all of them must call): every rank's
+// contribution to units [0, nunits) of this slot has been pushed into the peers' inboxes (at `inbox0` + source rank *
+// `inbox_stride` of the epoch's half) and fenced at system scope by the threads that wrote it. Raises this rank's flag
+// in every peer, waits - bounded - for every peer's flag, then adds the `world` inboxes of the LOCAL buffer in rank
+// order in f32 and stores units of `out`. NAMED: the threads are a subset of the CTA that meets on named barrier 1.
+// `scratch` = one word of shared memory. Returns false (on all threads) if a peer did not arrive in time.
 template <typename T, bool NAMED>
-__device__ __forceinline__ bool peer_allreduce_slice(const PeerExchange& px, size_t staging, int slot, const void* in, void* out,
-                                                     long long u0, long long u1, int tid, int nthreads, unsigned int* status,
-                                                     volatile unsigned int* scratch) {
+__device__ __forceinline__ bool peer_signal_wait_reduce(const PeerExchange& px, int slot, unsigned int e, long long inbox0,
+                                                        long long inbox_stride, void* out, long long nunits, int tid, int nthreads,
+                                                        unsigned int* status, volatile unsigned int* scratch) {
     using V = Vec16<T>;
     uint8_t* mine = px.bufs[px.rank];
-    if (tid == 0) {
-        unsigned int* epoch = reinterpret_cast<unsigned int*>(mine + PAR_EPOCH_OFFSET) + slot;
-        const unsigned int e1 = *epoch + 1u;
-        *epoch = e1;
-        scratch[0] = e1;
-        scratch[1] = 1u;
-    }
+    if (tid == 0) scratch[0] = 1u;
     if (NAMED) named_bar_sync(1, nthreads); else __syncthreads();
-    const unsigned int e = scratch[0];
-    const size_t half_off = staging + (size_t)(e & 1u) * (size_t)px.capacity;
-
-    // 1. this rank's slice into its staging half (read past L1: other CTAs may have produced it)
-    {
-        const uint4* src = reinterpret_cast<const uint4*>(in);
-        uint4* dst = reinterpret_cast<uint4*>(mine + half_off);
-        for (long long u = u0 + tid; u < u1; u += nthreads) dst[u] = __ldcg(src + u);
-    }
-    __threadfence_system();
-    if (NAMED) named_bar_sync(1, nthreads); else __syncthreads();
-
-    // 2. tell every rank, then wait for every rank
     if (tid < px.world) {
         st_release_sys(reinterpret_cast<unsigned int*>(px.bufs[tid]) + slot * 16 + px.rank, e);
         const unsigned int* flag = reinterpret_cast<const unsigned int*>(mine) + slot * 16 + tid;
@@ -132,18 +140,17 @@ __device__ __forceinline__ bool peer_allreduce_slice(const PeerExchange& px, siz
             if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
         }
         if (!ok) {
-            scratch[1] = 0u;
+            scratch[0] = 0u;
             record_failure(status, STATUS_WAIT_PEER_TIMEOUT, (unsigned int)(slot * 16 + tid));
         }
     }
     if (NAMED) named_bar_sync(1, nthreads); else __syncthreads();
-    if (scratch[1] == 0u) return false;
-
-    // 3. the same sum in the same order on every rank
+    if (scratch[0] == 0u) return false;
+    // the same sum in the same order on every rank, from local memory
     uint4* o = reinterpret_cast<uint4*>(out);
-    for (long long u = u0 + tid; u < u1; u += nthreads) {
+    for (long long u = tid; u < nunits; u += nthreads) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < px.world; ++r) V::add(ld_volatile_16(px.bufs[r] + half_off + (size_t)u * 16), acc);
+        for (int r = 0; r < px.world; ++r) V::add(ld_volatile_16(mine + inbox0 + r * inbox_stride + (size_t)u * 16), acc);
         o[u] = V::pack(acc);
     }
     return true;

@@ -15,7 +15,9 @@ ARCH_DIR = "sm100a"
 
 
 class KernelLibraryError(RuntimeError):
-    pass
+    """`status` carries the library's return code where one caused the error (< 0: a B200Q_ERR_* code, > 0: a cudaError_t)."""
+
+    status: int | None = None
 
 
 _vp, _i32, _i64 = C.c_void_p, C.c_int, C.c_int64
@@ -30,10 +32,16 @@ for _e in ("bf16", "f16", "f32"):
     SYMBOLS[f"launch_mmvq_gguf_quantize_q8_1_{_e}"] = (_QUANT_ARGS, None)
     for _t in ("q8_0", "q4_k", "q6_k"):
         SYMBOLS[f"launch_mmvq_gguf_{_t}_{_e}_plain"] = (_PLAIN_ARGS, None)
+for _e in ("bf16", "f16", "f32"):
+    SYMBOLS[f"launch_mmvq_tc_quantize_{_e}"] = ([_vp, _vp, _i32, _i32, _vp], None)
+    for _t in ("q4_k", "q6_k"):
+        SYMBOLS[f"launch_mmvq_tc_gguf_{_t}_{_e}_plain"] = ([_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp], None)
 for _e in ("bf16", "f32"):
     SYMBOLS[f"launch_mmvq_gguf_q8_0_{_e}_exact"] = ([_vp, _vp, _vp, _i32, _i32, _i32, _vp], None)
 for _l in ("D4", "DS4"):
     SYMBOLS[f"launch_mmq_quantize_q8_1_{_l}"] = (_MMQ_QUANT_ARGS, None)
+for _t in ("q8_0", "q4_k", "q6_k"):
+    SYMBOLS[f"launch_mmq_gguf_{_t}"] = ([_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i64, _i32, _i32, _vp], None)
 SYMBOLS.update({
     "b200q_version": ([], C.c_char_p),
     "b200q_last_error": ([], C.c_char_p),
@@ -54,6 +62,9 @@ SYMBOLS.update({
     "b200q_gemv_static_scratch": ([_i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
     "b200q_gemv_plan": ([_i32, _i32, _i32, _i32, C.POINTER(_i32 * 10)], _i32),
     "b200q_set_weight_successor": ([_vp, _vp, _i32, _i32, _i32], _i32),
+    "b200q_quantize": ([_i32, _vp, _vp, _i64, _vp], _i32),
+    "b200q_dequantize": ([_i32, _i32, _vp, _vp, _i64, _i32, _vp], _i32),
+    "b200q_get_rows": ([_i32, _i32, _vp, _vp, _vp, _i64, _i32, _i64, _vp], _i32),
     "b200q_clear_weight_successors": ([], _i32),
 })
 DATA_SYMBOLS = ["inference_kernel_build_id"]
@@ -112,7 +123,9 @@ def build_id() -> str:
 def check(rc: int, what: str = "") -> None:
     if rc != 0:
         msg = library().b200q_last_error().decode()
-        raise KernelLibraryError(f"{what or 'b200q call'} failed with status {rc}: {msg}")
+        err = KernelLibraryError(f"{what or 'b200q call'} failed with status {rc}: {msg}")
+        err.status = rc
+        raise err
 
 
 def device_status() -> tuple[int, int, int, int]:

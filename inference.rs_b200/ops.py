@@ -46,6 +46,38 @@ def upload_weights(packed: np.ndarray | torch.Tensor, dtype: GgmlDType, device="
     return buf
 
 
+def quantize_weights(x: torch.Tensor, dtype: GgmlDType) -> torch.Tensor:
+    """`b200q_quantize`: f32 [n, k] on the device -> packed blocks followed by the reference's padding (a buffer
+    `upload_weights` would have produced), byte for byte the reference CPU quantizer's."""
+    _require_cuda(x)
+    if x.dtype != torch.float32:
+        raise TypeError("weights are quantized from f32")
+    n, k = x.shape
+    nbytes = n * dtype.row_bytes(k)
+    padding = MATRIX_ROW_PADDING * dtype.type_size // dtype.block_size
+    buf = torch.zeros(nbytes + padding, dtype=torch.uint8, device=x.device)
+    kl.check(kl.library().b200q_quantize(int(dtype), x.data_ptr(), buf.data_ptr(), n * k, _stream()), "b200q_quantize")
+    return buf
+
+
+def dequantize(dtype: GgmlDType, w: torch.Tensor, n: int, k: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """`b200q_dequantize`: packed [n, k] -> values [n, k] of `out_dtype`."""
+    _require_cuda(w)
+    out = torch.empty((n, k), dtype=out_dtype, device=w.device)
+    kl.check(kl.library().b200q_dequantize(int(dtype), elem_of(out_dtype), w.data_ptr(), out.data_ptr(), n, k, _stream()), "b200q_dequantize")
+    return out
+
+
+def get_rows(dtype: GgmlDType, w: torch.Tensor, ids: torch.Tensor, n: int, k: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """`b200q_get_rows`: rows `ids` (int32, any shape) of a packed [n, k] table -> [*ids.shape, k] of `out_dtype`."""
+    _require_cuda(w)
+    flat = ids.reshape(-1).to(device=w.device, dtype=torch.int32).contiguous()
+    out = torch.empty((flat.numel(), k), dtype=out_dtype, device=w.device)
+    kl.check(kl.library().b200q_get_rows(int(dtype), elem_of(out_dtype), w.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.numel(), k, n,
+                                         _stream()), "b200q_get_rows")
+    return out.reshape(*ids.shape, k)
+
+
 def quantize_q8_1(x: torch.Tensor, k_padded: int | None = None) -> torch.Tensor:
     """`launch_mmvq_gguf_quantize_q8_1_<dtype>`: x [rows, k] -> uint8 [rows, k_padded / 32 * 36]."""
     _require_cuda(x)
@@ -79,6 +111,56 @@ def mmvq_plain(dtype: GgmlDType, w: torch.Tensor, vy: torch.Tensor, n: int, k: i
     rc = kl.library().b200q_take_launch_status()
     if rc:
         raise kl.KernelLibraryError(f"launch_mmvq_gguf_{dtype.tag}_*_plain failed with status {rc}")
+    return dst
+
+
+MMQ_LAYOUT = {GgmlDType.Q8_0: "D4", GgmlDType.Q4K: "DS4", GgmlDType.Q6K: "D4"}  # fast_mmq.rs:167-190
+
+
+def mmq(dtype: GgmlDType, w: torch.Tensor, vy: torch.Tensor, m: int, n: int, k: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """`launch_mmq_gguf_<type>` on activation blocks `vy` from `quantize_mmq_q8_1(x, MMQ_LAYOUT[dtype])`; returns
+    [m, n] of `out_dtype`, called as the reference's host calls it (crates/inference-quant/src/gguf/fast_mmq.rs:489-512)."""
+    _require_cuda(w, vy)
+    dst = torch.empty((m, n), dtype=out_dtype, device=w.device)
+    props = torch.cuda.get_device_properties(w.device)
+    fn = getattr(kl.library(), f"launch_mmq_gguf_{dtype.tag}")
+    fn(None, w.data_ptr(), vy.data_ptr(), dst.data_ptr(), k, n, m, k // dtype.block_size, n, (props.major * 10 + props.minor) * 10,
+       props.multi_processor_count, 232448, 32, MMQ_TYPE_X[elem_of(out_dtype)], _stream())
+    rc = kl.library().b200q_take_launch_status()
+    if rc:
+        raise kl.KernelLibraryError(f"launch_mmq_gguf_{dtype.tag} failed with status {rc}")
+    return dst
+
+
+TC_ACT_BLOCK_BYTES = 288  # per 32-value block and 8-row half (crates/inference-quant/src/gguf/fast_mmvq.rs:94)
+
+
+def mmvq_tc_quantize(x: torch.Tensor) -> torch.Tensor:
+    """`launch_mmvq_tc_quantize_<dtype>`: x [rows <= 16, k] contiguous -> the tensor-core tier's activation scratch,
+    uint8 [ceil(rows / 8) * ceil(k / 32) * 288] (the size the reference's host allocates, fast_mmvq.rs:1898-1902)."""
+    _require_cuda(x)
+    rows, k = x.shape
+    out = torch.empty(((rows + 7) // 8) * ((k + 31) // 32) * TC_ACT_BLOCK_BYTES, dtype=torch.uint8, device=x.device)
+    fn = getattr(kl.library(), f"launch_mmvq_tc_quantize_{ELEM_TAG[elem_of(x.dtype)]}")
+    fn(x.data_ptr(), out.data_ptr(), k, rows, _stream())
+    rc = kl.library().b200q_take_launch_status()
+    if rc:
+        raise kl.KernelLibraryError(f"launch_mmvq_tc_quantize_* failed with status {rc}")
+    return out
+
+
+def mmvq_tc_plain(dtype: GgmlDType, w: torch.Tensor, vy: torch.Tensor, n: int, k: int, b: int, out_dtype: torch.dtype,
+                  cfg: int = 1) -> torch.Tensor:
+    """`launch_mmvq_tc_gguf_{q4_k,q6_k}_<out>_plain` on the scratch `mmvq_tc_quantize` wrote; returns [b, n]."""
+    _require_cuda(w, vy)
+    if dtype not in (GgmlDType.Q4K, GgmlDType.Q6K):
+        raise ValueError("the reference's tensor-core matvec launchers exist for Q4_K and Q6_K")
+    dst = torch.empty((b, n), dtype=out_dtype, device=w.device)
+    fn = getattr(kl.library(), f"launch_mmvq_tc_gguf_{dtype.tag}_{ELEM_TAG[elem_of(out_dtype)]}_plain")
+    fn(w.data_ptr(), vy.data_ptr(), dst.data_ptr(), k, n, n, b, cfg, _stream())
+    rc = kl.library().b200q_take_launch_status()
+    if rc:
+        raise kl.KernelLibraryError(f"launch_mmvq_tc_gguf_{dtype.tag}_*_plain failed with status {rc}")
     return dst
 
 

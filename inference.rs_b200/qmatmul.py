@@ -13,6 +13,7 @@ import torch
 
 from . import ops
 from .dtypes import MATRIX_ROW_PADDING, GgmlDType, pad
+from .kernel_library import KernelLibraryError
 
 MMVQ_MAX_BATCH = 8  # rows the decode GEMV launchers take (fast_mmvq.rs:84)
 TENSOR_CORE_MAX_ROWS = 16  # rows the small-batch tensor-core kernel takes (fast_mmvq.rs:86)
@@ -73,6 +74,28 @@ class QTensor:
         """From host bytes (numpy uint8 or torch CPU tensor), uploaded with the trailing padding."""
         return cls(ops.upload_weights(packed, dtype, device), dtype, shape)
 
+    @classmethod
+    def quantize(cls, src: torch.Tensor, dtype: GgmlDType) -> "QTensor":
+        """`QTensor::quantize(&tensor, dtype)` (mod.rs:903-918): an f32 `[n, k]` tensor packed on its device by the library's
+        quantizer, byte for byte what the reference's host quantizer writes. `k` must hold whole blocks."""
+        if src.dim() != 2:
+            raise ValueError(f"quantize takes a matrix, got {tuple(src.shape)}")
+        n, k = src.shape
+        if k % dtype.block_size:
+            raise ValueError(f"quantized tensor last dim {k} is not a multiple of the {dtype.name} block size {dtype.block_size}")
+        x = src.detach().to(dtype=torch.float32).contiguous()
+        if not x.is_cuda:
+            x = x.cuda()
+        return cls(ops.quantize_weights(x, dtype), dtype, (n, k))
+
+    def dequantize(self, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """`QTensor::dequantize` (mod.rs:920-940): the values as a dense `[n, k]` tensor on the same device."""
+        return ops.dequantize(self.dtype, self.data, self.shape[0], self.shape[1], out_dtype)
+
+    def embedding(self, ids: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """The rows `ids` names, dequantized: the quantized embedding lookup (crates/inference-quant/src/gguf/mod.rs:546-548)."""
+        return ops.get_rows(self.dtype, self.data, ids, self.shape[0], self.shape[1], out_dtype)
+
     @property
     def storage_size_in_bytes(self) -> int:
         return self.shape[0] * self.dtype.row_bytes(self.shape[1])
@@ -128,7 +151,15 @@ def _forward_rows(w: QTensor, x: torch.Tensor, act_quant: int) -> torch.Tensor:
         return ops.gemv_tc(w.dtype, w.data, x, n, workspace=_tc_workspace(w.dtype, k, x.device))
     if prefers_mmvq(rows):
         if k % 128 == 0:
-            return ops.gemv(w.dtype, w.data, x, n, act_quant=act_quant)
+            try:
+                return ops.gemv(w.dtype, w.data, x, n, act_quant=act_quant)
+            except KernelLibraryError as exc:
+                # B200Q_ERR_UNSUPPORTED: no staged plan for this call (weights not 16-byte aligned, the simple kernel
+                # forced, no ring that fits). The library can still serve Q8_1 activations in two launches.
+                if act_quant != ops.ACT_QUANT_Q8_1 or exc.status != -1:
+                    raise
+        elif act_quant != ops.ACT_QUANT_Q8_1:
+            raise ValueError(f"the CPU path's activation format needs K a multiple of 128, got {k}")
         # shapes the one-launch kernel declines: the reference's own two-launch protocol
         vy = ops.quantize_q8_1(x, pad(k, MATRIX_ROW_PADDING))
         return ops.mmvq_plain(w.dtype, w.data, vy, n, k, rows, x.dtype)

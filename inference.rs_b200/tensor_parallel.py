@@ -160,14 +160,26 @@ class PeerSumAllReduce(SumAllReduce):
         if not xs.is_contiguous():
             raise ValueError("sum_all_reduce expects a contiguous tensor")
         nbytes = xs.numel() * xs.element_size()
-        if nbytes > self.capacity or nbytes % 16 or xs.data_ptr() % 16 or xs.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        # which collective runs is decided from what every rank shares (size and type), never from a rank's own
+        # addresses: ranks that disagreed would wait for each other in two different exchanges
+        if nbytes > self.capacity or nbytes % 16 or xs.dtype not in (torch.bfloat16, torch.float16, torch.float32):
             return super().sum_all_reduce(xs)
         from .ops import _stream, elem_of
+        if xs.data_ptr() % 16:
+            xs = xs.clone()  # torch allocations are aligned
         out = torch.empty_like(xs)
         self._kl.check(self._kl.library().b200q_peer_allreduce(self._ptrs, self.rank, self.world, self.capacity, elem_of(xs.dtype),
                                                                xs.data_ptr(), out.data_ptr(), xs.numel(), _stream()),
                        "b200q_peer_allreduce")
         return out
+
+    def check_status(self) -> None:
+        """Raises if a kernel on this device recorded a failed wait (a peer that never arrived leaves the output
+        unwritten and only the device status word says so). Synchronizes the device: not for captured steps."""
+        st = self._kl.device_status()
+        if st[0] != 0:
+            raise self._kl.KernelLibraryError(f"device status word reports a failed wait: code {st[0]}, block {st[1]}, detail {st[2]}, "
+                                              f"{st[3]} failures")
 
     def gemv_sum(self, dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
         """`b200q_gemv_allreduce`: this rank's row-parallel matmul (x `[rows <= 8, k / w]` contiguous) and the sum over
@@ -229,9 +241,32 @@ class RowParallelLayer:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x holds this rank's slice of the input features: `[..., k / w]`."""
-        y = self.weight.forward_raw(x).contiguous()
-        y = self.all_reduce.sum_all_reduce(y)
+        y = self._fused_forward(x)
+        if y is None:
+            y = self.weight.forward_raw(x).contiguous()
+            y = self.all_reduce.sum_all_reduce(y)
         return y if self.bias is None else y + self.bias.to(y.dtype)
+
+    def _fused_forward(self, x: torch.Tensor):
+        """Matmul and exchange in one launch (`b200q_gemv_allreduce`) where the exchange object offers it and the call
+        fits it: up to 8 rows, a sum within the exchange's capacity. The conditions only involve what all ranks share
+        (shapes, types), so every rank takes the same path. None = not applicable."""
+        ar = self.all_reduce
+        if not isinstance(ar, PeerSumAllReduce) or ar.world == 1 or not x.is_contiguous():
+            return None
+        q = self.weight.get_qtensor()
+        n, k = q.shape
+        x2 = x.reshape(-1, k)
+        rows = x2.shape[0]
+        nbytes = rows * n * x.element_size()
+        if rows < 1 or rows > 8 or k % 128 or nbytes % 16 or nbytes > ar.capacity or x.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            return None
+        from . import ops
+        if not ops.gemv_plan(q.dtype, k, n, rows)["staged"]:
+            return None
+        if x2.data_ptr() % 16:
+            x2 = x2.clone()  # a rank's own addresses never change the path: misaligned rows are copied (torch allocations are aligned)
+        return ar.gemv_sum(q.dtype, q.data, x2, n).reshape(*x.shape[:-1], n)
 
     __call__ = forward
 

@@ -119,3 +119,86 @@ def test_unsupported_inputs_are_refused():
         ops.gemm(DT[kq.Q4_K], w_dev, torch.zeros(32, 256, device="cuda", dtype=torch.float64), 128)
     with pytest.raises(kl.KernelLibraryError, match="bf16 or f16"):
         ops.gemm(DT[kq.Q4_K], w_dev, torch.zeros(32, 256, device="cuda", dtype=torch.float32), 128)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# The reference's prefill launcher pair: launch_mmq_quantize_q8_1_{D4,DS4} + launch_mmq_gguf_<type>
+# ---------------------------------------------------------------------------------------------------------------------
+def mmq_reference_math(type_id, x32, packed, k):
+    """(d q) . dequant(W)^T in double, with the prefill quantizer's d and q per 32 values (d_inv = 127 / amax,
+    q = roundf(x d_inv), d = 1 / d_inv; mmq_quantize.cu:158-198); the DS4 blocks Q4_K weights take store d as f16."""
+    m = x32.shape[0]
+    b = x32.reshape(m, k // 32, 32)
+    amax = np.abs(b).max(axis=2, keepdims=True).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        d_inv = (np.float32(127.0) / amax).astype(np.float32)
+        v = (b * d_inv).astype(np.float32)
+        q = np.where(amax == 0, 0, np.sign(v) * np.floor(np.abs(v) + np.float32(0.5)))
+        d = np.where(amax == 0, 0, (np.float32(1.0) / d_inv).astype(np.float32)).astype(np.float32)
+    if ops.MMQ_LAYOUT[DT[type_id]] == "DS4":
+        d = d.astype(np.float16).astype(np.float32)
+    return (d.astype(np.float64) * q).reshape(m, k), kq.dequantize(type_id, packed, k).astype(np.float64)
+
+
+def run_mmq(type_id, m, n, k, dtype=torch.bfloat16, packed=None, seed=0, real=None, sample_rows=None):
+    if real is None:
+        real = packed is None
+    if packed is None:
+        packed = kq.quantize(type_id, seeded_weights(n, k, 8000 + seed))
+    x = seeded_acts(m, k, 8100 + seed, dtype)
+    w_dev = ops.upload_weights(packed, DT[type_id])
+    layout = ops.MMQ_LAYOUT[DT[type_id]]
+    vy = ops.quantize_mmq_q8_1(x.cuda(), layout)
+    y = ops.mmq(DT[type_id], w_dev, vy, m, n, k, dtype)
+    torch.cuda.synchronize()
+    assert_device_ok()
+    rows = np.arange(m)
+    if sample_rows is not None and sample_rows < m:
+        rows = np.sort(np.random.default_rng(seed).choice(m, size=sample_rows, replace=False))
+    got = as_f32_numpy(y)[rows].astype(np.float64)
+    xq, wd = mmq_reference_math(type_id, as_f32_numpy(x)[rows], packed, k)
+    if k % 256 == 0 and DT[type_id].row_bytes(k) % 16 == 0:
+        # the tile kernel rounds d q and the dequantized weights to bf16 before the tensor core multiplies them
+        xq = torch.from_numpy(xq).to(torch.bfloat16).double().numpy()
+        wd = torch.from_numpy(wd).to(torch.bfloat16).double().numpy()
+    ref = xq @ wd.T
+    eps = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -22}[dtype]
+    scale = np.abs(ref).max()
+    bad = np.abs(got - ref) > 1e-4 * scale + eps * 1.01 * np.abs(ref)
+    assert not bad.any(), (f"{kq.TYPE_NAMES[type_id]} m={m} n={n} k={k}: {bad.sum()} outputs off, worst {np.abs(got - ref).max():.3e} "
+                           f"vs scale {scale:.3e}; first at {np.argwhere(bad)[:4].tolist()}")
+    cpu = kq.matmul(type_id, as_f32_numpy(x)[rows], packed, n)
+    assert np.abs(got - cpu).max() <= 1e-3 + (1e-2 if (real and k >= 1024) else 2e-2) * np.abs(cpu).max()
+    if rk.available():
+        # the same blocks, followed by the 128 spare blocks the reference's host allocates behind them (fast_mmq.rs:686-692)
+        vy_ref = torch.zeros(vy.numel() + 128 * 144, dtype=torch.uint8, device="cuda")
+        vy_ref[: vy.numel()] = vy.reshape(-1)
+        theirs = as_f32_numpy(rk.mmq(type_id, w_dev, vy_ref, m, n, k, dtype))[rows].astype(np.float64)
+        torch.cuda.synchronize()
+        assert np.abs(got - theirs).max() <= 2e-2 * np.abs(theirs).max(), "differs from the reference's MMQ on the same blocks"
+    return y
+
+
+@pytest.mark.parametrize("type_id", TYPES)
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (40, 64, 512), (17, 130, 256), (300, 200, 1024), (512, 384, 768), (2048, 4096, 512)])
+def test_mmq_launcher_small_tiles_and_ragged_edges(type_id, m, n, k):
+    run_mmq(type_id, m, n, k, seed=m + n)
+
+
+@pytest.mark.parametrize("type_id", TYPES)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_mmq_launcher_output_types(type_id, dtype):
+    run_mmq(type_id, 200, 256, 512, dtype=dtype)
+
+
+def test_mmq_launcher_shapes_the_tile_kernel_does_not_take():
+    run_mmq(kq.Q8_0, 20, 100, 96, seed=1)      # K not a multiple of 256
+    run_mmq(kq.Q6_K, 33, 64, 768, seed=2)      # 210-byte blocks: rows not a multiple of 16 bytes
+    run_mmq(kq.Q8_0, 9, 64, 1056, seed=3)
+
+
+@pytest.mark.parametrize("type_id", [kq.Q4_K, kq.Q6_K])
+@pytest.mark.parametrize("k,n", [(4096, 4096), (14336, 4096)])
+@pytest.mark.parametrize("m", [512, 2048])
+def test_mmq_launcher_prefill_shapes(type_id, k, n, m):
+    run_mmq(type_id, m, n, k, packed=real_packed(type_id, n, k), seed=m, real=True, sample_rows=128)

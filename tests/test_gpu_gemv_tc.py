@@ -73,9 +73,11 @@ def run_tc(type_id, m, n, k, dtype=torch.bfloat16, packed=None, seed=0, check_cp
         if real and k >= 1024 and m * n >= 4096:
             assert elementwise_pass_rate(got, cpu) >= Q8_1_VS_CPU_PASS_FLOOR[type_id]
     if rk.available() and type_id != kq.Q8_0 and scale == 1.0:
-        # the reference's tier on the same inputs (it has no Q8_0 instance): f32 scale products in another order
-        xd = x.cuda().contiguous()
-        theirs = as_f32_numpy(rk.tc_plain(type_id, w_dev, rk.tc_quantize(xd), n, k, m, dtype)).astype(np.float64)
+        # the reference's tier (it has no Q8_0 instance) on the same quantized activations, laid out for it by the oracle
+        # (its own quantizer is built with approximate division, so now and then one of its quants sits a step away):
+        # only the order of the f32 scale products differs
+        vy = torch.from_numpy(kq.quantize_mmvq_tc(as_f32_numpy(x))).cuda()
+        theirs = as_f32_numpy(rk.tc_plain(type_id, w_dev, vy, n, k, m, dtype)).astype(np.float64)
         torch.cuda.synchronize()
         # (two separately rounded outputs may sit one unit of the output type apart: 2 eps)
         off = np.abs(got - theirs) > 1e-4 * size + 2 * EPS[dtype] * 1.01 * np.abs(ref)
@@ -215,3 +217,79 @@ def test_unsupported_inputs_are_refused():
     ws = torch.empty(64, dtype=torch.uint8, device="cuda")
     with pytest.raises(kl.KernelLibraryError, match="workspace"):
         ops.gemv_tc(DT[kq.Q4_K], w_dev, torch.zeros(4, 256, device="cuda", dtype=torch.bfloat16), 128, workspace=ws)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# The reference tier's own pair of launchers: launch_mmvq_tc_quantize_* + launch_mmvq_tc_gguf_{q4_k,q6_k}_*_plain
+# ---------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,k", [(1, 256), (8, 1024), (9, 512), (16, 4096), (5, 1000)])
+def test_reference_activation_layout_is_bit_exact(dtype, rows, k):
+    x = seeded_acts(rows, k, 40 + rows, dtype)
+    mine = ops.mmvq_tc_quantize(x.cuda()).cpu().numpy()
+    torch.cuda.synchronize()
+    want = kq.quantize_mmvq_tc(as_f32_numpy(x))
+    assert mine.shape == want.shape and np.array_equal(mine, want)
+    if rk.available():
+        # the reference's build divides approximately (fast-math): scales identical, a quant may sit one step away
+        theirs = rk.tc_quantize(x.cuda()).cpu().numpy()
+        torch.cuda.synchronize()
+        nb = (k + 31) // 32
+        for h in range((rows + 7) // 8):
+            a, b = mine[h * nb * 288:(h + 1) * nb * 288], theirs[h * nb * 288:(h + 1) * nb * 288]
+            assert np.array_equal(a[nb * 256:nb * 272], b[nb * 256:nb * 272]), "scales differ"
+            dq = a[:nb * 256].view(np.int8).astype(np.int32) - b[:nb * 256].view(np.int8).astype(np.int32)
+            assert np.abs(dq).max() <= 1 and (dq != 0).mean() < 2e-3
+
+
+def run_tc_ref(type_id, m, n, k, dtype=torch.bfloat16, packed=None, seed=0):
+    """quantize + plain through the reference's symbols, with activations built by the ORACLE's layout function as well
+    as by the library's quantizer: both must give the tier's arithmetic."""
+    if packed is None:
+        packed = kq.quantize(type_id, seeded_weights(n, k, 5000 + seed))
+    x = seeded_acts(m, k, 6000 + seed, dtype)
+    w_dev = ops.upload_weights(packed, DT[type_id])
+    vy_oracle = torch.from_numpy(kq.quantize_mmvq_tc(as_f32_numpy(x))).cuda()
+    y = ops.mmvq_tc_plain(DT[type_id], w_dev, vy_oracle, n, k, m, dtype)
+    y2 = ops.mmvq_tc_plain(DT[type_id], w_dev, ops.mmvq_tc_quantize(x.cuda()), n, k, m, dtype)
+    torch.cuda.synchronize()
+    assert_device_ok()
+    assert torch.equal(y, y2)
+    got = as_f32_numpy(y).astype(np.float64)
+    ref = requantized(as_f32_numpy(x)) @ kq.dequantize(type_id, packed, k).astype(np.float64).T
+    size = np.abs(ref).max()
+    bad = np.abs(got - ref) > 2e-5 * size + EPS[dtype] * 1.01 * np.abs(ref)
+    assert not bad.any(), f"{kq.TYPE_NAMES[type_id]} m={m} n={n} k={k}: {bad.sum()} outputs off, worst {np.abs(got - ref).max():.3e} vs {size:.3e}"
+    cpu = kq.matmul(type_id, as_f32_numpy(x), packed, n)
+    assert np.abs(got - cpu).max() <= 1e-3 + (1e-2 if k >= 1024 else 2e-2) * np.abs(cpu).max()
+    if rk.available():
+        theirs = as_f32_numpy(rk.tc_plain(type_id, w_dev, vy_oracle, n, k, m, dtype)).astype(np.float64)
+        torch.cuda.synchronize()
+        off = np.abs(got - theirs) > 1e-4 * size + 2 * EPS[dtype] * 1.01 * np.abs(ref)
+        assert not off.any(), f"{off.sum()} outputs differ from the reference's kernel on the same scratch"
+    return y
+
+
+@pytest.mark.parametrize("type_id", [kq.Q4_K, kq.Q6_K])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 2048), (3, 64, 2048), (8, 1000, 2048), (9, 300, 4096), (16, 148 * 128 + 77, 2048), (12, 9000, 2048)])
+def test_reference_launcher_pair(type_id, m, n, k):
+    run_tc_ref(type_id, m, n, k, seed=m + n)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_reference_launcher_pair_other_types(dtype):
+    run_tc_ref(kq.Q4_K, 7, 512, 1024, dtype=dtype)
+
+
+@pytest.mark.parametrize("type_id", [kq.Q4_K, kq.Q6_K])
+def test_reference_launcher_pair_at_baseline_shapes(type_id):
+    for k, n in ((4096, 4096), (14336, 4096)):
+        packed = real_packed(type_id, n, k)
+        run_tc_ref(type_id, 16, n, k, packed=packed, seed=1)
+        run_tc_ref(type_id, 4, n, k, packed=packed, seed=2)
+
+
+def test_reference_launcher_pair_on_rows_the_tma_path_cannot_take():
+    # Q6_K rows of 210 * k / 256 bytes are a multiple of 16 only when k is a multiple of 2048: other k take the plain kernel
+    run_tc_ref(kq.Q6_K, 5, 200, 768, seed=3)
+    run_tc_ref(kq.Q6_K, 16, 64, 1280, seed=4)

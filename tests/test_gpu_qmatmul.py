@@ -144,6 +144,25 @@ def test_qmatmul_errors_mirror_the_reference():
         QTensor(torch.zeros(100, dtype=torch.uint8, device="cuda"), DT[kq.Q4_K], (1, 100))
 
 
+def test_forward_falls_back_to_two_launches_where_the_one_launch_gemv_declines():
+    from inference_rs_b200 import ops
+    n, k = 96, 512
+    packed = kq.quantize(kq.Q6_K, seeded_weights(n, k, 7))
+    qmm = QMatMul.from_qtensor(QTensor.from_packed(packed, DT[kq.Q6_K], (n, k)))
+    x = seeded_acts(2, k, 8, torch.float32).cuda()
+    want = qmm.forward(x)
+    ops.set_option("force_simple_gemv", 1)  # b200q_gemv now answers B200Q_ERR_UNSUPPORTED
+    try:
+        got = qmm.forward(x)
+        with pytest.raises(pkg.KernelLibraryError):  # the CPU path's format exists only in the one-launch kernel
+            qmm.forward(x, act_quant=ops.ACT_QUANT_CPU)
+    finally:
+        ops.set_option("force_simple_gemv", 0)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(as_f32_numpy(got), as_f32_numpy(want), rtol=0, atol=2e-5 * float(want.abs().max()))
+    assert_device_ok()
+
+
 def test_bias_is_added_after_the_matmul():
     n, k = 32, 256
     packed = kq.quantize(kq.Q8_0, seeded_weights(n, k, 2))
