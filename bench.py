@@ -757,6 +757,44 @@ def main():
 
         extras = not tp and not args.quick and not args.shard_of
 
+        # ---- tensor parallel, the configuration's other two legs: decode at batch 32 and a 2048-token prefill through the
+        # operator (QMatMul routes both to the tile GEMM), the [rows, hidden] sums of the row-parallel projections by NCCL
+        # (512 KiB and 32 MiB: bandwidth-sized, beyond the peer kernel's capacity). Eager launches, CUDA events, max over ranks.
+        tp_extra = None
+        if tp and not args.quick:
+            tp_extra = {}
+            qms = [[pkg.QMatMul.from_qtensor(pkg.QTensor(w, p.dtype, (p.n, p.k))) for p, w in zip(projs, layer)] for layer in chain.layers]
+            head_qm = pkg.QMatMul.from_qtensor(pkg.QTensor(chain.head_w, head.dtype, (head.n, head.k)))
+            for label, rows, reps in (("decode_batch_32", 32, 5), ("prefill_2048", 2048, 2)):
+                xs = {k: torch.randn(rows, k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(k)).to(torch.bfloat16)
+                      for k in chain.ks}
+
+                def big_step():
+                    for layer in qms:
+                        for p, qm in zip(projs, layer):
+                            y = qm.forward(xs[p.k])
+                            if p.split == "row":
+                                dist.all_reduce(y)
+                    head_qm.forward(xs[head.k][-1:] if rows > 32 else xs[head.k])  # a prefill samples from its last token only
+
+                big_step()
+                barrier()
+                b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                b0.record(stream)
+                for _ in range(reps):
+                    big_step()
+                b1.record(stream)
+                barrier()
+                t = torch.tensor([b0.elapsed_time(b1) / reps], device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms_big = float(t.item())
+                flops = 2.0 * rows * sum(p.n * p.k for p in projs) * model.layers
+                tp_extra[label] = {"rows": rows, "ms_per_step": round(ms_big, 3), "tok_per_s": round(rows * 1000.0 / ms_big, 1),
+                                   "TFLOPs_per_gpu": round(flops / (ms_big * 1e-3) / 1e12, 1),
+                                   "allreduce": f"NCCL, {rows * model.hidden * 2 // 1024} KiB per sum"}
+                del xs
+            del qms, head_qm
+
         # ---- the element-wise-exact mode: the same chain with activations quantized to the CPU path's format (Q8_K /
         # Q8_0) in the kernel prologue, one launch per projection (the grouped kernel quantizes to Q8_1 only)
         cpu_format = None
@@ -903,6 +941,8 @@ def main():
     line["hbm_frac_of_nominal_8TBps"] = line["weights_GBps_per_gpu"] / 8000.0
     if tp_check is not None:
         line["tp_check"] = tp_check
+    if tp_extra is not None:
+        line["tp_other_legs"] = tp_extra
     if cpu_format is not None:
         line["cpu_format_activations"] = cpu_format
     if prefill is not None:

@@ -96,6 +96,71 @@ void launch_mmvq_gguf_q8_0_bf16_exact(const void* vx, const void* vy, void* dst,
 void launch_mmvq_gguf_q8_0_f32_exact(const void* vx, const void* vy, void* dst, int ncols_x, int nrows_x, int b_size,
                                      void* stream);
 
+/* Fused decode matvecs on Q8_1 activation blocks (vy as launch_mmvq_gguf_quantize_q8_1_* writes them, stride_col_y
+ * blocks per activation row), b_size 1..8.
+ *  fused_glu: dst[j * stride_col_dst + row] = act(gate[row] . y[j]) * (up[row] . y[j]) for two matrices of the same type
+ *    and shape; gate and up are rounded to the output type, the activation is evaluated in f32 on the rounded gate and
+ *    rounded, the product is formed in the output type. activation: 0 SiLU, 1 GELU (tanh), 2 ReLU, 3 GELU (erf),
+ *    4 sigmoid; other ids mean SiLU.
+ *  fused_qkv: three matrices of one type on the same activations: q_dst[j * nrows_q + row], k_dst[j * nrows_k + row],
+ *    v_dst[j * nrows_v + row].
+ * Replaces crates/inference-quant/src/gguf/ffi.rs:1032-1118 (kernels/cuda/mmvq_gguf/mmvq_gguf.cuh:761-962; host side
+ * fast_mmvq::fused_glu / fused_qkv). */
+void launch_mmvq_gguf_q8_0_bf16_fused_glu(const void* vx_gate, const void* vx_up, const void* vy, void* dst, int ncols_x,
+                                          int nrows_x, int stride_col_y, int stride_col_dst, int b_size, int activation,
+                                          void* stream);
+void launch_mmvq_gguf_q8_0_f16_fused_glu(const void* vx_gate, const void* vx_up, const void* vy, void* dst, int ncols_x,
+                                         int nrows_x, int stride_col_y, int stride_col_dst, int b_size, int activation,
+                                         void* stream);
+void launch_mmvq_gguf_q8_0_f32_fused_glu(const void* vx_gate, const void* vx_up, const void* vy, void* dst, int ncols_x,
+                                         int nrows_x, int stride_col_y, int stride_col_dst, int b_size, int activation,
+                                         void* stream);
+void launch_mmvq_gguf_q4_k_bf16_fused_glu(const void* vx_gate, const void* vx_up, const void* vy, void* dst, int ncols_x,
+                                          int nrows_x, int stride_col_y, int stride_col_dst, int b_size, int activation,
+                                          void* stream);
+void launch_mmvq_gguf_q4_k_f16_fused_glu(const void* vx_gate, const void* vx_up, const void* vy, void* dst, int ncols_x,
+                                         int nrows_x, int stride_col_y, int stride_col_dst, int b_size, int activation,
+                                         void* stream);
+void launch_mmvq_gguf_q4_k_f32_fused_glu(const void* vx_gate, const void* vx_up, const void* vy, void* dst, int ncols_x,
+                                         int nrows_x, int stride_col_y, int stride_col_dst, int b_size, int activation,
+                                         void* stream);
+void launch_mmvq_gguf_q6_k_bf16_fused_glu(const void* vx_gate, const void* vx_up, const void* vy, void* dst, int ncols_x,
+                                          int nrows_x, int stride_col_y, int stride_col_dst, int b_size, int activation,
+                                          void* stream);
+void launch_mmvq_gguf_q6_k_f16_fused_glu(const void* vx_gate, const void* vx_up, const void* vy, void* dst, int ncols_x,
+                                         int nrows_x, int stride_col_y, int stride_col_dst, int b_size, int activation,
+                                         void* stream);
+void launch_mmvq_gguf_q6_k_f32_fused_glu(const void* vx_gate, const void* vx_up, const void* vy, void* dst, int ncols_x,
+                                         int nrows_x, int stride_col_y, int stride_col_dst, int b_size, int activation,
+                                         void* stream);
+void launch_mmvq_gguf_q8_0_bf16_fused_qkv(const void* vx_q, const void* vx_k, const void* vx_v, const void* vy, void* q_dst,
+                                          void* k_dst, void* v_dst, int ncols_x, int nrows_q, int nrows_k, int nrows_v,
+                                          int stride_col_y, int b_size, void* stream);
+void launch_mmvq_gguf_q8_0_f16_fused_qkv(const void* vx_q, const void* vx_k, const void* vx_v, const void* vy, void* q_dst,
+                                         void* k_dst, void* v_dst, int ncols_x, int nrows_q, int nrows_k, int nrows_v,
+                                         int stride_col_y, int b_size, void* stream);
+void launch_mmvq_gguf_q8_0_f32_fused_qkv(const void* vx_q, const void* vx_k, const void* vx_v, const void* vy, void* q_dst,
+                                         void* k_dst, void* v_dst, int ncols_x, int nrows_q, int nrows_k, int nrows_v,
+                                         int stride_col_y, int b_size, void* stream);
+void launch_mmvq_gguf_q4_k_bf16_fused_qkv(const void* vx_q, const void* vx_k, const void* vx_v, const void* vy, void* q_dst,
+                                          void* k_dst, void* v_dst, int ncols_x, int nrows_q, int nrows_k, int nrows_v,
+                                          int stride_col_y, int b_size, void* stream);
+void launch_mmvq_gguf_q4_k_f16_fused_qkv(const void* vx_q, const void* vx_k, const void* vx_v, const void* vy, void* q_dst,
+                                         void* k_dst, void* v_dst, int ncols_x, int nrows_q, int nrows_k, int nrows_v,
+                                         int stride_col_y, int b_size, void* stream);
+void launch_mmvq_gguf_q4_k_f32_fused_qkv(const void* vx_q, const void* vx_k, const void* vx_v, const void* vy, void* q_dst,
+                                         void* k_dst, void* v_dst, int ncols_x, int nrows_q, int nrows_k, int nrows_v,
+                                         int stride_col_y, int b_size, void* stream);
+void launch_mmvq_gguf_q6_k_bf16_fused_qkv(const void* vx_q, const void* vx_k, const void* vx_v, const void* vy, void* q_dst,
+                                          void* k_dst, void* v_dst, int ncols_x, int nrows_q, int nrows_k, int nrows_v,
+                                          int stride_col_y, int b_size, void* stream);
+void launch_mmvq_gguf_q6_k_f16_fused_qkv(const void* vx_q, const void* vx_k, const void* vx_v, const void* vy, void* q_dst,
+                                         void* k_dst, void* v_dst, int ncols_x, int nrows_q, int nrows_k, int nrows_v,
+                                         int stride_col_y, int b_size, void* stream);
+void launch_mmvq_gguf_q6_k_f32_fused_qkv(const void* vx_q, const void* vx_k, const void* vx_v, const void* vy, void* q_dst,
+                                         void* k_dst, void* v_dst, int ncols_x, int nrows_q, int nrows_k, int nrows_v,
+                                         int stride_col_y, int b_size, void* stream);
+
 /* Prefill activation quantizer: rows -> 144-byte blocks of 128 values, block index (k / 128) * ne1 + row.
  * D4 stores four f32 scales, DS4 four half2 (d, sum(x)). type_x: 0 = f32, 1 = f16, 30 = bf16. ne00 = row length,
  * s01 = row stride in elements, ne0 = padded row length (multiple of 128), ne1 = rows; only ne2 = ne3 = 1.

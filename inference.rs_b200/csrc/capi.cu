@@ -234,7 +234,7 @@ int b200q_quantize(int type, const void* x, void* out, long long n, void* stream
     if (!x || !out) return set_error(B200Q_ERR_INVALID, "null pointer");
     const int rc = quantize_weights(type, static_cast<const float*>(x), out, n, (cudaStream_t)stream);
     if (rc == B200Q_ERR_UNSUPPORTED) return set_error(rc, "weight type is not Q8_0, Q4_K or Q6_K");
-    if (rc == B200Q_ERR_INVALID) return set_error(rc, "the number of values is not a multiple of the block size");
+    if (rc == B200Q_ERR_INVALID) return set_error(rc, "the number of values is not a multiple of the block size, or the output is not 2-byte aligned");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "quantize failed");
     return B200Q_OK;
 }

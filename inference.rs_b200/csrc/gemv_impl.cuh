@@ -20,6 +20,8 @@
 //    partial sums in a fixed order, so results are deterministic.
 //  * Every mbarrier wait is bounded and reports through the device status word.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 #include "peer_allreduce.cuh"
 #include "runtime.h"
@@ -1087,9 +1089,10 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
     }
 }
 
-template <typename dst_t, typename act_t, int NREG>
+// ACT: ACT_RAW_Q8_1 (raw row, quantized here to Q8_1 as the two-launch protocol does) or ACT_Q8_1 (blocks already
+// quantized by the caller: the reference's fused q/k/v launcher)
+template <typename dst_t, typename act_t, int NREG, int ACT = ACT_RAW_Q8_1>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvGroupParams p) {
-    constexpr int ACT = ACT_RAW_Q8_1;  // activations quantized to Q8_1, as the two-launch protocol does
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + GEMV_MAX_STAGES;
@@ -1164,8 +1167,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
         pre.issue(p.act, 1, p.K, p.K, p.act_vec != 0, tid);
     }
     // the activation row is quantized once for all matrices
-    stage_acts_raw<1, act_t, TYPE_Q4_K, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.K, p.act_vec != 0, tid,
-                                             GEMV_CONSUMER_THREADS, pre);
+    if constexpr (ACT == ACT_Q8_1)
+        stage_acts_q8_1<1>(acts, reinterpret_cast<const uint8_t*>(p.act), p.K, 0, tid, GEMV_CONSUMER_THREADS, pre);
+    else
+        stage_acts_raw<1, act_t, TYPE_Q4_K, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.K, p.act_vec != 0, tid,
+                                                 GEMV_CONSUMER_THREADS, pre);
     named_bar_sync(1, GEMV_CONSUMER_THREADS);
 
     const int items = p.K / 128;
@@ -1403,8 +1409,10 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     if (S < 2) return plan;  // does not fit: simple kernel
     p.nstages = S;
     R = p.rows_per_stage;
-    // first stage: one pass of all warps where a stage holds two, so that the first rows land in half the time
-    p.first_rows = (passes == 2 && R % 2 == 0 && (R / 2) % unit0 == 0) ? R / 2 : R;
+    // (a smaller first stage lands sooner, but a stage of one pass gives every warp a single row, and a warp needs two
+    // rows in flight to hide its latencies: measured slower on every decode shape, so all stages are equal)
+    p.first_rows = R;
+    (void)unit0;
     const long long units = (N + p.row_align - 1) / p.row_align;
     long long grid = rt.sm_count;
     if (grid > units) grid = units;
@@ -1534,7 +1542,7 @@ static inline int launch_gemv(const void* vx, const void* act, void* dst, int K,
 
 // Plans and launches a grouped GEMV (one activation row). Returns B200Q_ERR_UNSUPPORTED when the group does not fit
 // the staged kernel's preconditions; the caller then launches the matrices one by one.
-template <typename dst_t>
+template <typename dst_t, int ACT = ACT_RAW_Q8_1>
 static inline int launch_gemv_group(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K,
                                     const void* x, cudaStream_t s) {
     const RuntimeInfo& rt = runtime_info();
@@ -1604,9 +1612,10 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
         cfg.numAttrs = p.use_pdl ? 1 : 0;
         return (int)cudaLaunchKernelEx(&cfg, kernel, p);
     };
-    if (nreg == 1) return launch(gemv_group_kernel<dst_t, dst_t, 1>);
-    if (nreg == 2) return launch(gemv_group_kernel<dst_t, dst_t, 2>);
-    return launch(gemv_group_kernel<dst_t, dst_t, 0>);
+    using act_t = typename std::conditional<ACT == ACT_Q8_1, float, dst_t>::type;
+    if (nreg == 1) return launch(gemv_group_kernel<dst_t, act_t, 1, ACT>);
+    if (nreg == 2) return launch(gemv_group_kernel<dst_t, act_t, 2, ACT>);
+    return launch(gemv_group_kernel<dst_t, act_t, 0, ACT>);
 }
 
 // One weight type's dispatcher over the output element type; defined once per type in gemv_<type>.cu.

@@ -49,11 +49,14 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* __restr
     for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(xb[i]));
     const float d = amax / 127.0f;
     const float id = d != 0.0f ? 1.0f / d : 0.0f;
-    uint8_t* o = out + b * Q8_0_BYTES;
-    const unsigned short dh = f16_bits(d);
-    o[0] = (uint8_t)dh;
-    o[1] = (uint8_t)(dh >> 8);
-    for (int i = 0; i < 32; ++i) o[2 + i] = (uint8_t)(int8_t)sat_i8(roundf(xb[i] * id));
+    // a block is 34 bytes at a 2-byte-aligned address: seventeen 16-bit stores
+    unsigned short* o = reinterpret_cast<unsigned short*>(out + b * Q8_0_BYTES);
+    o[0] = f16_bits(d);
+    for (int i = 0; i < 16; ++i) {
+        const unsigned lo = (unsigned)sat_i8(roundf(xb[2 * i] * id)) & 0xffu;
+        const unsigned hi = (unsigned)sat_i8(roundf(xb[2 * i + 1] * id)) & 0xffu;
+        o[1 + i] = (unsigned short)(lo | (hi << 8));
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -349,7 +352,7 @@ __global__ void __launch_bounds__(256) dequant_rows_kernel(int type, const uint8
 
 int quantize_weights(int type, const float* x, void* out, long long n, cudaStream_t s) {
     if (type_block_bytes(type) == 0) return B200Q_ERR_UNSUPPORTED;
-    if (n < 0 || n % type_block_elems(type) != 0) return B200Q_ERR_INVALID;
+    if (n < 0 || n % type_block_elems(type) != 0 || reinterpret_cast<uintptr_t>(out) % 2 != 0) return B200Q_ERR_INVALID;
     if (n == 0) return 0;
     const long long nb = n / type_block_elems(type);
     if (type == TYPE_Q8_0) quantize_q8_0_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, s>>>(x, static_cast<uint8_t*>(out), nb);

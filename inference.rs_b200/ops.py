@@ -114,6 +114,40 @@ def mmvq_plain(dtype: GgmlDType, w: torch.Tensor, vy: torch.Tensor, n: int, k: i
     return dst
 
 
+GLU_ACTIVATIONS = {"silu": 0, "gelu": 1, "relu": 2, "gelu_erf": 3, "sigmoid": 4}  # kernels/cuda/glu_activation.cuh:4-10
+
+
+def mmvq_fused_glu(dtype: GgmlDType, w_gate: torch.Tensor, w_up: torch.Tensor, vy: torch.Tensor, n: int, k: int, b: int,
+                   out_dtype: torch.dtype, activation: str = "silu", k_padded: int | None = None) -> torch.Tensor:
+    """`launch_mmvq_gguf_<type>_<out>_fused_glu` on Q8_1 blocks `vy`: act(y . gate^T) * (y . up^T), [b, n]
+    (fast_mmvq::fused_glu, crates/inference-quant/src/gguf/fast_mmvq.rs)."""
+    _require_cuda(w_gate, w_up, vy)
+    k_padded = pad(k, MATRIX_ROW_PADDING) if k_padded is None else k_padded
+    dst = torch.empty((b, n), dtype=out_dtype, device=vy.device)
+    name = f"launch_mmvq_gguf_{dtype.tag}_{ELEM_TAG[elem_of(out_dtype)]}_fused_glu"
+    getattr(kl.library(), name)(w_gate.data_ptr(), w_up.data_ptr(), vy.data_ptr(), dst.data_ptr(), k, n, k_padded // 32, n, b,
+                                GLU_ACTIVATIONS[activation], _stream())
+    rc = kl.library().b200q_take_launch_status()
+    if rc:
+        raise kl.KernelLibraryError(f"{name} failed with status {rc}")
+    return dst
+
+
+def mmvq_fused_qkv(dtype: GgmlDType, wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, vy: torch.Tensor, nq: int, nk: int,
+                   nv: int, k: int, b: int, out_dtype: torch.dtype, k_padded: int | None = None) -> list[torch.Tensor]:
+    """`launch_mmvq_gguf_<type>_<out>_fused_qkv` on Q8_1 blocks `vy`: the three projections [b, nq], [b, nk], [b, nv]."""
+    _require_cuda(wq, wk, wv, vy)
+    k_padded = pad(k, MATRIX_ROW_PADDING) if k_padded is None else k_padded
+    outs = [torch.empty((b, n), dtype=out_dtype, device=vy.device) for n in (nq, nk, nv)]
+    name = f"launch_mmvq_gguf_{dtype.tag}_{ELEM_TAG[elem_of(out_dtype)]}_fused_qkv"
+    getattr(kl.library(), name)(wq.data_ptr(), wk.data_ptr(), wv.data_ptr(), vy.data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(),
+                                outs[2].data_ptr(), k, nq, nk, nv, k_padded // 32, b, _stream())
+    rc = kl.library().b200q_take_launch_status()
+    if rc:
+        raise kl.KernelLibraryError(f"{name} failed with status {rc}")
+    return outs
+
+
 MMQ_LAYOUT = {GgmlDType.Q8_0: "D4", GgmlDType.Q4K: "DS4", GgmlDType.Q6K: "D4"}  # fast_mmq.rs:167-190
 
 

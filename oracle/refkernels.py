@@ -108,11 +108,12 @@ def mmvq(type_id: int, w, x, n: int):
     return mmvq_plain(type_id, w, quantize_q8_1(x), n, x.shape[1], x.shape[0], x.dtype)
 
 
-def fused_glu(type_id: int, w_gate, w_up, x, n: int, activation: str = "silu"):
-    """act(x . gate^T) * (x . up^T) in one launch (launch_mmvq_gguf_<type>_<elem>_fused_glu), b = 1..8."""
+def fused_glu(type_id: int, w_gate, w_up, x, n: int, activation: str = "silu", vy=None):
+    """act(x . gate^T) * (x . up^T) in one launch (launch_mmvq_gguf_<type>_<elem>_fused_glu), b = 1..8; on the Q8_1
+    blocks `vy` of x where given, else on the reference quantizer's."""
     import torch
     b, k = x.shape
-    vy = quantize_q8_1(x)
+    vy = quantize_q8_1(x) if vy is None else vy
     out = torch.empty(b, n, dtype=x.dtype, device=x.device)
     getattr(lib(), f"launch_mmvq_gguf_{NAMES[type_id]}_{_elem(x.dtype)}_fused_glu")(
         w_gate.data_ptr(), w_up.data_ptr(), vy.data_ptr(), out.data_ptr(), k, n, vy.numel() // 36 // b, n, b,
@@ -120,11 +121,12 @@ def fused_glu(type_id: int, w_gate, w_up, x, n: int, activation: str = "silu"):
     return out
 
 
-def fused_qkv(type_id: int, wq, wk, wv, x, nq: int, nk: int, nv: int):
-    """q, k, v projections of one input in one launch (launch_mmvq_gguf_<type>_<elem>_fused_qkv), b = 1..8."""
+def fused_qkv(type_id: int, wq, wk, wv, x, nq: int, nk: int, nv: int, vy=None):
+    """q, k, v projections of one input in one launch (launch_mmvq_gguf_<type>_<elem>_fused_qkv), b = 1..8; on the Q8_1
+    blocks `vy` of x where given, else on the reference quantizer's."""
     import torch
     b, k = x.shape
-    vy = quantize_q8_1(x)
+    vy = quantize_q8_1(x) if vy is None else vy
     outs = [torch.empty(b, n, dtype=x.dtype, device=x.device) for n in (nq, nk, nv)]
     getattr(lib(), f"launch_mmvq_gguf_{NAMES[type_id]}_{_elem(x.dtype)}_fused_qkv")(
         wq.data_ptr(), wk.data_ptr(), wv.data_ptr(), vy.data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(),

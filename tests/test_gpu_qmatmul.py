@@ -243,6 +243,31 @@ def _peer_rank(rank, world, port, ret):
             gathered = [torch.empty_like(got) for _ in range(world)]
             dist.all_gather(gathered, got)
             same = same and all(torch.equal(gathered[0], t) for t in gathered)  # identical bits on every rank
+        # calls of different sizes straight after one another, nothing in between that would line the ranks up again: a
+        # slot's inboxes do not depend on the vector's length, so no call may touch what a slower peer is still reading
+        shapes = [((1, 8192), torch.bfloat16), ((16, 2048), torch.float16), ((3, 1000), torch.float32), ((1, 8), torch.bfloat16),
+                  ((2, 4096), torch.bfloat16), ((1, 24), torch.float32), ((16, 2048), torch.bfloat16)] * 4
+        ins, outs = [], []
+        for i, (shape, dtype) in enumerate(shapes):
+            g = torch.Generator().manual_seed(5000 + 10 * i + rank)
+            ins.append(torch.randn(*shape, generator=g).to(dtype).cuda(rank))
+        torch.cuda.synchronize()
+        for x in ins:
+            outs.append(ar.sum_all_reduce(x))
+        torch.cuda.synchronize()
+        for x, got in zip(ins, outs):
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            tol = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -22}[x.dtype]
+            worst = max(worst, float(((got.float() - ref).abs() / (ref.abs() + 1e-3)).max()) / tol)
+        # the row-parallel layer takes the fused launch when it is given the peer exchange, and gives the same bits
+        from inference_rs_b200.tensor_parallel import RowParallelLayer as RPL
+        packed_l = kq.quantize(kq.Q4_K, seeded_weights(2048, 4096, 77))
+        lay_peer = RPL(packed_l, DT[kq.Q4_K], (2048, 4096), rank, world, device=f"cuda:{rank}", all_reduce=ar)
+        lay_nccl = RPL(packed_l, DT[kq.Q4_K], (2048, 4096), rank, world, device=f"cuda:{rank}")
+        xs = seeded_acts(1, 4096 // world, 78 + rank, torch.bfloat16).cuda(rank)
+        y_peer, y_nccl = lay_peer(xs), lay_nccl(xs)
+        same = same and float((y_peer.float() - y_nccl.float()).abs().max()) <= 2.0 ** -7 * float(y_nccl.float().abs().max())
         # the fused launch (row-parallel matmul + exchange) equals the two separate calls bit for bit
         from inference_rs_b200 import ops as ops_
         fused_ok = True
@@ -290,6 +315,30 @@ def test_peer_memory_all_reduce_matches_nccl_and_is_identical_on_all_ranks():
         for r in range(world):
             worst, same, replay_ok, status = ret[r]
             assert worst <= 1.01 and same and replay_ok and status[0] == 0, dict(ret)
+
+
+def test_kernels_run_on_a_second_device_of_the_same_process():
+    """Kernel attributes (dynamic shared memory) belong to a (function, device) pair: every kernel family once on device 0,
+    then on device 1."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from inference_rs_b200 import ops
+    n, k = 512, 2048
+    packed = kq.quantize(kq.Q4_K, seeded_weights(n, k, 90))
+    outs = []
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            w = ops.upload_weights(packed, DT[kq.Q4_K], f"cuda:{dev}")
+            x1 = seeded_acts(1, k, 91, torch.bfloat16).cuda(dev)
+            x8 = seeded_acts(8, k, 92, torch.bfloat16).cuda(dev)
+            x64 = seeded_acts(64, k, 93, torch.bfloat16).cuda(dev)
+            res = [ops.gemv(DT[kq.Q4_K], w, x1, n), ops.gemv_group([DT[kq.Q4_K]] * 2, [w, w], x1, [n, n])[1],
+                   ops.gemv_tc(DT[kq.Q4_K], w, x8, n), ops.gemm(DT[kq.Q4_K], w, x64, n)]
+            torch.cuda.synchronize(dev)
+            outs.append([r.cpu() for r in res])
+            assert pkg.kernel_library.device_status()[0] == 0
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
 
 
 def test_column_then_row_parallel_over_nccl():
