@@ -213,8 +213,10 @@ const char* b200q_version(void);
 const char* b200q_last_error(void);
 
 /* Options: "pdl" (launch GEMVs and quantizers with programmatic stream serialization), "force_simple_gemv",
- * "gemv_stage_bytes", "l2_prefetch_bytes" (see b200q_set_weight_successor; 0 switches the prefetch off). get also
- * answers "sm_count" and "smem_optin". */
+ * "gemv_stage_bytes", "gemv_passes" (0 = the planner's choice, 1 or 2 passes of all warps per stage),
+ * "gemv_pass_limit_bytes" (bytes one pass may cover before a row is given more warps), "gemv_ctas_per_sm", "tc_ksplit",
+ * "gemm_direct", "l2_prefetch_bytes" (see b200q_set_weight_successor; 0 switches the prefetch off). get also answers
+ * "sm_count" and "smem_optin". */
 int b200q_set_option(const char* name, int value);
 int b200q_get_option(const char* name, int* value);
 
@@ -309,9 +311,10 @@ int b200q_gemv_tc(int type, int elem, const void* w, const void* x, void* y, int
  * crates/inference-quant/src/distributed/mod.rs:516-670; distributed/layers.rs:814-1190). Every rank calls it with the
  * same n and elem; out = sum over ranks of in, added in rank order in f32, so all ranks hold identical bits; in == out
  * is allowed. `bufs` is a host array of `world` device pointers: every rank's exchange buffer as mapped in THIS
- * process (bufs[rank] is the local one), each b200q_peer_allreduce_buffer_bytes(capacity) bytes (about 32 capacity: an inbox
- * per source rank, half and slot), zeroed once before
- * the first call and otherwise touched only by this function; capacity (bytes, multiple of 16) bounds n * sizeof(elem).
+ * process (bufs[rank] is the local one), each b200q_peer_allreduce_buffer_bytes(capacity) bytes (1 KB + 64 capacity: per
+ * path - this function, b200q_gemv_allreduce - and call parity an inbox per source rank of twice the vector's size,
+ * because every 8 bytes travel together with the number of the call they belong to), zeroed once before the first call
+ * and otherwise touched only by these two functions; capacity (bytes, multiple of 16) bounds n * sizeof(elem).
  * Needs 16-byte aligned in / out and n * sizeof(elem) a multiple of 16; world <= 8. Device-side sequence numbers only:
  * captured calls can be replayed. A rank that never arrives makes the others give up after about a second, set the
  * device status word (b200q_device_status) and leave `out` unwritten. */
@@ -321,11 +324,12 @@ int b200q_peer_allreduce(const void* const* bufs, int rank, int world, long long
 
 /* The row-parallel matmul and its exchange in ONE launch (the reference runs them as two operations:
  * RowParallelLayer::forward_raw, crates/inference-quant/src/distributed/layers.rs:1036-1046): b200q_gemv on contiguous
- * x [b_size][K] -> dst [b_size][N] whose last CTA to finish (device-wide arrival counter in the exchange buffer) runs
- * b200q_peer_allreduce's protocol on dst in place, so that after the launch every rank's dst holds the sum of all
- * ranks' partial outputs, bit-identical on all ranks and to b200q_gemv followed by b200q_peer_allreduce. Same `bufs`,
- * `capacity` and calling discipline as b200q_peer_allreduce (all ranks, same order); b_size * N * sizeof(elem) must be a
- * multiple of 16 and at most `capacity`, dst 16-byte aligned; B200Q_ERR_UNSUPPORTED otherwise or where b200q_gemv has
+ * x [b_size][K] -> dst [b_size][N] in which every CTA, when its rows are done, sends them to all ranks and adds up what
+ * the same CTA of every rank sent (b200q_peer_allreduce's protocol, piece by piece), so that after the launch every
+ * rank's dst holds the sum of all ranks' partial outputs, bit-identical on all ranks and to b200q_gemv followed by
+ * b200q_peer_allreduce. Same `bufs`, `capacity` and calling discipline as b200q_peer_allreduce (all ranks, same order);
+ * N * sizeof(elem) must be a multiple of 8, b_size * N * sizeof(elem) at most `capacity`, dst 8-byte aligned and
+ * contiguous; B200Q_ERR_UNSUPPORTED otherwise or where b200q_gemv has
  * no staged kernel for the shape (then: the two separate calls). world == 1 is a plain b200q_gemv. */
 int b200q_gemv_allreduce(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int b_size,
                          const void* const* bufs, int rank, int world, long long capacity, void* stream);

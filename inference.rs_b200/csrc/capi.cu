@@ -57,6 +57,12 @@ int b200q_set_option(const char* name, int value) {
     } else if (!std::strcmp(name, "l2_prefetch_bytes")) {
         if (value < 0) return set_error(B200Q_ERR_INVALID, "l2_prefetch_bytes must be >= 0");
         rt.l2_prefetch_bytes = value & ~15;
+    } else if (!std::strcmp(name, "gemv_passes")) {
+        if (value < 0 || value > 2) return set_error(B200Q_ERR_INVALID, "gemv_passes is 0 (planner's choice), 1 or 2");
+        rt.gemv_passes = value;
+    } else if (!std::strcmp(name, "gemv_pass_limit_bytes")) {
+        if (value < 1024) return set_error(B200Q_ERR_INVALID, "gemv_pass_limit_bytes must be >= 1024");
+        rt.gemv_pass_limit = value;
     } else if (!std::strcmp(name, "gemv_ctas_per_sm")) {
         if (value != 1 && value != 2) return set_error(B200Q_ERR_INVALID, "gemv_ctas_per_sm is 1 or 2");
         rt.gemv_ctas_per_sm = value;
@@ -72,6 +78,8 @@ int b200q_get_option(const char* name, int* value) {
     else if (!std::strcmp(name, "force_simple_gemv")) *value = rt.force_simple;
     else if (!std::strcmp(name, "gemv_stage_bytes")) *value = rt.gemv_stage_target;
     else if (!std::strcmp(name, "gemv_ctas_per_sm")) *value = rt.gemv_ctas_per_sm;
+    else if (!std::strcmp(name, "gemv_passes")) *value = rt.gemv_passes;
+    else if (!std::strcmp(name, "gemv_pass_limit_bytes")) *value = rt.gemv_pass_limit;
     else if (!std::strcmp(name, "gemm_direct")) *value = rt.gemm_direct;
     else if (!std::strcmp(name, "tc_ksplit")) *value = rt.tc_ksplit;
     else if (!std::strcmp(name, "l2_prefetch_bytes")) *value = rt.l2_prefetch_bytes;

@@ -93,7 +93,9 @@ struct GemvParams {
     int act_vec;         // raw activations: rows are 16-byte aligned
     unsigned int* status;  // device status word
     unsigned long long* trace;  // optional: 16 timestamps (ns) written by the first and by the last CTA, or nullptr
-    PeerExchange px;     // px.world > 1: the last CTA to finish sums dst over the ranks in place (row-parallel matmul)
+    PeerExchange px;     // px.world > 1: every CTA exchanges its rows of dst with the other ranks and stores their sum
+    int ar_rows;         // fused exchange: rows per activation row of the CTA's output staging area (a multiple of row_align)
+    int ar_offset;       // and its offset in dynamic shared memory
     NextPrefetch next;   // the registered successor matrix, or w == nullptr
 };
 
@@ -742,25 +744,18 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
                 if (item0 + j * item_step < items) areg[b][j].load(acts_addr + b * act_row_bytes, item0 + j * item_step);
     }
 
-    // Row-parallel matmul with the exchange fused in: every output is pushed, as it is produced, into this rank's inbox
-    // in EVERY rank's exchange buffer (plain peer stores over NVLink, the own buffer included); the last CTA to finish
-    // then only raises the flags, waits for the peers' and adds the inboxes of the local buffer (peer_allreduce.cuh).
+    // Row-parallel matmul with the exchange fused in (peer_allreduce.cuh): the CTA keeps its rows of the output in shared
+    // memory and, when its last row is done, pushes them to every rank and sums what the same CTA of every rank pushed.
     unsigned int ar_epoch = 0;
-    long long ar_inbox = 0;
+    dst_t* ar_stage = reinterpret_cast<dst_t*>(smem + p.ar_offset);
     if constexpr (AR) {
-        // the call number: one more than the finished calls (written by the last CTA of the previous launch, which this
-        // grid was ordered after - by the stream, or by grid_dependency_wait above under programmatic launch)
-        ar_epoch = *reinterpret_cast<volatile unsigned int*>(p.px.bufs[p.px.rank] + PAR_EPOCH_OFFSET + 4 * PAR_FUSED_BLOCK) + 1u;
-        ar_inbox = par_fused_inbox_offset(p.px.capacity, ar_epoch & 1u, p.px.rank);
+        // the call number: one more than the finished launches (published by the last CTA of the previous launch,
+        // which this grid was ordered after - by the stream, or by grid_dependency_wait above under programmatic launch)
+        ar_epoch = par_next_epoch(*reinterpret_cast<volatile unsigned int*>(par_header(p.px) + PAR_EPOCH_FUSED));
     }
     auto store_out = [&](int b, int row, float v) {
-        if constexpr (AR) {
-            const dst_t o = from_float<dst_t>(v);
-            const size_t at = (size_t)ar_inbox + ((size_t)b * p.N + row) * sizeof(dst_t);
-            for (int r = 0; r < p.px.world; ++r) *reinterpret_cast<dst_t*>(p.px.bufs[r] + at) = o;
-        } else {
-            dst[(size_t)b * p.stride_dst + row] = from_float<dst_t>(v);
-        }
+        if constexpr (AR) ar_stage[b * p.ar_rows + (row - row0)] = from_float<dst_t>(v);
+        else dst[(size_t)b * p.stride_dst + row] = from_float<dst_t>(v);
     };
     GEMV_TRACE(7);
     bool alive = true;
@@ -923,26 +918,27 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         if (rot >= rows_per_pass) rot -= rows_per_pass;
     }
     if constexpr (AR) {
-        // the CTA that finishes last (device-wide arrival counter in the exchange buffer) completes the exchange: no
-        // second launch, no second trip through the host queue, one NVLink crossing on the critical path
-        __shared__ unsigned int s_px[3];
-        __threadfence_system();  // this thread's pushes, at every rank, before the CTA is counted
-        named_bar_sync(1, GEMV_CONSUMER_THREADS);
-        if (tid == 0) {
-            unsigned int* counter = reinterpret_cast<unsigned int*>(p.px.bufs[p.px.rank] + PAR_COUNTER_OFFSET);
-            const unsigned int before = atomicAdd(counter, 1u);
-            s_px[2] = before == gridDim.x - 1 ? 1u : 0u;
-            if (s_px[2]) *counter = 0u;  // for the next launch
+        // Every CTA completes the exchange for its own rows: 8-byte pieces of the [B][N] output (row0 and the row count
+        // are whole pieces: the planner aligned the CTA's row range), each stamped with the call number and stored into
+        // this rank's inbox on every rank, then summed from the local inboxes as the peers' CTAs deliver theirs. No
+        // fence, no flag, no last CTA: one NVLink crossing after the slowest rank's CTA has finished its rows.
+        named_bar_sync(1, GEMV_CONSUMER_THREADS);  // the CTA's outputs are in shared memory
+        constexpr int PIECE = 8 / (int)sizeof(dst_t);
+        const int pieces_per_row = (row1 - row0) / PIECE;
+        const int total = B * pieces_per_row;
+        for (int i = tid; i < total; i += GEMV_CONSUMER_THREADS) {
+            const int b = B == 1 ? 0 : i / pieces_per_row, pr = i - b * pieces_per_row;
+            const uint2 mine = *reinterpret_cast<const uint2*>(ar_stage + b * p.ar_rows + pr * PIECE);
+            peer_push_piece<dst_t>(p.px, PAR_PATH_FUSED, ar_epoch, ((long long)b * p.N + row0) / PIECE + pr, mine);
+        }
+        for (int i = tid; i < total; i += GEMV_CONSUMER_THREADS) {
+            const int b = B == 1 ? 0 : i / pieces_per_row, pr = i - b * pieces_per_row;
+            const long long piece = ((long long)b * p.N + row0) / PIECE + pr;
+            uint2 sum;
+            if (peer_sum_piece<dst_t>(p.px, PAR_PATH_FUSED, ar_epoch, piece, sum, p.status)) reinterpret_cast<uint2*>(p.dst)[piece] = sum;
         }
         named_bar_sync(1, GEMV_CONSUMER_THREADS);
-        if (s_px[2]) {
-            __threadfence_system();  // the other CTAs' pushes, ordered before theirs counts, before this rank's flags go up
-            const long long units = (long long)B * p.N * (long long)sizeof(dst_t) / 16;
-            peer_signal_wait_reduce<dst_t, true>(p.px, PAR_FUSED_BLOCK, ar_epoch, par_fused_inbox_offset(p.px.capacity, ar_epoch & 1u, 0),
-                                                 p.px.capacity, p.dst, units, tid, GEMV_CONSUMER_THREADS, p.status, s_px);
-            if (tid == 0)
-                *reinterpret_cast<volatile unsigned int*>(p.px.bufs[p.px.rank] + PAR_EPOCH_OFFSET + 4 * PAR_FUSED_BLOCK) = ar_epoch;
-        }
+        if (tid == 0) peer_finish_call(p.px, PAR_EPOCH_FUSED, PAR_COUNT_FUSED, ar_epoch, gridDim.x);
     }
     GEMV_TRACE(4);
 }
@@ -1331,7 +1327,7 @@ struct GemvPlan {
 
 // Chooses the lane-to-item mapping, rows per stage, ring depth and grid for a shape. `w` is only inspected for
 // alignment (nullptr = assume aligned).
-static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
+static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w, int out_piece_rows = 1) {
     const RuntimeInfo& rt = runtime_info();
     GemvPlan plan{};
     GemvParams& p = plan.p;
@@ -1340,6 +1336,15 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     p.N = N;
     p.row_bytes = K / be * bb;
     p.row_align = 16 / gcd_int(p.row_bytes, 16);
+    // fused exchange (out_piece_rows > 1): every CTA's row range is whole 8-byte pieces of the output, and the CTA keeps
+    // its outputs in shared memory until it exchanges them
+    if (out_piece_rows > 1) p.row_align = p.row_align * out_piece_rows / gcd_int(p.row_align, out_piece_rows);
+    const long long units = (N + p.row_align - 1) / p.row_align;
+    long long grid = rt.sm_count;
+    if (grid > units) grid = units;
+    if (grid < 1) grid = 1;
+    p.ar_rows = (int)((units + grid - 1) / grid) * p.row_align;
+    const int ar_bytes = out_piece_rows > 1 ? ((B * p.ar_rows * 4 + 127) & ~127) : 0;
     p.act_bytes = ((B * (K / 64) * ACT_REC_BYTES) + 127) & ~127;
     p.use_pdl = rt.use_pdl;
     plan.staged = false;
@@ -1364,7 +1369,7 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     }
     // keep a stage (one pass of all warps) under ~48 KB: trade the second slot for more warps per row
     while (ipl > 1 && wpr < GEMV_CONSUMER_WARPS &&
-           (long long)(GEMV_CONSUMER_WARPS / wpr) * rpw * p.row_bytes > 48 * 1024) {
+           (long long)(GEMV_CONSUMER_WARPS / wpr) * rpw * p.row_bytes > rt.gemv_pass_limit) {
         ipl /= 2;
         wpr *= 2;
     }
@@ -1377,7 +1382,7 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     plan.nreg = (B == 1 && ipl <= 2) ? ipl : ((B == 2 && ipl == 1) ? 1 : 0);
     // with one register-resident slot a warp keeps two rows of a stage in flight (rows r and r + rows_per_pass), so a
     // stage holds two passes
-    const int passes = plan.nreg == 1 ? 2 : 1;
+    const int passes = plan.nreg == 1 ? (rt.gemv_passes == 1 ? 1 : 2) : 1;
     const int unit0 = rows_per_pass * p.row_align / gcd_int(rows_per_pass, p.row_align);
     const int unit = unit0 * passes;
     int R = passes * rt.gemv_stage_target / (unit * p.row_bytes) * unit;
@@ -1390,7 +1395,7 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     p.log2_islots = 0;
     while ((1 << p.log2_islots) < islots) ++p.log2_islots;
     p.stage_bytes = (R * p.row_bytes + 16 + 127) & ~127;
-    const int budget = rt.smem_optin - 1024;  // one CTA per SM; 1 KB per CTA is reserved by the system
+    const int budget = rt.smem_optin - 1024 - ar_bytes;  // one CTA per SM; 1 KB per CTA is reserved by the system
     int S = 0;
     for (;;) {
         p.rows_per_stage = R;
@@ -1413,10 +1418,8 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w) {
     // rows in flight to hide its latencies: measured slower on every decode shape, so all stages are equal)
     p.first_rows = R;
     (void)unit0;
-    const long long units = (N + p.row_align - 1) / p.row_align;
-    long long grid = rt.sm_count;
-    if (grid > units) grid = units;
-    if (grid < 1) grid = 1;
+    p.ar_offset = (int)plan.smem;
+    plan.smem += ar_bytes;
     plan.grid = (int)grid;
     p.units_per_cta = (int)(units / grid);
     p.units_extra = (int)(units % grid);
@@ -1492,7 +1495,15 @@ static inline int launch_staged(const GemvPlan& plan, cudaStream_t s) {
 template <int TYPE, int B, typename dst_t>
 static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int K, int N, int stride_act, int stride_dst,
                                 int act_mode, const PeerExchange* px, cudaStream_t s) {
-    GemvPlan plan = plan_gemv(TYPE, K, N, B, vx);
+    const bool exchange = px != nullptr && px->world > 1;
+    constexpr int PIECE = 8 / (int)sizeof(dst_t);  // output rows per 8-byte piece of the exchange
+    if (exchange) {
+        // fused all-reduce: contiguous [B][N] output, rows of whole 8-byte pieces, within the capacity; staged kernel only
+        const long long bytes = (long long)B * N * (long long)sizeof(dst_t);
+        if (stride_dst != N || N % PIECE != 0 || bytes > px->capacity || reinterpret_cast<uintptr_t>(dst) % 8 != 0) return B200Q_ERR_UNSUPPORTED;
+    }
+    GemvPlan plan = plan_gemv(TYPE, K, N, B, vx, exchange ? PIECE : 1);
+    if (exchange && !plan.staged) return B200Q_ERR_UNSUPPORTED;
     plan.p.w = (const uint8_t*)vx;
     plan.p.act = act;
     plan.p.dst = dst;
@@ -1501,14 +1512,8 @@ static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int 
     plan.p.status = status_ptr();
     plan.p.trace = trace_slot();
     plan.p.px.world = 0;
+    if (exchange) plan.p.px = *px;
     plan.p.next = plan_next_prefetch(vx);
-    if (px != nullptr && px->world > 1) {
-        // fused all-reduce: the staged kernel only, contiguous [B][N] output of whole 16-byte units within the capacity
-        const long long bytes = (long long)B * N * (long long)sizeof(dst_t);
-        if (!plan.staged || stride_dst != N || bytes % 16 != 0 || bytes > px->capacity || reinterpret_cast<uintptr_t>(dst) % 16 != 0)
-            return B200Q_ERR_UNSUPPORTED;
-        plan.p.px = *px;
-    }
     if (plan.staged) {
         if (act_mode == ACT_Q8_1) return launch_staged<TYPE, B, dst_t, ACT_Q8_1, float>(plan, s);
         // raw activations have the output's type

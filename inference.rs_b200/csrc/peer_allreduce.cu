@@ -5,22 +5,20 @@
 // NCCL all-reduce is a launch of its own of some tens of microseconds, 160 times per token.
 //
 // Every rank owns one buffer of the same layout (peer_allreduce.cuh), mapped into every other rank's address space (the
-// caller provides the mappings; the Python side gets them from torch's symmetric memory). The exchange PUSHES: a call
-// on every rank (same sizes everywhere) runs up to seven independent blocks, block i on bytes [i * slot_cap, (i + 1) *
-// slot_cap) of the vector:
-//   1. e = ++epoch[i]; store the slice of `in` into inbox[i][e & 1][my rank] of EVERY rank's buffer (plain peer stores
-//      over NVLink, the own buffer included); system-scope fence;
-//   2. write e into arrive[i][my rank] of every peer (release), then wait until every arrive[i][r] of the own buffer has
-//      reached e (acquire): all ranks' slices have landed here;
-//   3. read the slice from the `world` inboxes of the LOCAL buffer in rank order, add in f32, store to `out`: every rank
-//      computes the same sum in the same order, so all ranks hold identical bits.
-// One NVLink crossing lies on the critical path (stores, then the flag), and nothing is read remotely. The two halves
-// make a second barrier unnecessary: a rank writes half e & 1 of a peer's inbox again only in its call e + 2, which it
-// enters after its call e + 1 has seen that peer's signal e + 1, sent after the peer finished reading in call e. A
-// slot's inboxes do not depend on the vector's length, so calls of different sizes may follow one another directly.
-// Everything is device-side (no host-provided sequence numbers), so a captured call can be replayed.
-// The wait is bounded: a rank that never arrives makes the others record STATUS_WAIT_PEER_TIMEOUT in the device status
-// word and return without writing `out`; nothing traps, nothing spins forever.
+// caller provides the mappings; the Python side gets them from torch's symmetric memory). The exchange PUSHES, and the
+// data carries its own arrival mark: a call (same sizes on every rank) has the number e = finished calls + 1, and a
+// thread owns 8-byte pieces of the vector. For each of its pieces it
+//   1. stores the piece, stamped with e, into inbox[e & 1][my rank] of EVERY rank's buffer (one 16-byte peer store per
+//      rank: {4 bytes, e, 4 bytes, e}; the own buffer included);
+//   2. polls the same cell of the `world` inboxes of the LOCAL buffer until it carries e, adds the pieces in rank order
+//      in f32 and stores the sum to `out`: every rank computes the same sum in the same order - identical bits.
+// One NVLink crossing lies on the critical path; there is no flag, no fence and nothing is read remotely. The two
+// halves make a second barrier unnecessary: a rank writes half e & 1 of a peer's inbox again only in its call e + 2,
+// which it enters after its call e + 1 has received that peer's pieces of call e + 1, sent after the peer finished
+// call e. The call number lives in the local buffer and is advanced by the last block of a call to finish, so a
+// captured call can be replayed. The wait is bounded: a rank that never arrives makes the others record
+// STATUS_WAIT_PEER_TIMEOUT in the device status word and return without writing those pieces of `out`; nothing traps,
+// nothing spins forever.
 #include "common.cuh"
 #include "peer_allreduce.cuh"
 #include "runtime.h"
@@ -35,35 +33,23 @@ struct PeerAllReduceParams {
     unsigned int* status;
 };
 
-// `in`, `out` 16-byte aligned, n a multiple of Vec16<T>::N (the host checks); gridDim.x = ceil(bytes / slot_cap)
+// `in`, `out` 8-byte aligned, the vector a whole number of 8-byte pieces (the host checks)
 template <typename T>
 __global__ void __launch_bounds__(PAR_THREADS) peer_allreduce_kernel(const PeerAllReduceParams p) {
-    __shared__ unsigned int scratch[2];
-    const int slot = blockIdx.x, tid = threadIdx.x;
-    const long long units = p.n / Vec16<T>::N;
-    const long long per_slot = par_slot_cap(p.px.capacity) / 16;
-    const long long u0 = (long long)slot * per_slot;
-    const long long nunits = (u0 + per_slot < units ? u0 + per_slot : units) - u0;
-    uint8_t* mine = p.px.bufs[p.px.rank];
-    if (tid == 0) {
-        unsigned int* epoch = reinterpret_cast<unsigned int*>(mine + PAR_EPOCH_OFFSET) + slot;
-        const unsigned int e1 = *epoch + 1u;
-        *epoch = e1;
-        scratch[1] = e1;
+    const unsigned int e = par_next_epoch(*reinterpret_cast<volatile unsigned int*>(par_header(p.px) + PAR_EPOCH_ALONE));
+    const long long pieces = p.n / Vec8<T>::N;
+    const uint2* src = reinterpret_cast<const uint2*>(p.in);
+    uint2* dst = reinterpret_cast<uint2*>(p.out);
+    const long long step = (long long)gridDim.x * PAR_THREADS;
+    const long long first = (long long)blockIdx.x * PAR_THREADS + threadIdx.x;
+    // (read past L1: another kernel's CTAs produced the vector)
+    for (long long i = first; i < pieces; i += step) peer_push_piece<T>(p.px, PAR_PATH_ALONE, e, i, __ldcg(src + i));
+    for (long long i = first; i < pieces; i += step) {
+        uint2 sum;
+        if (peer_sum_piece<T>(p.px, PAR_PATH_ALONE, e, i, sum, p.status)) dst[i] = sum;
     }
     __syncthreads();
-    const unsigned int e = scratch[1];
-    // 1. this rank's slice into its inbox on every rank (read past L1: other CTAs may have produced it)
-    const long long my_inbox = par_inbox_offset(p.px.capacity, slot, e & 1u, p.px.rank);
-    const uint4* src = reinterpret_cast<const uint4*>(p.in) + u0;
-    for (long long u = tid; u < nunits; u += PAR_THREADS) {
-        const uint4 v = __ldcg(src + u);
-        for (int r = 0; r < p.px.world; ++r) st_global_16(p.px.bufs[r] + my_inbox + (size_t)u * 16, v);
-    }
-    __threadfence_system();
-    // 2. + 3.
-    peer_signal_wait_reduce<T, false>(p.px, slot, e, par_inbox_offset(p.px.capacity, slot, e & 1u, 0), par_slot_cap(p.px.capacity),
-                                      reinterpret_cast<uint4*>(p.out) + u0, nunits, tid, PAR_THREADS, p.status, scratch);
+    if (threadIdx.x == 0) peer_finish_call(p.px, PAR_EPOCH_ALONE, PAR_COUNT_ALONE, e, gridDim.x);
 }
 
 long long peer_allreduce_buffer_bytes(long long capacity) { return par_buffer_bytes(capacity); }
@@ -93,11 +79,10 @@ int peer_allreduce(const void* const* bufs, int rank, int world, long long capac
     p.out = out;
     p.n = n;
     p.status = status_ptr();
-    // one block per slot the vector reaches, at most seven (slot 7 belongs to the fused launches): every rank derives
-    // the same count
-    const long long slot_cap = par_slot_cap(capacity);
-    long long blocks = (n * esize + slot_cap - 1) / slot_cap;
-    if (blocks > PAR_MAX_BLOCKS) return B200Q_ERR_TOO_LARGE;
+    // a thread per 8-byte piece, at most one block per SM (every rank derives the same grid from the same sizes)
+    const long long pieces = n * esize / 8;
+    long long blocks = (pieces + PAR_THREADS - 1) / PAR_THREADS;
+    if (blocks > runtime_info().sm_count) blocks = runtime_info().sm_count;
     if (elem == ELEM_F32) peer_allreduce_kernel<float><<<(unsigned)blocks, PAR_THREADS, 0, s>>>(p);
     else if (elem == ELEM_F16) peer_allreduce_kernel<__half><<<(unsigned)blocks, PAR_THREADS, 0, s>>>(p);
     else if (elem == ELEM_BF16) peer_allreduce_kernel<__nv_bfloat16><<<(unsigned)blocks, PAR_THREADS, 0, s>>>(p);

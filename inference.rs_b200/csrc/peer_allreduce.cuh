@@ -6,13 +6,14 @@
 namespace b200q {
 
 constexpr int PAR_MAX_WORLD = 8;
-constexpr int PAR_MAX_BLOCKS = 7;
 constexpr int PAR_HEADER_BYTES = 1024;
-constexpr int PAR_EPOCH_OFFSET = 768;
-constexpr int PAR_THREADS = 512;
-
-constexpr int PAR_COUNTER_OFFSET = 832;  // arrival counter of the CTAs of a fused matmul + all-reduce launch
-constexpr int PAR_FUSED_BLOCK = 7;       // flag / epoch slot of the fused path (stand-alone calls use slots 0..6)
+constexpr int PAR_THREADS = 256;
+// header words (u32, read and written by the owning rank only)
+constexpr int PAR_EPOCH_ALONE = 0;    // number of the last finished stand-alone call
+constexpr int PAR_COUNT_ALONE = 1;    // finished blocks of the running stand-alone call
+constexpr int PAR_EPOCH_FUSED = 2;    // number of the last finished matmul + all-reduce launch
+constexpr int PAR_COUNT_FUSED = 3;    // finished CTAs of the running one
+constexpr int PAR_PATH_ALONE = 0, PAR_PATH_FUSED = 1;
 
 // The ranks' exchange buffers as mapped in this process; world <= 1 means "no exchange".
 struct PeerExchange {
@@ -21,139 +22,109 @@ struct PeerExchange {
     int rank, world;
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-// peer data is read past the L1 cache: the same addresses carry new values every second call
-__device__ __forceinline__ uint4 ld_volatile_16(const void* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
-
-template <typename T> struct Vec16;  // 16 bytes of T <-> floats
-template <> struct Vec16<float> {
-    static constexpr int N = 4;
-    static __device__ __forceinline__ void add(const uint4& u, float (&a)[8]) {
-        a[0] += __uint_as_float(u.x); a[1] += __uint_as_float(u.y); a[2] += __uint_as_float(u.z); a[3] += __uint_as_float(u.w);
-    }
-    static __device__ __forceinline__ uint4 pack(const float (&a)[8]) {
-        return make_uint4(__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]), __float_as_uint(a[3]));
-    }
-};
-template <> struct Vec16<__half> {
-    static constexpr int N = 8;
-    static __device__ __forceinline__ void add(const uint4& u, float (&a)[8]) {
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-            a[2 * i] += f.x;
-            a[2 * i + 1] += f.y;
-        }
-    }
-    static __device__ __forceinline__ uint4 pack(const float (&a)[8]) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const __half2 h = __floats2half2_rn(a[2 * i], a[2 * i + 1]);
-            w[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        return make_uint4(w[0], w[1], w[2], w[3]);
-    }
-};
-template <> struct Vec16<__nv_bfloat16> {
-    static constexpr int N = 8;
-    static __device__ __forceinline__ void add(const uint4& u, float (&a)[8]) {
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
-            a[2 * i] += f.x;
-            a[2 * i + 1] += f.y;
-        }
-    }
-    static __device__ __forceinline__ uint4 pack(const float (&a)[8]) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
-            w[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        return make_uint4(w[0], w[1], w[2], w[3]);
-    }
-};
-
 // ---- buffer layout (every rank's buffer is the same; `capacity` = largest vector in bytes, a multiple of 16) ----
-//   [0, 512)      arrive[slot 0..7][source rank 0..15]  u32, written by the peers
-//   768           epoch[slot 0..7]                       u32, local
-//   832           arrival counter of the CTAs of a fused matmul + all-reduce launch
-//   [1024, ...)   inboxes: for stand-alone slot i < 7, half h, source rank r: slot_cap bytes at
-//                 1024 + ((i * 2 + h) * 8 + r) * slot_cap, slot_cap = ceil16(capacity / 7): slot i always carries bytes
-//                 [i * slot_cap, (i + 1) * slot_cap) of a vector, whatever the vector's length, so a slot's inboxes
-//                 only ever meet that slot's own earlier calls;
-//                 then the fused launches' inboxes (slot 7): capacity bytes at fused_base + (h * 8 + r) * capacity.
-__host__ __device__ inline long long par_slot_cap(long long capacity) { return ((capacity + PAR_MAX_BLOCKS - 1) / PAR_MAX_BLOCKS + 15) & ~15LL; }
-__host__ __device__ inline long long par_inbox_offset(long long capacity, int slot, unsigned int half, int src) {
-    return PAR_HEADER_BYTES + (((long long)slot * 2 + half) * PAR_MAX_WORLD + src) * par_slot_cap(capacity);
+//   [0, 16)       the four header words above
+//   [1024, ...)   inboxes: for path p (stand-alone calls, fused launches), half h, source rank r, 2 * capacity bytes at
+//                 1024 + ((p * 2 + h) * 8 + r) * 2 * capacity.
+// An inbox holds a vector as 16-byte cells {payload, call number, payload, call number}: every 8 bytes of the vector
+// travel with the number of the call they belong to, in ONE store, so a reader that finds both numbers equal to its own
+// call's has the data - no flag to raise afterwards, no fence between data and flag, one NVLink crossing in all. (The
+// pairing of a payload word with the number next to it is what the exchange relies on, as NCCL's low-latency protocol
+// does.) Call numbers start at 1 on a zeroed buffer and skip 0 when they wrap.
+__host__ __device__ inline long long par_inbox_offset(long long capacity, int path, unsigned int half, int src) {
+    return PAR_HEADER_BYTES + (((long long)path * 2 + half) * PAR_MAX_WORLD + src) * 2 * capacity;
 }
-__host__ __device__ inline long long par_fused_base(long long capacity) {
-    return PAR_HEADER_BYTES + (long long)PAR_MAX_BLOCKS * 2 * PAR_MAX_WORLD * par_slot_cap(capacity);
-}
-__host__ __device__ inline long long par_fused_inbox_offset(long long capacity, unsigned int half, int src) {
-    return par_fused_base(capacity) + ((long long)half * PAR_MAX_WORLD + src) * capacity;
-}
-__host__ __device__ inline long long par_buffer_bytes(long long capacity) { return par_fused_base(capacity) + 2LL * PAR_MAX_WORLD * capacity; }
+__host__ __device__ inline long long par_buffer_bytes(long long capacity) { return PAR_HEADER_BYTES + 4LL * PAR_MAX_WORLD * 2 * capacity; }
 
-__device__ __forceinline__ void st_global_16(void* p, const uint4& v) {
-    asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+__device__ __forceinline__ unsigned int par_next_epoch(unsigned int finished) {
+    unsigned int e = finished + 1u;
+    return e == 0u ? 2u : e;  // 0 is what a fresh buffer holds; skipping two numbers keeps the halves alternating
+}
+__device__ __forceinline__ unsigned int* par_header(const PeerExchange& px) { return reinterpret_cast<unsigned int*>(px.bufs[px.rank]); }
+
+// cell `i` of an inbox <- 8 bytes of the vector, stamped with call number e
+__device__ __forceinline__ void ll_store(uint8_t* inbox, long long i, uint2 v, unsigned int e) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(inbox + i * 16), "r"(v.x), "r"(e), "r"(v.y), "r"(e) : "memory");
+}
+// cell `i` of a local inbox, once it carries call number e; false after WAIT_SPINS polls without it
+__device__ __forceinline__ bool ll_load(const uint8_t* inbox, long long i, unsigned int e, uint2& v) {
+    for (unsigned int spin = 0; spin < WAIT_SPINS; ++spin) {
+        uint4 c;
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(c.x), "=r"(c.y), "=r"(c.z), "=r"(c.w) : "l"(inbox + i * 16) : "memory");
+        if (c.y == e && c.w == e) {
+            v = make_uint2(c.x, c.z);
+            return true;
+        }
+        if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
+    }
+    return false;
 }
 
-// Second half of an exchange, by `nthreads` threads of one CTA (tid < nthreads; all of them must call): every rank's
-// contribution to units [0, nunits) of this slot has been pushed into the peers' inboxes (at `inbox0` + source rank *
-// `inbox_stride` of the epoch's half) and fenced at system scope by the threads that wrote it. Raises this rank's flag
-// in every peer, waits - bounded - for every peer's flag, then adds the `world` inboxes of the LOCAL buffer in rank
-// order in f32 and stores units of `out`. NAMED: the threads are a subset of the CTA that meets on named barrier 1.
-// `scratch` = one word of shared memory. Returns false (on all threads) if a peer did not arrive in time.
-template <typename T, bool NAMED>
-__device__ __forceinline__ bool peer_signal_wait_reduce(const PeerExchange& px, int slot, unsigned int e, long long inbox0,
-                                                        long long inbox_stride, void* out, long long nunits, int tid, int nthreads,
-                                                        unsigned int* status, volatile unsigned int* scratch) {
-    using V = Vec16<T>;
-    uint8_t* mine = px.bufs[px.rank];
-    if (tid == 0) scratch[0] = 1u;
-    if (NAMED) named_bar_sync(1, nthreads); else __syncthreads();
-    if (tid < px.world) {
-        st_release_sys(reinterpret_cast<unsigned int*>(px.bufs[tid]) + slot * 16 + px.rank, e);
-        const unsigned int* flag = reinterpret_cast<const unsigned int*>(mine) + slot * 16 + tid;
-        bool ok = false;
-        for (unsigned int spin = 0; spin < WAIT_SPINS; ++spin) {
-            if ((int)(ld_acquire_sys(flag) - e) >= 0) {
-                ok = true;
-                break;
-            }
-            if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
-        }
-        if (!ok) {
-            scratch[0] = 0u;
-            record_failure(status, STATUS_WAIT_PEER_TIMEOUT, (unsigned int)(slot * 16 + tid));
-        }
+// 8 bytes of T <-> floats
+template <typename T> struct Vec8;
+template <> struct Vec8<float> {
+    static constexpr int N = 2;
+    static __device__ __forceinline__ void add(const uint2& u, float (&a)[4]) { a[0] += __uint_as_float(u.x); a[1] += __uint_as_float(u.y); }
+    static __device__ __forceinline__ uint2 pack(const float (&a)[4]) { return make_uint2(__float_as_uint(a[0]), __float_as_uint(a[1])); }
+};
+template <> struct Vec8<__half> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void add(const uint2& u, float (&a)[4]) {
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&u.x)), hi = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+        a[0] += lo.x; a[1] += lo.y; a[2] += hi.x; a[3] += hi.y;
     }
-    if (NAMED) named_bar_sync(1, nthreads); else __syncthreads();
-    if (scratch[0] == 0u) return false;
-    // the same sum in the same order on every rank, from local memory
-    uint4* o = reinterpret_cast<uint4*>(out);
-    for (long long u = tid; u < nunits; u += nthreads) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < px.world; ++r) V::add(ld_volatile_16(mine + inbox0 + r * inbox_stride + (size_t)u * 16), acc);
-        o[u] = V::pack(acc);
+    static __device__ __forceinline__ uint2 pack(const float (&a)[4]) {
+        const __half2 lo = __floats2half2_rn(a[0], a[1]), hi = __floats2half2_rn(a[2], a[3]);
+        return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     }
+};
+template <> struct Vec8<__nv_bfloat16> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void add(const uint2& u, float (&a)[4]) {
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        a[0] += lo.x; a[1] += lo.y; a[2] += hi.x; a[3] += hi.y;
+    }
+    static __device__ __forceinline__ uint2 pack(const float (&a)[4]) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(a[0], a[1]), hi = __floats2bfloat162_rn(a[2], a[3]);
+        return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
+};
+
+// One 8-byte piece of the vector (piece index i): pushes this rank's value into its inbox on EVERY rank (the own buffer
+// included), then waits - bounded - for the piece from every rank in the local inboxes and returns their sum, added in
+// rank order in f32: every rank computes the same sum in the same order, so all ranks hold identical bits.
+// Returns false when a peer's piece did not come in time (STATUS_WAIT_PEER_TIMEOUT is recorded; `sum` is not valid).
+template <typename T>
+__device__ __forceinline__ void peer_push_piece(const PeerExchange& px, int path, unsigned int e, long long i, uint2 mine) {
+    const long long off = par_inbox_offset(px.capacity, path, e & 1u, px.rank);
+    for (int r = 0; r < px.world; ++r) ll_store(px.bufs[r] + off, i, mine, e);
+}
+template <typename T>
+__device__ __forceinline__ bool peer_sum_piece(const PeerExchange& px, int path, unsigned int e, long long i, uint2& sum, unsigned int* status) {
+    const uint8_t* base = px.bufs[px.rank];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < px.world; ++r) {
+        uint2 v;
+        if (!ll_load(base + par_inbox_offset(px.capacity, path, e & 1u, r), i, e, v)) {
+            record_failure(status, STATUS_WAIT_PEER_TIMEOUT, (unsigned int)r);
+            return false;
+        }
+        Vec8<T>::add(v, acc);
+    }
+    sum = Vec8<T>::pack(acc);
     return true;
+}
+
+// The last block / CTA of a call to finish (local arrival counter) publishes the call number: every block has read the
+// previous one by then. Called by one thread per block after the block's pieces are done.
+__device__ __forceinline__ void peer_finish_call(const PeerExchange& px, int epoch_word, int count_word, unsigned int e, unsigned int nblocks) {
+    unsigned int* hdr = par_header(px);
+    const unsigned int before = atomicAdd(hdr + count_word, 1u);
+    if (before == nblocks - 1u) {
+        hdr[count_word] = 0u;
+        *reinterpret_cast<volatile unsigned int*>(hdr + epoch_word) = e;
+    }
 }
 
 }  // namespace b200q
