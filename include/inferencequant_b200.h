@@ -227,7 +227,8 @@ int b200q_reset_device_status(void);
 /* First non-zero status a void launcher of part 1 produced since the last call, then cleared. */
 int b200q_take_launch_status(void);
 
-/* Diagnostics. `dev` is device memory for records * 32 uint64; every following GEMV launch takes the next record
+/* Diagnostics, in libraries built with -DB200Q_GEMV_TRACE=1 (B200Q_ERR_UNSUPPORTED otherwise: the timestamp sites are
+ * left out of the kernels by default). `dev` is device memory for records * 32 uint64; every following GEMV launch takes the next record
  * (wrapping) and its first / last CTA write %globaltimer nanoseconds into slots [0..15] / [16..31]: 0 start,
  * 1 barriers ready, 2 activations staged, 3 first stage landed, 4 done, 5 first weight copy issued, 6 activations
  * quantized, 7 activations in registers, 8 barriers initialised, 9 initial copies issued, 10 activation loads back,

@@ -25,6 +25,9 @@ NVCC_FLAGS = [
 ]
 
 
+# diagnostics builds: B200Q_BUILD_DEFINES="-DB200Q_GEMV_TRACE=1" adds the decode GEMV's timestamp sites (part of the digest)
+NVCC_FLAGS += os.environ.get("B200Q_BUILD_DEFINES", "").split()
+
 # per-file additions: the weight quantizers repeat the reference's scale searches operation for operation, which rules out
 # contracting a multiply and an add into one fused operation
 EXTRA_FLAGS = {"quantize_weights.cu": ["-fmad=false"]}

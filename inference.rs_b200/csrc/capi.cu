@@ -7,6 +7,10 @@
 #include "peer_allreduce.cuh"
 #include "runtime.h"
 
+#ifndef B200Q_GEMV_TRACE
+#define B200Q_GEMV_TRACE 0
+#endif
+
 namespace b200q {
 int gemv_q4_k(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
 int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
@@ -109,8 +113,13 @@ int b200q_reset_device_status(void) {
 // Diagnostics: `dev` points at records * 32 u64; every following GEMV launch takes the next record and its first / last CTA
 // write nanosecond timestamps into slots [0..15] / [16..31] (slot meanings: include/inferencequant_b200.h). records = 0: off.
 int b200q_set_trace_buffer(void* dev, int records) {
+#if B200Q_GEMV_TRACE
     set_trace_buffer(static_cast<unsigned long long*>(dev), dev ? records : 0);
     return B200Q_OK;
+#else
+    if (dev != nullptr && records > 0) return set_error(B200Q_ERR_UNSUPPORTED, "this library was built without -DB200Q_GEMV_TRACE=1");
+    return B200Q_OK;
+#endif
 }
 
 // First non-zero status a void launcher produced since the last call (then cleared).

@@ -104,6 +104,12 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+// Launch timelines are a build option (-DB200Q_GEMV_TRACE=1): fifteen timestamp sites are a few hundred instructions in
+// every kernel, and the decode chain is sensitive to the size of its kernels' code.
+#ifndef B200Q_GEMV_TRACE
+#define B200Q_GEMV_TRACE 0
+#endif
+#if B200Q_GEMV_TRACE
 #define GEMV_TRACE_ANY(slot)                                                                               \
     do {                                                                                                   \
         if (p.trace != nullptr && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))                        \
@@ -114,6 +120,10 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
         if (p.trace != nullptr && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))            \
             p.trace[(blockIdx.x == 0 ? 0 : 16) + (slot)] = global_timer_ns();                               \
     } while (0)
+#else
+#define GEMV_TRACE_ANY(slot) do { } while (0)
+#define GEMV_TRACE(slot) do { } while (0)
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // Activation staging (generic stores into shared memory; read back with explicit shared loads)
@@ -296,6 +306,8 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
     constexpr unsigned gmask = 0xffffffffu;
     const int total = B * chunks;
     int u = 0;  // which of this thread's chunks
+    // (One chunk after the other: processing the chunks loaded ahead side by side shortens a single launch by 3-5 % and
+    // makes the kernel's code larger; in the decode chain, where three kernels alternate, that cost 10 %.)
     for (int i = tid; i - lane < total; i += nthreads, ++u) {
         const bool valid = i < total;
         // integer divisions are dozens of dependent instructions on a path every launch runs exactly once
@@ -353,8 +365,9 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
                 for (int j = 0; j < 8; ++j) q[j] = (int)roundf(v[j] * id);
             } else {
                 // roundf(x / d) without eight IEEE divisions: one exact reciprocal, a residual-corrected quotient
-                // (accurate to a couple of ulp), and the exact division only where that quotient lies within 1e-3
-                // of a rounding boundary, so the result is always the one the quantize launcher computes
+                // (within an ulp of the true one: under 4e-6 for |q| < 128), and the exact division only where that
+                // quotient lies within 1e-4 of a rounding boundary (one value in 5000), so the result is always the one
+                // the quantize launcher computes
                 // (the reciprocal only seeds the quotient, so the approximate one does; |q| <= 127.5, so the magic-number
                 // rounding applies)
                 const float rcp = amax == 0.0f ? 0.0f : __frcp_rn(d);
@@ -365,7 +378,7 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
                     const float q1 = fmaf(fmaf(-d, q0, v[j]), rcp, q0);
                     const float qr = (q1 + 12582912.0f) - 12582912.0f;  // nearest integer
                     q[j] = amax == 0.0f ? 0 : (int)qr;
-                    near_half |= (fabsf(q1 - qr) > 0.499f) ? (1u << j) : 0u;
+                    near_half |= (fabsf(q1 - qr) > 0.4999f) ? (1u << j) : 0u;
                 }
                 if (near_half != 0u && amax != 0.0f) {  // rare: decided by the division itself, out of line
 #pragma unroll
@@ -705,11 +718,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         grid_dependency_wait();  // the previous grid has finished and its stores are visible
         pre.issue(p.act, B, p.K, p.stride_act, p.act_vec != 0, tid);
     }
+#if B200Q_GEMV_TRACE
     if (p.trace != nullptr && tid == 0) {  // when this thread's first activation load has come back
         if constexpr (ACT == ACT_Q8_1) asm volatile("" ::"r"(pre.v[0]));
         else asm volatile("" ::"r"(pre.raw[0][0]));
         GEMV_TRACE(10);
     }
+#endif
     if constexpr (ACT == ACT_Q8_1)
         stage_acts_q8_1<B>(acts, reinterpret_cast<const uint8_t*>(p.act), p.K, p.stride_act, tid, GEMV_CONSUMER_THREADS, pre);
     else

@@ -243,8 +243,8 @@ def _peer_rank(rank, world, port, ret):
             gathered = [torch.empty_like(got) for _ in range(world)]
             dist.all_gather(gathered, got)
             same = same and all(torch.equal(gathered[0], t) for t in gathered)  # identical bits on every rank
-        # calls of different sizes straight after one another, nothing in between that would line the ranks up again: a
-        # slot's inboxes do not depend on the vector's length, so no call may touch what a slower peer is still reading
+        # calls of different sizes straight after one another, nothing in between that would line the ranks up again: no
+        # call may touch what a slower peer is still reading, whatever the lengths of the vectors before it
         shapes = [((1, 8192), torch.bfloat16), ((16, 2048), torch.float16), ((3, 1000), torch.float32), ((1, 8), torch.bfloat16),
                   ((2, 4096), torch.bfloat16), ((1, 24), torch.float32), ((16, 2048), torch.bfloat16)] * 4
         ins, outs = [], []
