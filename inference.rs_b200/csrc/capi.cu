@@ -61,6 +61,8 @@ int b200q_set_option(const char* name, int value) {
     } else if (!std::strcmp(name, "l2_prefetch_bytes")) {
         if (value < 0) return set_error(B200Q_ERR_INVALID, "l2_prefetch_bytes must be >= 0");
         rt.l2_prefetch_bytes = value & ~15;
+    } else if (!std::strcmp(name, "gemv_one_kernel")) {
+        rt.gemv_one_kernel = value ? 1 : 0;
     } else if (!std::strcmp(name, "gemv_passes")) {
         if (value < 0 || value > 2) return set_error(B200Q_ERR_INVALID, "gemv_passes is 0 (planner's choice), 1 or 2");
         rt.gemv_passes = value;
@@ -82,6 +84,7 @@ int b200q_get_option(const char* name, int* value) {
     else if (!std::strcmp(name, "force_simple_gemv")) *value = rt.force_simple;
     else if (!std::strcmp(name, "gemv_stage_bytes")) *value = rt.gemv_stage_target;
     else if (!std::strcmp(name, "gemv_ctas_per_sm")) *value = rt.gemv_ctas_per_sm;
+    else if (!std::strcmp(name, "gemv_one_kernel")) *value = rt.gemv_one_kernel;
     else if (!std::strcmp(name, "gemv_passes")) *value = rt.gemv_passes;
     else if (!std::strcmp(name, "gemv_pass_limit_bytes")) *value = rt.gemv_pass_limit;
     else if (!std::strcmp(name, "gemm_direct")) *value = rt.gemm_direct;

@@ -77,8 +77,6 @@ struct GemvParams {
     int stride_dst;
     int row_bytes;
     int rows_per_stage;  // R: rows one stage holds (multiple of row_align and of the number of row groups)
-    int first_rows;      // rows of the CTA's very first stage (<= R): a smaller one lands sooner, and nothing can be
-                         // computed before it has
     int warps_per_row;   // WPR: power of two <= 16; 16 / WPR row groups work on different rows at once
     int log2_wpr;        // shifts instead of divisions in the kernel: WPR = 1 << log2_wpr,
     int log2_islots;     // islots (lanes that share a row inside a warp: items rounded up to a power of two, <= 32)
@@ -478,12 +476,15 @@ __device__ __forceinline__ float dot(const Weights<TYPE_Q4_K>& W, const ActPair&
             dh0 = dp4a_us(W.w[8 * cc + j] & 0xf0f0f0f0u, A.q[16 * cc + 8 + j], dh0);       // 16 * high nibble
             dh1 = dp4a_us(W.w[8 * cc + 4 + j] & 0xf0f0f0f0u, A.q[16 * cc + 12 + j], dh1);
         }
-        const int sc_lo = (int)((W.sc4 >> (16 * cc)) & 0xffu), sc_hi = (int)((W.sc4 >> (16 * cc + 8)) & 0xffu);
-        const int m_lo = (int)((W.m4 >> (16 * cc)) & 0xffu), m_hi = (int)((W.m4 >> (16 * cc + 8)) & 0xffu);
+        // one byte of the packed scales / mins each (a byte permute: one instruction instead of shift + mask)
+        const int sc_lo = (int)__byte_perm(W.sc4, 0u, 0x4440u + 2 * cc), sc_hi = (int)__byte_perm(W.sc4, 0u, 0x4441u + 2 * cc);
+        // a min (<= 63) as a float: its byte dropped into the low byte of 2^23 + 2^22 (exact), minus that constant
+        const float m_lo = __uint_as_float(__byte_perm(W.m4, 0x4B400000u, 0x7650u + 2 * cc)) - 12582912.0f;
+        const float m_hi = __uint_as_float(__byte_perm(W.m4, 0x4B400000u, 0x7651u + 2 * cc)) - 12582912.0f;
         // integer scale folding: |sc * dot| <= 63 * 32 * 15 * 127 < 2^22
         accd += A.d[2 * cc] * int_to_float_small(sc_lo * (dl0 + dl1));
         accd += A.d[2 * cc + 1] * int_to_float_small(sc_hi * ((dh0 + dh1) >> 4));
-        accm += int_to_float_small(m_lo) * A.ds[2 * cc] + int_to_float_small(m_hi) * A.ds[2 * cc + 1];
+        accm += m_lo * A.ds[2 * cc] + m_hi * A.ds[2 * cc + 1];
     }
     return W.d * accd - W.dmin * accm;
 }
@@ -668,7 +669,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         GEMV_TRACE_ANY(5);
         int r = row0;
         for (; r < row1 && issued < S; ++issued) {
-            const int rows = min(issued == 0 ? p.first_rows : R, row1 - r);
+            const int rows = min(R, row1 - r);
             const uint32_t bytes = ((uint32_t)rows * (uint32_t)p.row_bytes + 15u) & ~15u;
             mbar_arrive_expect_tx(&full[issued], bytes);
             bulk_copy_g2s(ring + (size_t)issued * p.stage_bytes, p.w + (size_t)r * p.row_bytes, bytes, &full[issued]);
@@ -780,9 +781,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
     int rot = 0;
     int rot_step = R;  // R mod rows_per_pass (R is at most a few passes)
     while (rot_step >= rows_per_pass) rot_step -= rows_per_pass;
-    int first_rot_step = p.first_rows;
-    while (first_rot_step >= rows_per_pass) first_rot_step -= rows_per_pass;
-    for (int it = 0, rbase = row0; rbase < row1; rbase += (it == 0 ? p.first_rows : R), ++it) {
+    for (int it = 0, rbase = row0; rbase < row1; rbase += R, ++it) {
         if (alive && !mbar_wait_bounded(&full[s], ph)) {
             record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, it);
             alive = false;  // keep arriving so that the others are not held up, but compute nothing
@@ -790,7 +789,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         if (it == 0) GEMV_TRACE(3);
         else if (it <= 2) GEMV_TRACE(10 + 2 * it);  // 12, 14: stages 1 and 2 landed
         const uint32_t st = ring_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
-        const int rows_here = min(it == 0 ? p.first_rows : R, row1 - rbase);
+        const int rows_here = min(R, row1 - rbase);
         // rows of consecutive stages go to consecutive warp groups, so a stage may hold fewer rows than one pass of
         // all warps without leaving the same warps idle every time
         const int my_slot = row_slot >= rot ? row_slot - rot : row_slot - rot + rows_per_pass;
@@ -929,7 +928,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
             s = 0;
             ph ^= 1u;
         }
-        rot += it == 0 ? first_rot_step : rot_step;
+        rot += rot_step;
         if (rot >= rows_per_pass) rot -= rows_per_pass;
     }
     if constexpr (AR) {
@@ -983,7 +982,6 @@ struct GemvGroupParams {
     int K;
     int warps_per_row, items_per_lane, log2_wpr, log2_islots;
     int nstages, stage_bytes, act_bytes, max_rows_per_stage;
-    int first_rows[GEMV_GROUP_MAX];  // rows of the first stage of each matrix; < rows_per_stage only for the first matrix
     int use_pdl, act_vec;
     unsigned int* status;
     NextPrefetch next;
@@ -1031,12 +1029,20 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
                     acc[u] += (alive && has_row[u] && item_ok) ? d : 0.0f;
                 }
             }
+            if (islots == 32) {  // a whole warp per row (every K from 4096 up): no per-level test
 #pragma unroll
-            for (int m = 16; m > 0; m >>= 1)
-                if (m < islots) {
+                for (int m = 16; m > 0; m >>= 1) {
 #pragma unroll
                     for (int u = 0; u < U; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
                 }
+            } else {
+#pragma unroll
+                for (int m = 8; m > 0; m >>= 1)
+                    if (m < islots) {
+#pragma unroll
+                        for (int u = 0; u < U; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
+                    }
+            }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (lane_i == 0 && has_row[u]) {
@@ -1145,12 +1151,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
                 int row0, row1;
                 group_rows(p, m, cta, row0, row1);
                 const int R = p.rows_per_stage[m];
-                for (int r = row0; r < row1 && ok; r += (r == row0 ? p.first_rows[m] : R), ++g) {
+                for (int r = row0; r < row1 && ok; r += R, ++g) {
                     if (g >= S) {
                         ok = mbar_wait_bounded(&empty[s], ph);
                         if (!ok) { record_failure(p.status, STATUS_WAIT_EMPTY_TIMEOUT, g); break; }
                     }
-                    const int rows = min(r == row0 ? p.first_rows[m] : R, row1 - r);
+                    const int rows = min(R, row1 - r);
                     const uint32_t bytes = ((uint32_t)rows * (uint32_t)p.row_bytes[m] + 15u) & ~15u;
                     mbar_arrive_expect_tx(&full[s], bytes);
                     bulk_copy_g2s(ring + (size_t)s * p.stage_bytes, p.w[m] + (size_t)r * p.row_bytes[m], bytes, &full[s]);
@@ -1216,16 +1222,16 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
         const int R = p.rows_per_stage[m];
         const int mtype = p.type[m];
         dst_t* dst = reinterpret_cast<dst_t*>(p.dst[m]);
-        for (int r = row0; r < row1; r += (r == row0 ? p.first_rows[m] : R), ++g) {
+        for (int r = row0; r < row1; r += R, ++g) {
             if (alive && !mbar_wait_bounded(&full[s], ph)) {
                 record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, g);
                 alive = false;
             }
             const uint32_t st = ring_addr + (uint32_t)s * (uint32_t)p.stage_bytes;
-            const int rows_here = min(r == row0 ? p.first_rows[m] : R, row1 - r);
-            const int my_slot = row_slot >= rot ? row_slot - rot : row_slot - rot + rows_per_pass;
-            rot += rows_here;
-            while (rot >= rows_per_pass) rot -= rows_per_pass;
+            const int rows_here = min(R, row1 - r);
+            // (rows_per_pass is a power of two: both the warp groups and the rows per warp are)
+            const int my_slot = (row_slot - rot) & (rows_per_pass - 1);
+            rot = (rot + rows_here) & (rows_per_pass - 1);
             float* part_base = partial + (size_t)s * RMAX * WPR;
             int* cnt_base = counters + s * RMAX;
             if (mtype == TYPE_Q4_K)
@@ -1398,8 +1404,7 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w, i
     // with one register-resident slot a warp keeps two rows of a stage in flight (rows r and r + rows_per_pass), so a
     // stage holds two passes
     const int passes = plan.nreg == 1 ? (rt.gemv_passes == 1 ? 1 : 2) : 1;
-    const int unit0 = rows_per_pass * p.row_align / gcd_int(rows_per_pass, p.row_align);
-    const int unit = unit0 * passes;
+    const int unit = rows_per_pass * p.row_align / gcd_int(rows_per_pass, p.row_align) * passes;
     int R = passes * rt.gemv_stage_target / (unit * p.row_bytes) * unit;
     if (R < unit) R = unit;
     p.rows_per_stage = R;
@@ -1429,10 +1434,6 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w, i
     if (S < 2) return plan;  // does not fit: simple kernel
     p.nstages = S;
     R = p.rows_per_stage;
-    // (a smaller first stage lands sooner, but a stage of one pass gives every warp a single row, and a warp needs two
-    // rows in flight to hide its latencies: measured slower on every decode shape, so all stages are equal)
-    p.first_rows = R;
-    (void)unit0;
     p.ar_offset = (int)plan.smem;
     plan.smem += ar_bytes;
     plan.grid = (int)grid;
@@ -1507,10 +1508,23 @@ static inline int launch_staged(const GemvPlan& plan, cudaStream_t s) {
     return launch_staged_n<TYPE, B, dst_t, ACT, act_t, 0>(plan, s);
 }
 
+// (defined once, in gemv_group.cu: every caller must reach the SAME copy of the grouped kernel)
+int gemv_group(int elem, int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, const void* x,
+               cudaStream_t s);
+
 template <int TYPE, int B, typename dst_t>
 static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int K, int N, int stride_act, int stride_dst,
                                 int act_mode, const PeerExchange* px, cudaStream_t s) {
     const bool exchange = px != nullptr && px->world > 1;
+    if (B == 1 && act_mode == ACT_RAW_Q8_1 && !exchange && runtime_info().gemv_one_kernel) {
+        // One row of raw activations: the grouped kernel with a single matrix - the same arithmetic in the same order, a
+        // little more bookkeeping per row, but a decode chain then alternates between fewer kernels, and its launches
+        // are sensitive to how much code they have to fetch (+2 % on the chain).
+        const int type = TYPE;
+        constexpr int elem = sizeof(dst_t) == 4 ? ELEM_F32 : (std::is_same<dst_t, __half>::value ? ELEM_F16 : ELEM_BF16);
+        const int rc = gemv_group(elem, 1, &type, &vx, &dst, &N, K, act, s);
+        if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+    }
     constexpr int PIECE = 8 / (int)sizeof(dst_t);  // output rows per 8-byte piece of the exchange
     if (exchange) {
         // fused all-reduce: contiguous [B][N] output, rows of whole 8-byte pieces, within the capacity; staged kernel only
@@ -1590,7 +1604,6 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
         p.type[m] = types[m];
         p.row_bytes[m] = one.p.row_bytes;
         p.rows_per_stage[m] = one.p.rows_per_stage;
-        p.first_rows[m] = m == 0 ? one.p.first_rows : one.p.rows_per_stage;
         p.row_align[m] = one.p.row_align;
         if (one.p.stage_bytes > max_stage) max_stage = one.p.stage_bytes;
         if (one.p.rows_per_stage > max_R) max_R = one.p.rows_per_stage;

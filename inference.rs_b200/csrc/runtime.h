@@ -23,6 +23,8 @@ struct RuntimeInfo {
     int gemm_direct;       // 1: the GEMM reads packed weights straight from global memory (no shared-memory staging)
     int gemv_ctas_per_sm;  // CTAs of one GEMV grid per SM: 2, or 1 to leave the other slot to the next grid
     int tc_ksplit;         // small-batch tensor-core kernel: split K over CTAs for matrices with few rows (1, testing: 0)
+    int gemv_one_kernel;   // one-row GEMVs on raw activations run on the grouped kernel, so that a decode chain alternates
+                           // between fewer kernels (1; 0 = the per-type kernels)
     int gemv_passes;       // decode GEMV planner: passes of all warps a stage holds (0 = the planner's own choice; 1 or 2)
     int gemv_pass_limit;   // decode GEMV planner: bytes one pass of all warps may cover before rows get more warps
     int l2_prefetch_bytes; // decode GEMV: bytes of the registered successor matrix each CTA asks L2 to fetch (0 = off)
