@@ -17,7 +17,7 @@ int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int
 int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
 void gemv_describe(int type, int K, int N, int b, int* out);
 int gemv_group(int elem, int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, const void* x,
-               cudaStream_t s);
+               cudaStream_t s, const PeerExchange* px);
 int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s);
 int gemv_tc_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace, cudaStream_t s);
 size_t gemv_tc_workspace_bytes(int type, int K);
@@ -178,7 +178,7 @@ int b200q_gemv_group(int nmat, const int* types, const void* const* ws, void* co
                      const void* x, void* stream) {
     if (!types || !ws || !dsts || !Ns || !x) return set_error(B200Q_ERR_INVALID, "null pointer");
     if (nmat < 1 || nmat > 4) return set_error(B200Q_ERR_INVALID, "b200q_gemv_group takes 1..4 matrices");
-    const int rc = gemv_group(elem, nmat, types, ws, dsts, Ns, K, x, (cudaStream_t)stream);
+    const int rc = gemv_group(elem, nmat, types, ws, dsts, Ns, K, x, (cudaStream_t)stream, nullptr);
     if (rc == B200Q_ERR_UNSUPPORTED)
         return set_error(rc, "group not supported (K must be a multiple of 128, weights 16-byte aligned): launch the matrices one by one");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "grouped gemv failed");

@@ -606,6 +606,33 @@ __device__ __forceinline__ float dot(const Weights<TYPE_Q8_0>& W, const ActPair&
     return part;
 }
 
+// Fused exchange, called by the consumer threads of a CTA whose rows [row0, row1) of the [B][N] output sit in shared
+// memory (`stage`, `stage_rows` entries per activation row): 8-byte pieces of the output (row0 and the row count are whole
+// pieces: the planner aligned the CTA's row range), each stamped with the call number and stored into this rank's inbox
+// on every rank, then summed from the local inboxes as the peers' CTAs deliver theirs, and written to `dst`. No fence,
+// no flag, no last CTA: one NVLink crossing after the slowest rank's CTA has finished its rows (peer_allreduce.cuh).
+template <typename dst_t, int B>
+__device__ __forceinline__ void exchange_cta_rows(const PeerExchange& px, const dst_t* stage, int stage_rows, int row0, int row1, int N,
+                                                  void* dst, unsigned int* status, int tid, unsigned int epoch) {
+    named_bar_sync(1, GEMV_CONSUMER_THREADS);  // the CTA's outputs are in shared memory
+    constexpr int PIECE = 8 / (int)sizeof(dst_t);
+    const int pieces_per_row = (row1 - row0) / PIECE;
+    const int total = B * pieces_per_row;
+    for (int i = tid; i < total; i += GEMV_CONSUMER_THREADS) {
+        const int b = B == 1 ? 0 : i / pieces_per_row, pr = i - b * pieces_per_row;
+        const uint2 mine = *reinterpret_cast<const uint2*>(stage + b * stage_rows + pr * PIECE);
+        peer_push_piece<dst_t>(px, PAR_PATH_FUSED, epoch, ((long long)b * N + row0) / PIECE + pr, mine);
+    }
+    for (int i = tid; i < total; i += GEMV_CONSUMER_THREADS) {
+        const int b = B == 1 ? 0 : i / pieces_per_row, pr = i - b * pieces_per_row;
+        const long long piece = ((long long)b * N + row0) / PIECE + pr;
+        uint2 sum;
+        if (peer_sum_piece<dst_t>(px, PAR_PATH_FUSED, epoch, piece, sum, status)) reinterpret_cast<uint2*>(dst)[piece] = sum;
+    }
+    named_bar_sync(1, GEMV_CONSUMER_THREADS);
+    if (tid == 0) peer_finish_call(px, PAR_EPOCH_FUSED, PAR_COUNT_FUSED, epoch, gridDim.x);
+}
+
 // ---------------------------------------------------------------------------------------------
 // The kernel. NREG = item slots per lane whose activations live in registers (0: read from shared memory each time).
 //
@@ -931,29 +958,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const Gemv
         rot += rot_step;
         if (rot >= rows_per_pass) rot -= rows_per_pass;
     }
-    if constexpr (AR) {
-        // Every CTA completes the exchange for its own rows: 8-byte pieces of the [B][N] output (row0 and the row count
-        // are whole pieces: the planner aligned the CTA's row range), each stamped with the call number and stored into
-        // this rank's inbox on every rank, then summed from the local inboxes as the peers' CTAs deliver theirs. No
-        // fence, no flag, no last CTA: one NVLink crossing after the slowest rank's CTA has finished its rows.
-        named_bar_sync(1, GEMV_CONSUMER_THREADS);  // the CTA's outputs are in shared memory
-        constexpr int PIECE = 8 / (int)sizeof(dst_t);
-        const int pieces_per_row = (row1 - row0) / PIECE;
-        const int total = B * pieces_per_row;
-        for (int i = tid; i < total; i += GEMV_CONSUMER_THREADS) {
-            const int b = B == 1 ? 0 : i / pieces_per_row, pr = i - b * pieces_per_row;
-            const uint2 mine = *reinterpret_cast<const uint2*>(ar_stage + b * p.ar_rows + pr * PIECE);
-            peer_push_piece<dst_t>(p.px, PAR_PATH_FUSED, ar_epoch, ((long long)b * p.N + row0) / PIECE + pr, mine);
-        }
-        for (int i = tid; i < total; i += GEMV_CONSUMER_THREADS) {
-            const int b = B == 1 ? 0 : i / pieces_per_row, pr = i - b * pieces_per_row;
-            const long long piece = ((long long)b * p.N + row0) / PIECE + pr;
-            uint2 sum;
-            if (peer_sum_piece<dst_t>(p.px, PAR_PATH_FUSED, ar_epoch, piece, sum, p.status)) reinterpret_cast<uint2*>(p.dst)[piece] = sum;
-        }
-        named_bar_sync(1, GEMV_CONSUMER_THREADS);
-        if (tid == 0) peer_finish_call(p.px, PAR_EPOCH_FUSED, PAR_COUNT_FUSED, ar_epoch, gridDim.x);
-    }
+    if constexpr (AR) exchange_cta_rows<dst_t, B>(p.px, ar_stage, p.ar_rows, row0, row1, p.N, p.dst, p.status, tid, ar_epoch);
     GEMV_TRACE(4);
 }
 
@@ -985,6 +990,8 @@ struct GemvGroupParams {
     int use_pdl, act_vec;
     unsigned int* status;
     NextPrefetch next;
+    PeerExchange px;  // px.world > 1 (one matrix only): the row-parallel matmul with the exchange fused in, as gemv_staged_kernel
+    int ar_rows, ar_offset;
 };
 
 // rows [row0, row1) of matrix m that CTA `cta` owns
@@ -1108,7 +1115,7 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
 
 // ACT: ACT_RAW_Q8_1 (raw row, quantized here to Q8_1 as the two-launch protocol does) or ACT_Q8_1 (blocks already
 // quantized by the caller: the reference's fused q/k/v launcher)
-template <typename dst_t, typename act_t, int NREG, int ACT = ACT_RAW_Q8_1>
+template <typename dst_t, typename act_t, int NREG, int ACT = ACT_RAW_Q8_1, bool AR = false>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvGroupParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -1211,6 +1218,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
             if (item0 + j * item_step < items) areg[j].load(acts_addr, item0 + j * item_step);
     }
 
+    // fused exchange (one matrix): the CTA's outputs go to shared memory first, then to every rank
+    unsigned int ar_epoch = 0;
+    dst_t* ar_stage = reinterpret_cast<dst_t*>(smem + p.ar_offset);
+    if constexpr (AR) ar_epoch = par_next_epoch(*reinterpret_cast<volatile unsigned int*>(par_header(p.px) + PAR_EPOCH_FUSED));
+
     bool alive = true;
     int g = 0;
     int s = 0;
@@ -1221,7 +1233,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
         group_rows(p, m, cta, row0, row1);
         const int R = p.rows_per_stage[m];
         const int mtype = p.type[m];
-        dst_t* dst = reinterpret_cast<dst_t*>(p.dst[m]);
+        dst_t* dst = AR ? ar_stage - row0 : reinterpret_cast<dst_t*>(p.dst[m]);
         for (int r = row0; r < row1; r += R, ++g) {
             if (alive && !mbar_wait_bounded(&full[s], ph)) {
                 record_failure(p.status, STATUS_WAIT_FULL_TIMEOUT, g);
@@ -1250,6 +1262,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
                 ph ^= 1u;
             }
         }
+    }
+    if constexpr (AR) {
+        int row0, row1;
+        group_rows(p, 0, cta, row0, row1);
+        exchange_cta_rows<dst_t, 1>(p.px, ar_stage, p.ar_rows, row0, row1, p.N[0], p.dst[0], p.status, tid, ar_epoch);
     }
 }
 
@@ -1510,20 +1527,22 @@ static inline int launch_staged(const GemvPlan& plan, cudaStream_t s) {
 
 // (defined once, in gemv_group.cu: every caller must reach the SAME copy of the grouped kernel)
 int gemv_group(int elem, int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, const void* x,
-               cudaStream_t s);
+               cudaStream_t s, const PeerExchange* px);
 
 template <int TYPE, int B, typename dst_t>
 static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int K, int N, int stride_act, int stride_dst,
                                 int act_mode, const PeerExchange* px, cudaStream_t s) {
     const bool exchange = px != nullptr && px->world > 1;
-    if (B == 1 && act_mode == ACT_RAW_Q8_1 && !exchange && runtime_info().gemv_one_kernel) {
+    if (B == 1 && act_mode == ACT_RAW_Q8_1 && runtime_info().gemv_one_kernel) {
         // One row of raw activations: the grouped kernel with a single matrix - the same arithmetic in the same order, a
         // little more bookkeeping per row, but a decode chain then alternates between fewer kernels, and its launches
         // are sensitive to how much code they have to fetch (+2 % on the chain).
         const int type = TYPE;
         constexpr int elem = sizeof(dst_t) == 4 ? ELEM_F32 : (std::is_same<dst_t, __half>::value ? ELEM_F16 : ELEM_BF16);
-        const int rc = gemv_group(elem, 1, &type, &vx, &dst, &N, K, act, s);
-        if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+        if (!exchange || stride_dst == N) {
+            const int rc = gemv_group(elem, 1, &type, &vx, &dst, &N, K, act, s, exchange ? px : nullptr);
+            if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+        }
     }
     constexpr int PIECE = 8 / (int)sizeof(dst_t);  // output rows per 8-byte piece of the exchange
     if (exchange) {
@@ -1578,9 +1597,15 @@ static inline int launch_gemv(const void* vx, const void* act, void* dst, int K,
 // the staged kernel's preconditions; the caller then launches the matrices one by one.
 template <typename dst_t, int ACT = ACT_RAW_Q8_1>
 static inline int launch_gemv_group(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K,
-                                    const void* x, cudaStream_t s) {
+                                    const void* x, cudaStream_t s, const PeerExchange* px = nullptr) {
     const RuntimeInfo& rt = runtime_info();
     if (nmat < 1 || nmat > GEMV_GROUP_MAX || K <= 0 || K % 128 != 0 || rt.force_simple) return B200Q_ERR_UNSUPPORTED;
+    // fused exchange: one matrix, rows of whole 8-byte pieces, within the capacity (as launch_gemv_b checks it)
+    const bool exchange = px != nullptr && px->world > 1;
+    constexpr int PIECE = 8 / (int)sizeof(dst_t);
+    if (exchange && (nmat != 1 || ACT != ACT_RAW_Q8_1 || Ns[0] % PIECE != 0 || (long long)Ns[0] * (long long)sizeof(dst_t) > px->capacity ||
+                     reinterpret_cast<uintptr_t>(dsts[0]) % 8 != 0))
+        return B200Q_ERR_UNSUPPORTED;
     GemvGroupParams p{};
     p.nmat = nmat;
     p.K = K;
@@ -1594,8 +1619,9 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
     for (int m = 0; m < nmat; ++m) {
         if (type_block_bytes(types[m]) == 0 || K % type_block_elems(types[m]) != 0) return B200Q_ERR_UNSUPPORTED;
         if (reinterpret_cast<uintptr_t>(ws[m]) % 16 != 0 || Ns[m] <= 0) return B200Q_ERR_UNSUPPORTED;
-        const GemvPlan one = plan_gemv(types[m], K, Ns[m], 1, ws[m]);
+        const GemvPlan one = plan_gemv(types[m], K, Ns[m], 1, ws[m], exchange ? PIECE : 1);
         if (!one.staged) return B200Q_ERR_UNSUPPORTED;
+        p.ar_rows = one.p.ar_rows;
         if (m == 0) { wpr = one.p.warps_per_row; ipl = one.p.items_per_lane; p.log2_wpr = one.p.log2_wpr; p.log2_islots = one.p.log2_islots; }
         if (one.p.warps_per_row != wpr || one.p.items_per_lane != ipl) return B200Q_ERR_UNSUPPORTED;  // same K: cannot differ
         p.w[m] = static_cast<const uint8_t*>(ws[m]);
@@ -1617,7 +1643,8 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
     p.items_per_lane = ipl;
     p.stage_bytes = max_stage;
     p.max_rows_per_stage = max_R;
-    const int budget = rt.smem_optin - 1024;
+    const int ar_bytes = exchange ? ((p.ar_rows * 4 + 127) & ~127) : 0;
+    const int budget = rt.smem_optin - 1024 - ar_bytes;
     int S = 0;
     size_t smem = 0;
     for (S = GEMV_MAX_STAGES; S >= 2; --S) {
@@ -1629,6 +1656,9 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
     }
     if (S < 2) return B200Q_ERR_UNSUPPORTED;
     p.nstages = S;
+    p.ar_offset = (int)smem;
+    smem += ar_bytes;
+    if (exchange) p.px = *px;
     const int nreg = ipl <= 2 ? ipl : 0;
     auto launch = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, rt.smem_optin - 1024);
@@ -1646,6 +1676,13 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
         return (int)cudaLaunchKernelEx(&cfg, kernel, p);
     };
     using act_t = typename std::conditional<ACT == ACT_Q8_1, float, dst_t>::type;
+    if constexpr (ACT == ACT_RAW_Q8_1) {
+        if (exchange) {
+            if (nreg == 1) return launch(gemv_group_kernel<dst_t, act_t, 1, ACT, true>);
+            if (nreg == 2) return launch(gemv_group_kernel<dst_t, act_t, 2, ACT, true>);
+            return launch(gemv_group_kernel<dst_t, act_t, 0, ACT, true>);
+        }
+    }
     if (nreg == 1) return launch(gemv_group_kernel<dst_t, act_t, 1, ACT>);
     if (nreg == 2) return launch(gemv_group_kernel<dst_t, act_t, 2, ACT>);
     return launch(gemv_group_kernel<dst_t, act_t, 0, ACT>);
