@@ -442,6 +442,45 @@ def time_chain(torch, stream, step, steps, warmup, use_graph=True):
         return e0.elapsed_time(e1) / steps
 
 
+def gguf_round_trip(torch, pkg, ops, chain):
+    """The benched weights as FILE bytes: the first layer's seven projections are written to a llama-shaped GGUF file
+    (tensor names and metadata as llama.cpp writes them), read back through the container reader and the llama name map,
+    uploaded, and multiplied: the outputs must equal, bit for bit, those of the buffers the chain runs on."""
+    import os
+    import tempfile
+
+    from inference_rs_b200 import llama_gguf
+    from inference_rs_b200.gguf_file import Content
+
+    model = chain.model
+    projs = model.layer_projections()
+    layer0 = {p.name: w for p, w in zip(chain.projs, chain.layers[0])}
+
+    def make(name, p):
+        buf = layer0[name.split(".")[2]]
+        return buf[: p.n * p.dtype.row_bytes(p.k)].cpu().numpy()
+
+    fd, path = tempfile.mkstemp(suffix=".gguf")
+    try:
+        with os.fdopen(fd, "wb") as f:
+            llama_gguf.write_random_llama(f, model, 1, make, include_output=False)
+        size = os.path.getsize(path)
+        with open(path, "rb") as f:
+            content = Content.read(f)
+            loaded = llama_gguf.load_projections(f, content, "cuda")
+    finally:
+        os.unlink(path)
+    identical = True
+    for p in projs:
+        q = loaded[llama_gguf.checkpoint_name(f"blk.0.{p.name}.weight")]
+        x = chain.x_dev[p.k]
+        a = ops.gemv(p.dtype, q.data, x, p.n)
+        b = ops.gemv(p.dtype, layer0[p.name], x, p.n)
+        identical = identical and bool(torch.equal(a, b))
+    torch.cuda.synchronize()
+    return {"layers": 1, "tensors": len(projs), "file_bytes": size, "outputs_identical": identical}
+
+
 def reference_cuda_numbers(torch, pkg, chain, stream, peak, bf16_peak, steps):
     """The reference's own CUDA kernels on this GPU (oracle/_ref, built from the reference checkout): its decode chain
     as its host would launch it - one Q8_1 quantize per distinct input, plain matvecs for q/k/v (mixed types), the
@@ -885,6 +924,13 @@ def main():
                         ops.set_weight_successor(w, None)
                     del ws
 
+        gguf_trip = None
+        if extras:
+            try:
+                gguf_trip = gguf_round_trip(torch, pkg, ops, chain)
+            except Exception as exc:
+                gguf_trip = {"unavailable": f"{type(exc).__name__}: {exc}"}
+
         ref_cuda = None
         if extras:
             try:
@@ -951,6 +997,8 @@ def main():
         line["small_batch"] = small
     if sweep is not None:
         line["sweep"] = sweep
+    if gguf_trip is not None:
+        line["gguf_round_trip"] = gguf_trip
     if ref_cuda is not None:
         line["reference_cuda"] = ref_cuda
     if tp_base is not None:

@@ -916,12 +916,10 @@ static int launch_gemm_t(const void* w, const void* x, void* y, int M, int N, in
     if (encode == nullptr) return B200Q_ERR_UNSUPPORTED;
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)ldx * sizeof(T)};
     const cuuint32_t box[2] = {GEMM_BK, GEMM_BM};
-    const cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = ElemFormat<T>::value == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUresult r = encode(&map, dt, 2, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode_tiled_2d_cached(&map, dt, x, dims, (cuuint64_t)ldx * sizeof(T), box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     if (r != CUDA_SUCCESS) return B200Q_ERR_INVALID;
     GemmParams p{};
     p.w = static_cast<const uint8_t*>(w);

@@ -864,12 +864,9 @@ static int tcq_encode_w(CUtensorMap& map_w, const void* w, int N, int K, int til
     const int row_bytes = K / type_block_elems(TYPE) * type_block_bytes(TYPE);
     const bool u16 = TYPE == TYPE_Q8_0;  // a 272-byte chunk is more than 256 one-byte elements
     const cuuint64_t dims[2] = {(cuuint64_t)(u16 ? row_bytes / 2 : row_bytes), (cuuint64_t)N};
-    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
     const cuuint32_t box[2] = {(cuuint32_t)(u16 ? TT::PITCH / 2 : TT::PITCH), (cuuint32_t)tile_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(&map_w, u16 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(w), dims, strides,
-                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode_tiled_2d_cached(&map_w, u16 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, w, dims,
+                                        (cuuint64_t)row_bytes, box, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     return r == CUDA_SUCCESS ? 0 : B200Q_ERR_INVALID;
 }
 
@@ -905,11 +902,9 @@ static int launch_gemv_tc_i8(const void* w, const void* x, void* y, int M, int N
     if (rc != 0) return rc;
     {
         const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)TT::XROWS};
-        const cuuint64_t strides[1] = {(cuuint64_t)K};
         const cuuint32_t box[2] = {128, (cuuint32_t)TT::XROWS};
-        const cuuint32_t estr[2] = {1, 1};
-        CUresult r = encode(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, q, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        CUresult r = encode_tiled_2d_cached(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, q, dims, (cuuint64_t)K, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
         if (r != CUDA_SUCCESS) return B200Q_ERR_INVALID;
     }
 

@@ -1,6 +1,7 @@
 // Wrappers around the sm_100a instructions the tensor-core kernels share: tiled TMA loads, tensor-memory allocation,
 // tcgen05.mma / commit / ld, shared-memory operand descriptors, and the host lookup of cuTensorMapEncodeTiled.
 #pragma once
+#include <mutex>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -109,6 +110,52 @@ static inline EncodeTiledFn encode_tiled_fn() {
             cudaGetLastError();
     }
     return fn;
+}
+
+// cuTensorMapEncodeTiled for a 2-D map, remembered by its arguments: a decoder calls the same matrices with the same
+// shapes every step, and the encoding (a driver call of a microsecond or two on the host) depends on nothing else - a
+// map only describes an address range. A small direct-mapped table per translation unit, guarded by a mutex.
+struct TensorMapKey {
+    const void* ptr;
+    unsigned long long dim0, dim1, stride0;
+    unsigned int box0, box1;
+    int dtype, swizzle, l2;
+    bool operator==(const TensorMapKey& o) const {
+        return ptr == o.ptr && dim0 == o.dim0 && dim1 == o.dim1 && stride0 == o.stride0 && box0 == o.box0 && box1 == o.box1 &&
+               dtype == o.dtype && swizzle == o.swizzle && l2 == o.l2;
+    }
+};
+static inline CUresult encode_tiled_2d_cached(CUtensorMap* out, CUtensorMapDataType dt, const void* ptr, const cuuint64_t (&dims)[2],
+                                             cuuint64_t stride0, const cuuint32_t (&box)[2], CUtensorMapSwizzle swizzle,
+                                             CUtensorMapL2promotion l2) {
+    constexpr int SLOTS = 256;
+    struct Slot { TensorMapKey key; CUtensorMap map; bool used; };
+    static Slot table[SLOTS];
+    static std::mutex mu;
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (encode == nullptr) return CUDA_ERROR_NOT_SUPPORTED;
+    const TensorMapKey key{ptr, dims[0], dims[1], stride0, box[0], box[1], (int)dt, (int)swizzle, (int)l2};
+    unsigned long long h = reinterpret_cast<unsigned long long>(ptr) >> 4;
+    h = (h ^ (dims[1] * 0x9E3779B97F4A7C15ull) ^ (dims[0] << 7) ^ box[1]) * 0xD6E8FEB86659FD93ull;
+    Slot& slot = table[(h >> 40) % SLOTS];
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (slot.used && slot.key == key) {
+            *out = slot.map;
+            return CUDA_SUCCESS;
+        }
+    }
+    const cuuint64_t strides[1] = {stride0};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, l2,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+        std::lock_guard<std::mutex> lock(mu);
+        slot.key = key;
+        slot.map = *out;
+        slot.used = true;
+    }
+    return r;
 }
 
 }  // namespace b200q
