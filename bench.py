@@ -792,6 +792,33 @@ def main():
         if not args.no_prefetch:
             register_launch_order(ops, chain.launch_sequence())
         achieved = dom_bytes / (dom_us * 1e-6) / 1e9
+
+        # ---- every other launch of a layer the same way (one GPU): each kind timed alone over the layers' distinct
+        # weights, with its own algorithmic bytes. All of them are launches of the same kernel.
+        by_launch = None
+        if not tp and not args.shard_of:
+            by_launch = []
+            kinds = [[chain.projs[i] for i in g] for g in chain.groups] + [[p] for i, p in enumerate(chain.projs) if i not in chain.grouped]
+            for members in kinds:
+                idx = [chain.projs.index(p) for p in members]
+                k0 = members[0].k
+                outs_k = [torch.empty(1, p.n, dtype=torch.bfloat16, device="cuda") for p in members]
+                if len(members) > 1:
+                    fns = [(lambda li=li: ops.gemv_group([p.dtype for p in members], [chain.layers[li][i] for i in idx], chain.x_dev[k0],
+                                                         [p.n for p in members], outs=outs_k)) for li in range(nl)]
+                else:
+                    fns = [(lambda li=li: ops.gemv(members[0].dtype, chain.layers[li][idx[0]], chain.x_dev[k0], members[0].n, out=outs_k[0]))
+                           for li in range(nl)]
+                seq_k = [(chain.layers[li][idx[-1]], chain.layers[li][idx[0]], members[0].dtype, k0, members[0].n) for li in range(nl)]
+                if not args.no_prefetch:
+                    register_launch_order(ops, seq_k)
+                us_k = time_launch_list(torch, stream, fns, 10)
+                nbytes = sum(p.weight_bytes for p in members) + k0 * 2 + sum(p.n for p in members) * 2
+                by_launch.append({"launch": " + ".join(p.name for p in members), "types": "/".join(p.dtype.name for p in members),
+                                  "k": k0, "n": [p.n for p in members], "us_per_launch": round(us_k, 2), "algorithmic_bytes": nbytes,
+                                  "GBps": round(nbytes / us_k / 1e3, 1), "frac_of_measured_hbm": round(nbytes / us_k / 1e3 / peak, 3)})
+            if not args.no_prefetch:
+                register_launch_order(ops, chain.launch_sequence())
         clocks.__exit__(None, None, None)
 
         extras = not tp and not args.quick and not args.shard_of
@@ -985,6 +1012,8 @@ def main():
     }
     line["hbm_frac_of_measured"] = line["weights_GBps_per_gpu"] / peak
     line["hbm_frac_of_nominal_8TBps"] = line["weights_GBps_per_gpu"] / 8000.0
+    if by_launch is not None:
+        line["roofline_by_launch"] = by_launch
     if tp_check is not None:
         line["tp_check"] = tp_check
     if tp_extra is not None:
