@@ -164,7 +164,7 @@ def register_launch_order(ops, seq):
 
 # DRAM bytes per launch measured by ncu (dram__bytes_read.sum + dram__bytes_write.sum); the summaries are under profiles/
 NCU_TRAFFIC_GEMV_Q4K_4096_14336 = 33085184
-NCU_TRAFFIC_GROUP_GATE_UP = 66442752
+NCU_TRAFFIC_GROUP_GATE_UP = 66316288
 
 TYPE_TAGS = {"q4_k": "Q4K", "q6_k": "Q6K", "q8_0": "Q8_0"}
 
@@ -1006,7 +1006,11 @@ def main():
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "kernel": dom_kernel, "shape": f"K={gp.k} N={gp.n}",
                      "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
-                     "us_per_launch": dom_us, "algorithmic_bytes": dom_bytes, "traffic": dom_traffic},
+                     "us_per_launch": dom_us, "algorithmic_bytes": dom_bytes, "traffic": dom_traffic,
+                     "traffic_note": "dram read + write of one launch under ncu with the L2 prefetch of the next matrix off; with it on, "
+                                     "a launch also fetches up to 148 x 160 KB of the NEXT launch's rows, which that launch then "
+                                     "does not read from DRAM: over a layer's four launches the DRAM traffic measured in the chain "
+                                     "equals the algorithmic bytes (profiles/gemv_group_q4k_gate_up.txt)"},
         "clocks": clocks.summary(),
         "device_status": list(status),
     }
