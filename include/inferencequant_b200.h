@@ -172,6 +172,20 @@ void launch_mmq_quantize_q8_1_DS4(const void* x, const int32_t* ids, void* vy, i
                                   int64_t s02, int64_t s03, int64_t ne0, int64_t ne1, int64_t ne2, int64_t ne3,
                                   void* stream);
 
+/* The same quantizer with the gated activation of an MLP folded in: what is quantized is act(gate) * up (the activation
+ * in f32, rounded to the input type; the product in the input type), so that the down projection's prefill activations
+ * come straight from the gate and up outputs. gate, up: rows of ne00 values at stride s01; activation ids as for
+ * fused_glu above. The _f32 forms take f32 inputs without a type argument.
+ * Replaces crates/inference-quant/src/gguf/ffi.rs:702-770 (kernels/cuda/mmq_gguf/mmq_quantize.cu:201-330). */
+void launch_mmq_quantize_glu_q8_1_D4(const void* gate, const void* up, const int32_t* ids, void* vy, int type_x, int64_t ne00,
+                                     int64_t s01, int64_t ne0, int64_t ne1, int activation, void* stream);
+void launch_mmq_quantize_glu_q8_1_DS4(const void* gate, const void* up, const int32_t* ids, void* vy, int type_x, int64_t ne00,
+                                      int64_t s01, int64_t ne0, int64_t ne1, int activation, void* stream);
+void launch_mmq_quantize_glu_q8_1_D4_f32(const float* gate, const float* up, const int32_t* ids, void* vy, int64_t ne00,
+                                         int64_t s01, int64_t ne0, int64_t ne1, int activation, void* stream);
+void launch_mmq_quantize_glu_q8_1_DS4_f32(const float* gate, const float* up, const int32_t* ids, void* vy, int64_t ne00,
+                                          int64_t s01, int64_t ne0, int64_t ne1, int activation, void* stream);
+
 /* Prefill matmul on activations quantized by launch_mmq_quantize_q8_1_{D4,DS4}: dst[token * stride_col_dst + row] =
  * sum_k W[row][k] * (d q)[token][k] for token < ncols_y, row < nrows_x. x: packed weights, stride_row_x blocks per row;
  * y: the 144-byte activation blocks (D4 for Q8_0 and Q6_K weights, DS4 for Q4_K: the reference's host pairs them so,
@@ -215,8 +229,10 @@ const char* b200q_last_error(void);
 /* Options: "pdl" (launch GEMVs and quantizers with programmatic stream serialization), "force_simple_gemv",
  * "gemv_stage_bytes", "gemv_passes" (0 = the planner's choice, 1 or 2 passes of all warps per stage),
  * "gemv_pass_limit_bytes" (bytes one pass may cover before a row is given more warps), "gemv_ctas_per_sm", "tc_ksplit",
- * "gemm_direct", "l2_prefetch_bytes" (see b200q_set_weight_successor; 0 switches the prefetch off). get also answers
- * "sm_count" and "smem_optin". */
+ * "gemm_direct", "gemv_one_kernel" (one-row GEMVs on the grouped kernel, default 1), "l2_prefetch_bytes" (see
+ * b200q_set_weight_successor; 0 switches the prefetch off). get also answers "sm_count" and "smem_optin". Options are
+ * process-wide tuning and test switches, read by every launch without synchronization: set them once, before the
+ * threads that launch are started; the launchers themselves keep no other mutable state. */
 int b200q_set_option(const char* name, int value);
 int b200q_get_option(const char* name, int* value);
 

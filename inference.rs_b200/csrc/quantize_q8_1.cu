@@ -62,11 +62,31 @@ __device__ __forceinline__ float4 load4(const src_t* x, long long base, long lon
     return v;
 }
 
+// act(gate) * up as the reference's fused quantizer forms it (kernels/cuda/mmq_gguf/mmq_quantize.cu:201-235): the
+// activation in f32, rounded to the input type, the product in the input type. Activation ids: 0 SiLU, 1 GELU (tanh),
+// 2 ReLU, 3 GELU (erf), 4 sigmoid; anything else SiLU.
+__device__ __forceinline__ float mmq_glu_act(float x, int act) {
+    switch (act) {
+        case 1: return 0.5f * x * (1.0f + tanhf(0.7978845608f * (x + 0.044715f * (x * x * x))));
+        case 2: return fmaxf(x, 0.0f);
+        case 3: return x * normcdff(x);
+        case 4: return 1.0f / (1.0f + expf(-x));
+        default: return x / (1.0f + expf(-x));
+    }
+}
+template <typename src_t> __device__ __forceinline__ float mmq_glu_product(float gate, float up, int act) {
+    if constexpr (sizeof(src_t) == 4) return mmq_glu_act(gate, act) * up;
+    else return to_float<src_t>(__hmul(from_float<src_t>(mmq_glu_act(gate, act)), from_float<src_t>(up)));
+}
+
 // grid (rows, ceil(ne0 / 512)), block 128: thread t of block (row, cy) takes values i0 = (128 cy + t) * 4.
-template <typename src_t, int LAYOUT>
+// GLU: x is the gate, `up` the second operand of the same shape, and act(gate) * up is what gets quantized
+// (launch_mmq_quantize_glu_q8_1_*: the MLP's down projection reads its prefill activations straight from gate and up).
+template <typename src_t, int LAYOUT, bool GLU = false>
 __global__ void __launch_bounds__(128) quantize_mmq_q8_1_kernel(const src_t* __restrict__ x, const int32_t* __restrict__ ids,
                                                                uint8_t* __restrict__ vy, long long ne00, long long s01,
-                                                               long long ne0, int ne1) {
+                                                               long long ne0, int ne1, const src_t* __restrict__ up = nullptr,
+                                                               int activation = 0) {
     grid_dependency_wait();
     const long long i0 = ((long long)blockDim.x * blockIdx.y + threadIdx.x) * 4;
     // ne0 is a multiple of 128, so a warp (128 values) is inside or outside as a whole and the shuffles below
@@ -76,7 +96,12 @@ __global__ void __launch_bounds__(128) quantize_mmq_q8_1_kernel(const src_t* __r
         const long long i01 = ids ? ids[i1] : i1;
         const long long ib = (i0 / 128) * ne1 + i1;
         const int iqs = (int)(i0 % 128);
-        const float4 xi = load4<src_t>(x, i01 * s01 + i0, i0, ne00);
+        float4 xi = load4<src_t>(x, i01 * s01 + i0, i0, ne00);
+        if constexpr (GLU) {
+            const float4 u = load4<src_t>(up, i01 * s01 + i0, i0, ne00);
+            xi = make_float4(mmq_glu_product<src_t>(xi.x, u.x, activation), mmq_glu_product<src_t>(xi.y, u.y, activation),
+                             mmq_glu_product<src_t>(xi.z, u.z, activation), mmq_glu_product<src_t>(xi.w, u.w, activation));
+        }
         float amax = fmaxf(fmaxf(fabsf(xi.x), fabsf(xi.y)), fmaxf(fabsf(xi.z), fabsf(xi.w)));
 #pragma unroll
         for (int off = 4; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
@@ -120,6 +145,22 @@ static void launch_quantize_mmq(const void* x, const int32_t* ids, void* vy, int
         quantize_mmq_q8_1_kernel<__nv_bfloat16, LAYOUT><<<grid, 128, 0, s>>>((const __nv_bfloat16*)x, ids, (uint8_t*)vy, ne00, s01, ne0, (int)ne1);
 }
 
+template <int LAYOUT>
+static void launch_quantize_mmq_glu(const void* gate, const void* up, const int32_t* ids, void* vy, int type_x, long long ne00,
+                                    long long s01, long long ne0, long long ne1, int activation, cudaStream_t s) {
+    if (ne1 <= 0 || ne0 <= 0) return;
+    dim3 grid((unsigned)ne1, (unsigned)((ne0 + 511) / 512), 1);
+    if (type_x == 0)
+        quantize_mmq_q8_1_kernel<float, LAYOUT, true><<<grid, 128, 0, s>>>((const float*)gate, ids, (uint8_t*)vy, ne00, s01, ne0, (int)ne1,
+                                                                          (const float*)up, activation);
+    else if (type_x == 1)
+        quantize_mmq_q8_1_kernel<__half, LAYOUT, true><<<grid, 128, 0, s>>>((const __half*)gate, ids, (uint8_t*)vy, ne00, s01, ne0, (int)ne1,
+                                                                           (const __half*)up, activation);
+    else
+        quantize_mmq_q8_1_kernel<__nv_bfloat16, LAYOUT, true><<<grid, 128, 0, s>>>((const __nv_bfloat16*)gate, ids, (uint8_t*)vy, ne00, s01, ne0,
+                                                                                  (int)ne1, (const __nv_bfloat16*)up, activation);
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -148,6 +189,25 @@ void launch_mmq_quantize_q8_1_DS4(const void* x, const int32_t* ids, void* vy, i
                                   void* stream) {
     (void)s02; (void)s03; (void)ne2; (void)ne3;
     launch_quantize_mmq<MMQ_DS4>(x, ids, vy, type_x, ne00, s01, ne0, ne1, (cudaStream_t)stream);
+}
+
+// The prefill quantizer with the gated activation folded in: act(gate) * up, rows of ne00 values at stride s01, quantized to
+// the same blocks as launch_mmq_quantize_q8_1_* (crates/inference-quant/src/gguf/ffi.rs:702-770).
+void launch_mmq_quantize_glu_q8_1_D4(const void* gate, const void* up, const int32_t* ids, void* vy, int type_x, int64_t ne00, int64_t s01,
+                                     int64_t ne0, int64_t ne1, int activation, void* stream) {
+    launch_quantize_mmq_glu<MMQ_D4>(gate, up, ids, vy, type_x, ne00, s01, ne0, ne1, activation, (cudaStream_t)stream);
+}
+void launch_mmq_quantize_glu_q8_1_DS4(const void* gate, const void* up, const int32_t* ids, void* vy, int type_x, int64_t ne00, int64_t s01,
+                                      int64_t ne0, int64_t ne1, int activation, void* stream) {
+    launch_quantize_mmq_glu<MMQ_DS4>(gate, up, ids, vy, type_x, ne00, s01, ne0, ne1, activation, (cudaStream_t)stream);
+}
+void launch_mmq_quantize_glu_q8_1_D4_f32(const float* gate, const float* up, const int32_t* ids, void* vy, int64_t ne00, int64_t s01,
+                                         int64_t ne0, int64_t ne1, int activation, void* stream) {
+    launch_quantize_mmq_glu<MMQ_D4>(gate, up, ids, vy, 0, ne00, s01, ne0, ne1, activation, (cudaStream_t)stream);
+}
+void launch_mmq_quantize_glu_q8_1_DS4_f32(const float* gate, const float* up, const int32_t* ids, void* vy, int64_t ne00, int64_t s01,
+                                          int64_t ne0, int64_t ne1, int activation, void* stream) {
+    launch_quantize_mmq_glu<MMQ_DS4>(gate, up, ids, vy, 0, ne00, s01, ne0, ne1, activation, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -44,6 +44,9 @@ for _e in ("bf16", "f16", "f32"):
         SYMBOLS[f"launch_mmvq_gguf_{_t}_{_e}_fused_qkv"] = ([_vp] * 7 + [_i32] * 6 + [_vp], None)
 for _l in ("D4", "DS4"):
     SYMBOLS[f"launch_mmq_quantize_q8_1_{_l}"] = (_MMQ_QUANT_ARGS, None)
+for _l in ("D4", "DS4"):
+    SYMBOLS[f"launch_mmq_quantize_glu_q8_1_{_l}"] = ([_vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp], None)
+    SYMBOLS[f"launch_mmq_quantize_glu_q8_1_{_l}_f32"] = ([_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp], None)
 for _t in ("q8_0", "q4_k", "q6_k"):
     SYMBOLS[f"launch_mmq_gguf_{_t}"] = ([_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i64, _i32, _i32, _vp], None)
 SYMBOLS.update({

@@ -100,6 +100,28 @@ def quantize_mmq_q8_1(x: torch.Tensor, layout: str, k_padded: int | None = None)
     return out
 
 
+def quantize_mmq_q8_1_glu(gate: torch.Tensor, up: torch.Tensor, layout: str, activation: str = "silu", k_padded: int | None = None,
+                          typed: bool = True) -> torch.Tensor:
+    """`launch_mmq_quantize_glu_q8_1_{D4,DS4}` (or its `_f32` form when `typed` is false): act(gate) * up, [rows, k] each,
+    quantized to the prefill blocks; uint8 [k_padded / 128, rows, 144]."""
+    _require_cuda(gate, up)
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("gate and up have the same shape and type")
+    rows, k = gate.shape
+    k_padded = pad(pad(k, MATRIX_ROW_PADDING), 128) if k_padded is None else k_padded
+    out = torch.empty((k_padded // 128, rows, 144), dtype=torch.uint8, device=gate.device)
+    act = GLU_ACTIVATIONS[activation]
+    if typed:
+        getattr(kl.library(), f"launch_mmq_quantize_glu_q8_1_{layout}")(gate.data_ptr(), up.data_ptr(), None, out.data_ptr(),
+                                                                       MMQ_TYPE_X[elem_of(gate.dtype)], k, k, k_padded, rows, act, _stream())
+    else:
+        if gate.dtype != torch.float32:
+            raise TypeError("the _f32 launcher takes f32 inputs")
+        getattr(kl.library(), f"launch_mmq_quantize_glu_q8_1_{layout}_f32")(gate.data_ptr(), up.data_ptr(), None, out.data_ptr(), k, k,
+                                                                           k_padded, rows, act, _stream())
+    return out
+
+
 def mmvq_plain(dtype: GgmlDType, w: torch.Tensor, vy: torch.Tensor, n: int, k: int, b: int,
                out_dtype: torch.dtype, k_padded: int | None = None) -> torch.Tensor:
     """`launch_mmvq_gguf_<type>_<out>_plain` on Q8_1 blocks `vy`; returns [b, n]."""
