@@ -73,3 +73,15 @@ def test_gemv_plans_respect_hardware_limits(tag, k, n, b):
     assert plan["stage_bytes"] >= plan["rows_per_stage"] * dt.row_bytes(k) + 16
     assert (plan["row_align"] * dt.row_bytes(k)) % 16 == 0
     assert 1 <= plan["grid"] <= 148
+
+
+def test_trace_buffer_needs_a_trace_build():
+    """The launch timelines are a build option; the default library says so instead of silently ignoring the buffer."""
+    import ctypes
+    lib = pkg.library()
+    assert lib.b200q_set_trace_buffer(None, 0) == 0
+    rc = lib.b200q_set_trace_buffer(ctypes.c_void_p(4096), 4)
+    assert rc in (0, -1)  # B200Q_ERR_UNSUPPORTED; 0 only in a library built with -DB200Q_GEMV_TRACE=1
+    if rc != 0:
+        assert b"B200Q_GEMV_TRACE" in lib.b200q_last_error()
+    lib.b200q_set_trace_buffer(None, 0)
