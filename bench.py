@@ -373,9 +373,9 @@ class Chain:
         self.logits = torch.empty(1, self.head.n, dtype=torch.bfloat16, device="cuda")
         self.bytes_per_step = model.layers * sum(p.weight_bytes for p in self.projs) + self.head.weight_bytes  # per GPU
         # projections that read the same input go out in one launch: q/k/v, gate/up (the reference's fused_qkv / fused_glu
-        # matvec launches, crates/inference-quant/src/lib.rs:2441-2776); the grouped kernel quantizes to Q8_1 only
+        # matvec launches, crates/inference-quant/src/lib.rs:2441-2776)
         self.groups = []
-        if group and act_quant == 0:
+        if group:
             names = [p.name for p in self.projs]
             for members in (("attn_q", "attn_k", "attn_v"), ("ffn_gate", "ffn_up")):
                 self.groups.append([names.index(m) for m in members])
@@ -402,7 +402,7 @@ class Chain:
         for li in range(self.model.layers):
             for g in self.groups:
                 ops.gemv_group([self.projs[i].dtype for i in g], [self.layers[li][i] for i in g], self.x_dev[self.projs[g[0]].k],
-                               [self.projs[i].n for i in g], outs=[self.outs[li][i] for i in g])
+                               [self.projs[i].n for i in g], outs=[self.outs[li][i] for i in g], act_quant=self.act_quant)
             for i, (p, w, o) in enumerate(zip(self.projs, self.layers[li], self.outs[li])):
                 if i in self.grouped:
                     continue
@@ -862,16 +862,16 @@ def main():
             del qms, head_qm
 
         # ---- the element-wise-exact mode: the same chain with activations quantized to the CPU path's format (Q8_K /
-        # Q8_0) in the kernel prologue, one launch per projection (the grouped kernel quantizes to Q8_1 only)
+        # Q8_0) in the kernel prologue, grouped and routed like the headline chain
         cpu_format = None
         if extras:
             ops.clear_weight_successors()
-            exact = Chain(torch, pkg, ops, workloads, model, 1, 99, group=False, act_quant=1, weights_of=chain)
+            exact = Chain(torch, pkg, ops, workloads, model, 1, 99, group=not args.no_group, act_quant=1, weights_of=chain)
             if not args.no_prefetch:
                 register_launch_order(ops, exact.launch_sequence())
             ms_exact = time_chain(torch, stream, exact.step, max(3, args.steps // 4), 3)
             cpu_format = {"value": 1000.0 / ms_exact, "unit": UNIT, "ms_per_step": ms_exact, "launches_per_step": exact.launches_per_step,
-                          "note": "act_quant=1: activations in the reference CPU path's Q8_K / Q8_0 format, element-wise within 1e-2 / 1e-3 of it"}
+                          "note": "act_quant=1: activations in the reference CPU path's Q8_K / Q8_0 format, element-wise within 1e-2 / 1e-3 of it; same grouping and kernel routing as the headline"}
             ops.clear_weight_successors()
             if not args.no_prefetch:
                 register_launch_order(ops, chain.launch_sequence())

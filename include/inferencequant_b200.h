@@ -284,6 +284,10 @@ int b200q_clear_weight_successors(void);
  * them, accepts matrices of different types. The pointer arrays are host arrays read during the call. */
 int b200q_gemv_group(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, int elem,
                      const void* x, void* stream);
+/* The same with b200q_gemv's act_quant: 1 quantizes the activations to the reference CPU path's format (then the group's
+ * matrices must agree on it: all Q8_0, or all K-quants with K a multiple of 256). */
+int b200q_gemv_group_act(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, int elem,
+                         const void* x, int act_quant, void* stream);
 
 /* No counterpart in the reference. The decode GEMV for callers that cannot allocate device memory (their memory
  * belongs to a pool of their own, or they may not call cudaMalloc because it synchronizes the device and stalls

@@ -17,7 +17,7 @@ int gemv_q6_k(int, const void*, const void*, void*, int, int, int, int, int, int
 int gemv_q8_0(int, const void*, const void*, void*, int, int, int, int, int, int, const PeerExchange*, cudaStream_t);
 void gemv_describe(int type, int K, int N, int b, int* out);
 int gemv_group(int elem, int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, const void* x,
-               cudaStream_t s, const PeerExchange* px);
+               cudaStream_t s, const PeerExchange* px, int act_mode);
 int gemm_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, cudaStream_t s);
 int gemv_tc_dispatch(int type, int elem, const void* w, const void* x, void* y, int M, int N, int K, int ldx, int ldy, void* workspace, cudaStream_t s);
 size_t gemv_tc_workspace_bytes(int type, int K);
@@ -174,15 +174,26 @@ int b200q_clear_weight_successors(void) {
 }
 
 // Grouped decode GEMV: nmat (1..4) weight matrices with the same K applied to the same activation row x [K] in one launch.
-int b200q_gemv_group(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, int elem,
-                     const void* x, void* stream) {
+static int gemv_group_checked(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, int elem,
+                              const void* x, int act_quant, void* stream) {
     if (!types || !ws || !dsts || !Ns || !x) return set_error(B200Q_ERR_INVALID, "null pointer");
     if (nmat < 1 || nmat > 4) return set_error(B200Q_ERR_INVALID, "b200q_gemv_group takes 1..4 matrices");
-    const int rc = gemv_group(elem, nmat, types, ws, dsts, Ns, K, x, (cudaStream_t)stream, nullptr);
+    if (act_quant != 0 && act_quant != 1) return set_error(B200Q_ERR_INVALID, "act_quant is 0 (Q8_1) or 1 (CPU path's format)");
+    const int rc = gemv_group(elem, nmat, types, ws, dsts, Ns, K, x, (cudaStream_t)stream, nullptr, act_quant == 0 ? 1 : 2);
     if (rc == B200Q_ERR_UNSUPPORTED)
-        return set_error(rc, "group not supported (K must be a multiple of 128, weights 16-byte aligned): launch the matrices one by one");
+        return set_error(rc, "group not supported (K must be a multiple of 128 - 256 for K-quants with act_quant 1 -, weights 16-byte "
+                             "aligned, and with act_quant 1 all matrices Q8_0 or none): launch the matrices one by one");
     if (rc != 0) return set_error(rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "grouped gemv failed");
     return B200Q_OK;
+}
+int b200q_gemv_group(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, int elem,
+                     const void* x, void* stream) {
+    return gemv_group_checked(nmat, types, ws, dsts, Ns, K, elem, x, 0, stream);
+}
+// The same with the activation format chosen as in b200q_gemv (act_quant 1: the reference CPU path's Q8_K / Q8_0).
+int b200q_gemv_group_act(int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, int elem,
+                         const void* x, int act_quant, void* stream) {
+    return gemv_group_checked(nmat, types, ws, dsts, Ns, K, elem, x, act_quant, stream);
 }
 
 // Prefill GEMM on the tensor cores: y[M][ldy] = x[M][ldx] . W[N][K]^T, x and y of element type `elem` (bf16 or f16).

@@ -1191,11 +1191,21 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
         pre.issue(p.act, 1, p.K, p.K, p.act_vec != 0, tid);
     }
     // the activation row is quantized once for all matrices
-    if constexpr (ACT == ACT_Q8_1)
+    if constexpr (ACT == ACT_Q8_1) {
         stage_acts_q8_1<1>(acts, reinterpret_cast<const uint8_t*>(p.act), p.K, 0, tid, GEMV_CONSUMER_THREADS, pre);
-    else
+    } else if constexpr (ACT == ACT_RAW_CPU) {
+        // the CPU path's format depends on the weight type (Q8_K for the K-quants, Q8_0 for Q8_0): the launcher admits
+        // only groups whose matrices agree on it
+        if (p.type[0] == TYPE_Q8_0)
+            stage_acts_raw<1, act_t, TYPE_Q8_0, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.K, p.act_vec != 0, tid,
+                                                     GEMV_CONSUMER_THREADS, pre);
+        else
+            stage_acts_raw<1, act_t, TYPE_Q4_K, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.K, p.act_vec != 0, tid,
+                                                     GEMV_CONSUMER_THREADS, pre);
+    } else {
         stage_acts_raw<1, act_t, TYPE_Q4_K, ACT>(acts, reinterpret_cast<const act_t*>(p.act), p.K, p.K, p.act_vec != 0, tid,
                                                  GEMV_CONSUMER_THREADS, pre);
+    }
     named_bar_sync(1, GEMV_CONSUMER_THREADS);
 
     const int items = p.K / 128;
@@ -1527,20 +1537,20 @@ static inline int launch_staged(const GemvPlan& plan, cudaStream_t s) {
 
 // (defined once, in gemv_group.cu: every caller must reach the SAME copy of the grouped kernel)
 int gemv_group(int elem, int nmat, const int* types, const void* const* ws, void* const* dsts, const int* Ns, int K, const void* x,
-               cudaStream_t s, const PeerExchange* px);
+               cudaStream_t s, const PeerExchange* px, int act_mode);
 
 template <int TYPE, int B, typename dst_t>
 static inline int launch_gemv_b(const void* vx, const void* act, void* dst, int K, int N, int stride_act, int stride_dst,
                                 int act_mode, const PeerExchange* px, cudaStream_t s) {
     const bool exchange = px != nullptr && px->world > 1;
-    if (B == 1 && act_mode == ACT_RAW_Q8_1 && runtime_info().gemv_one_kernel) {
+    if (B == 1 && (act_mode == ACT_RAW_Q8_1 || (act_mode == ACT_RAW_CPU && !exchange)) && runtime_info().gemv_one_kernel) {
         // One row of raw activations: the grouped kernel with a single matrix - the same arithmetic in the same order, a
         // little more bookkeeping per row, but a decode chain then alternates between fewer kernels, and its launches
         // are sensitive to how much code they have to fetch (+2 % on the chain).
         const int type = TYPE;
         constexpr int elem = sizeof(dst_t) == 4 ? ELEM_F32 : (std::is_same<dst_t, __half>::value ? ELEM_F16 : ELEM_BF16);
         if (!exchange || stride_dst == N) {
-            const int rc = gemv_group(elem, 1, &type, &vx, &dst, &N, K, act, s, exchange ? px : nullptr);
+            const int rc = gemv_group(elem, 1, &type, &vx, &dst, &N, K, act, s, exchange ? px : nullptr, act_mode);
             if (rc != B200Q_ERR_UNSUPPORTED) return rc;
         }
     }
@@ -1606,6 +1616,12 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
     if (exchange && (nmat != 1 || ACT != ACT_RAW_Q8_1 || Ns[0] % PIECE != 0 || (long long)Ns[0] * (long long)sizeof(dst_t) > px->capacity ||
                      reinterpret_cast<uintptr_t>(dsts[0]) % 8 != 0))
         return B200Q_ERR_UNSUPPORTED;
+    if (ACT == ACT_RAW_CPU) {
+        // one activation format for the whole group: all Q8_0 (blocks of 32) or all K-quants (superblocks of 256)
+        for (int m = 0; m < nmat; ++m)
+            if ((types[m] == TYPE_Q8_0) != (types[0] == TYPE_Q8_0)) return B200Q_ERR_UNSUPPORTED;
+        if (types[0] != TYPE_Q8_0 && K % 256 != 0) return B200Q_ERR_UNSUPPORTED;
+    }
     GemvGroupParams p{};
     p.nmat = nmat;
     p.K = K;

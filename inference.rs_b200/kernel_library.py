@@ -66,6 +66,7 @@ SYMBOLS.update({
     "b200q_peer_allreduce": ([_vp, _i32, _i32, _i64, _i32, _vp, _vp, _i64, _vp], _i32),
     "b200q_gemv_allreduce": ([_i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _i32, _i32, _i64, _vp], _i32),
     "b200q_gemv_group": ([_i32, C.POINTER(_i32), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i32), _i32, _i32, _vp, _vp], _i32),
+    "b200q_gemv_group_act": ([_i32, C.POINTER(_i32), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i32), _i32, _i32, _vp, _i32, _vp], _i32),
     "b200q_gemv_static_scratch": ([_i32, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp], _i32),
     "b200q_gemv_plan": ([_i32, _i32, _i32, _i32, C.POINTER(_i32 * 10)], _i32),
     "b200q_set_weight_successor": ([_vp, _vp, _i32, _i32, _i32], _i32),

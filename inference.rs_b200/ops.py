@@ -38,7 +38,10 @@ def upload_weights(packed: np.ndarray | torch.Tensor, dtype: GgmlDType, device="
     """Packed GGUF blocks -> device buffer followed by 512 elements' worth of zero bytes, as the reference's
     `load_quantized` does (crates/inference-tensor/src/quantized/cuda.rs:511-530)."""
     if isinstance(packed, np.ndarray):
-        packed = torch.from_numpy(np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1))
+        arr = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1)
+    if not arr.flags.writeable:
+        arr = arr.copy()  # torch tensors alias their numpy source and want it writable
+    packed = torch.from_numpy(arr)
     packed = packed.reshape(-1)
     padding = MATRIX_ROW_PADDING * dtype.type_size // dtype.block_size
     buf = torch.zeros(packed.numel() + padding, dtype=torch.uint8, device=device)
@@ -253,8 +256,9 @@ def gemv(dtype: GgmlDType, w: torch.Tensor, x: torch.Tensor, n: int, out: torch.
     return dst
 
 
-def gemv_group(dtypes, ws, x: torch.Tensor, ns, outs=None):
-    """`b200q_gemv_group`: several weight matrices (same K) on one activation row x [1, k] in one launch."""
+def gemv_group(dtypes, ws, x: torch.Tensor, ns, outs=None, act_quant: int = 0):
+    """`b200q_gemv_group` / `b200q_gemv_group_act`: several weight matrices (same K) on one activation row x [1, k] in one
+    launch; `act_quant` as for `gemv`."""
     _require_cuda(x, *ws)
     if x.dim() != 2 or x.shape[0] != 1:
         raise ValueError("gemv_group takes a single activation row [1, k]")
@@ -266,7 +270,11 @@ def gemv_group(dtypes, ws, x: torch.Tensor, ns, outs=None):
     wp = (C.c_void_p * n)(*[w.data_ptr() for w in ws])
     dp = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
     nn = (C.c_int * n)(*[int(v) for v in ns])
-    kl.check(kl.library().b200q_gemv_group(n, types, wp, dp, nn, k, elem_of(x.dtype), x.data_ptr(), _stream()), "b200q_gemv_group")
+    if act_quant == 0:
+        kl.check(kl.library().b200q_gemv_group(n, types, wp, dp, nn, k, elem_of(x.dtype), x.data_ptr(), _stream()), "b200q_gemv_group")
+    else:
+        kl.check(kl.library().b200q_gemv_group_act(n, types, wp, dp, nn, k, elem_of(x.dtype), x.data_ptr(), act_quant, _stream()),
+                 "b200q_gemv_group_act")
     return outs
 
 

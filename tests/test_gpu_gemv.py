@@ -223,3 +223,25 @@ def test_grouped_launch_equals_separate_launches():
     for (t, n), w, o in zip(shapes, ws, outs):
         assert torch.equal(o, ops.gemv(DT[t], w, x, n))
     assert_device_ok()
+
+
+def test_grouped_launch_in_the_cpu_activation_format():
+    """act_quant=1 through the grouped kernel: equal to the single launches bit for bit and element-wise within 1e-2 / 1e-3
+    of the CPU path; a group that mixes Q8_0 with K-quants (two activation formats) is refused."""
+    from inference_rs_b200 import kernel_library as kl
+    k = 4096
+    x = seeded_acts(1, k, 41, torch.bfloat16).cuda()
+    for shapes in ([(kq.Q4_K, 512), (kq.Q4_K, 128), (kq.Q6_K, 130)], [(kq.Q8_0, 300), (kq.Q8_0, 7)]):
+        packed = [kq.quantize(t, seeded_weights(n, k, 40 + n)) for t, n in shapes]
+        ws = [ops.upload_weights(p, DT[t]) for p, (t, _) in zip(packed, shapes)]
+        outs = ops.gemv_group([DT[t] for t, _ in shapes], ws, x, [n for _, n in shapes], act_quant=ops.ACT_QUANT_CPU)
+        torch.cuda.synchronize()
+        for (t, n), p, w, o in zip(shapes, packed, ws, outs):
+            assert torch.equal(o, ops.gemv(DT[t], w, x, n, act_quant=ops.ACT_QUANT_CPU)), (kq.TYPE_NAMES[t], n)
+            ref = kq.matmul(t, x.float().cpu().numpy(), p, n)
+            got = o.float().cpu().numpy()
+            assert (np.abs(got - ref) <= 1e-3 + 1e-2 * np.abs(ref)).all(), (kq.TYPE_NAMES[t], n)
+    ws = [ops.upload_weights(random_packed(t, 64, k, seed=3), DT[t]) for t in (kq.Q8_0, kq.Q4_K)]
+    with pytest.raises(kl.KernelLibraryError):
+        ops.gemv_group([DT[kq.Q8_0], DT[kq.Q4_K]], ws, x, [64, 64], act_quant=ops.ACT_QUANT_CPU)
+    assert_device_ok()
