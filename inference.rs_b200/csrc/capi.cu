@@ -249,8 +249,8 @@ int b200q_peer_allreduce(const void* const* bufs, int rank, int world, long long
     return B200Q_OK;
 }
 
-// Row-parallel matmul and its sum over the ranks in ONE launch: b200q_gemv whose last CTA to finish runs the peer-memory
-// all-reduce on the output, in place.
+// Row-parallel matmul and its sum over the ranks in ONE launch: b200q_gemv in which every CTA exchanges its own rows of the
+// output with the same CTA of the other ranks (peer_allreduce.cuh) and stores their sum.
 int b200q_gemv_allreduce(int type, int elem, const void* w, const void* x, void* dst, int K, int N, int b_size, const void* const* bufs,
                          int rank, int world, long long capacity, void* stream) {
     if (!bufs) return set_error(B200Q_ERR_INVALID, "null pointer");

@@ -640,8 +640,8 @@ __device__ __forceinline__ void exchange_cta_rows(const PeerExchange& px, const 
 // lane owns items slice*32 + lane + j*32*WPR, j < IPL. With fewer, a warp works on 32 / islots rows at once
 // (islots = items rounded up to a power of two): lane = rsub * islots + item.
 // ---------------------------------------------------------------------------------------------
-// AR: the variant whose last CTA sums the output over the tensor-parallel ranks (its own instantiation, so that the
-// plain kernel carries none of it)
+// AR: the variant whose CTAs exchange their rows of the output with the other tensor-parallel ranks and store the sum (its
+// own instantiation, so that the plain kernel carries none of it)
 template <int TYPE, int B, typename dst_t, int ACT, typename act_t, int NREG, bool AR = false>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_staged_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];

@@ -1,5 +1,5 @@
 // Device side of the one-shot sum all-reduce over peer-mapped buffers (protocol and buffer layout: peer_allreduce.cu),
-// shared by the stand-alone kernel and by the GEMV whose last CTA runs it on the matmul's own output.
+// shared by the stand-alone kernel and by the GEMVs whose CTAs run it on their own rows of the matmul's output.
 #pragma once
 #include "common.cuh"
 
