@@ -565,7 +565,9 @@ def main():
     ap.add_argument("--gemm", nargs=4, metavar=("TYPE", "K", "N", "M"), help="time one prefill GEMM shape only")
     ap.add_argument("--copies", type=int, default=0, help="--single: number of rotating weight copies")
     ap.add_argument("--two-launch", action="store_true", help="--single: quantize launcher + GEMV launcher instead of one launch")
-    ap.add_argument("--pdl", type=int, default=None, help="programmatic dependent launch on/off")
+    ap.add_argument("--pdl", type=int, default=1,
+                    help="programmatic dependent launch for the decode chain (the library's 'pdl' option; its default is 0 because it "
+                         "assumes that the weights are not written by the work just before a launch - true of a decoder's weights)")
     ap.add_argument("--stage-bytes", type=int, default=None, help="GEMV planner: target bytes per shared-memory stage")
     ap.add_argument("--prefetch-bytes", type=int, default=None, help="bytes of the next matrix each CTA asks L2 for")
     args = ap.parse_args()
@@ -1008,7 +1010,7 @@ def main():
                      "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": dom_us, "algorithmic_bytes": dom_bytes, "traffic": dom_traffic,
                      "traffic_note": "dram read + write of one launch under ncu with the L2 prefetch of the next matrix off; with it on, "
-                                     "a launch also fetches up to 148 x 160 KB of the NEXT launch's rows, which that launch then "
+                                     "a launch also fetches up to 148 x 256 KB of the NEXT launch's rows, which that launch then "
                                      "does not read from DRAM: over a layer's four launches the DRAM traffic measured in the chain "
                                      "equals the algorithmic bytes (profiles/gemv_group_q4k_gate_up.txt)"},
         "clocks": clocks.summary(),

@@ -245,3 +245,45 @@ def test_grouped_launch_in_the_cpu_activation_format():
     with pytest.raises(kl.KernelLibraryError):
         ops.gemv_group([DT[kq.Q8_0], DT[kq.Q4_K]], ws, x, [64, 64], act_quant=ops.ACT_QUANT_CPU)
     assert_device_ok()
+
+
+def test_programmatic_dependent_launch_keeps_the_data_dependencies():
+    """pdl=1 lets a launch start (barriers, weight stream) while its predecessor still runs; only the consumers wait for
+    it before they read the activations. A chain in which every launch reads what the launch before it wrote - single and
+    grouped launches, short and long rows - must give the same bits as with pdl=0, launched one by one and as a replayed
+    CUDA graph."""
+    k = 4096
+    mats = [(kq.Q4_K, 4096), (kq.Q6_K, 4096), (kq.Q4_K, 4096), (kq.Q8_0, 4096), (kq.Q4_K, 4096), (kq.Q6_K, 4096)]
+    ws = [ops.upload_weights(kq.quantize(t, seeded_weights(n, k, 500 + i) * 4.0), DT[t]) for i, (t, n) in enumerate(mats)]
+    pair = [ops.upload_weights(kq.quantize(kq.Q4_K, seeded_weights(2048, k, 600 + i) * 4.0), DT[kq.Q4_K]) for i in range(2)]
+    x0 = seeded_acts(1, k, 77, torch.bfloat16).cuda()
+
+    def chain():
+        x = x0
+        for (t, n), w in zip(mats, ws):
+            x = ops.gemv(DT[t], w, x, n)                      # [1, 4096] feeds the next launch
+        a, b = ops.gemv_group([DT[kq.Q4_K]] * 2, pair, x, [2048, 2048])
+        return torch.cat([a, b], dim=1)                        # [1, 4096]
+
+    results = {}
+    try:
+        for pdl in (0, 1):
+            ops.set_option("pdl", pdl)
+            eager = chain()
+            torch.cuda.synchronize()
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    captured = chain()
+                for _ in range(3):
+                    graph.replay()
+                stream.synchronize()
+            results[pdl] = (eager.clone(), captured.clone())
+    finally:
+        ops.set_option("pdl", 0)
+    assert torch.isfinite(results[0][0].float()).all() and float(results[0][0].float().abs().max()) > 0
+    assert torch.equal(results[0][0], results[0][1])
+    assert torch.equal(results[1][0], results[0][0]), "pdl=1, eager launches"
+    assert torch.equal(results[1][1], results[0][0]), "pdl=1, graph replay"
+    assert_device_ok()
