@@ -378,10 +378,18 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
                     q[j] = amax == 0.0f ? 0 : (int)qr;
                     near_half |= (fabsf(q1 - qr) > 0.4999f) ? (1u << j) : 0u;
                 }
-                if (near_half != 0u && amax != 0.0f) {  // rare: decided by the division itself, out of line
+                // decided by the division itself, out of line: a lane rarely flags more than one of its values, so the
+                // warp goes round once per flagged value of its worst lane, not once per position any lane flagged
+                // (the block's warps meet at a barrier after this, so the slowest warp sets the time)
+                while (near_half != 0u) {
+                    const int j = __ffs(near_half) - 1;
+                    near_half &= near_half - 1u;
+                    float vj = v[0];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        if ((near_half >> j) & 1u) q[j] = round_div_exact(v[j], d);
+                    for (int t = 1; t < 8; ++t) vj = j == t ? v[t] : vj;
+                    const int r = round_div_exact(vj, d);
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) q[t] = j == t ? r : q[t];
                 }
             }
             d_used = __half2float(__float2half_rn(d));

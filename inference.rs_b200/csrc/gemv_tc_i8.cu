@@ -116,6 +116,8 @@ __global__ void __launch_bounds__(32 * TCQ_TOKENS) tcq_quantize_kernel(const src
                                                                       float2* __restrict__ ds, int K, int M, int ldx,
                                                                       unsigned int* __restrict__ counters) {
     const int kb = blockIdx.x, row = threadIdx.y, lane = threadIdx.x;
+    // the matvec launch that follows may start now: until its own dependency wait it only sets up and streams weights
+    grid_launch_dependents();
     if (kb == 0) {  // the K-split arrival counters of the launch that follows
         const int i = row * 32 + lane;
         for (int c = i; c < TCQ_COUNTERS; c += 32 * TCQ_TOKENS) counters[c] = 0u;
@@ -465,6 +467,11 @@ __global__ void __launch_bounds__(TCQ_THREADS, 1)
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
+    // Launched as a programmatic dependent of the quantize launch (launch_gemv_tc_i8_tok's `after_quantizer`), the CTA
+    // got this far, and its packed-row warp streams weights, while the quantizer still runs; what the quantizer writes
+    // (activation tiles, scales, the K-split counters) is first touched behind this wait, directly by warp 0 and by
+    // every other warp only after a stage that warp 0 has handed on. Without that launch attribute the wait returns at once.
+    if (warp == 0) grid_dependency_wait();
     if (warp == 0 && REF_ACTS) {
         // ---------------- activation tiles re-laid out from the reference tier's fragments, by the whole warp ----------------
         TcqRing xr;
@@ -803,14 +810,25 @@ size_t gemv_tc_workspace_bytes(int type, int K) {
 
 template <int TYPE, typename T, int TOK, bool REF_ACTS = false>
 static int launch_gemv_tc_i8_tok(const CUtensorMap& map_w, const CUtensorMap& map_x, const TcqParams& p, int grid, int smem_bytes,
-                                 cudaStream_t s) {
+                                 cudaStream_t s, bool after_quantizer = false) {
     auto kernel = gemv_tc_i8_kernel<TYPE, T, TOK, REF_ACTS>;
     static PerDeviceOnce configured;  // per instantiation and device
     const cudaError_t attr_err =
         configured.run([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TCQ_SMEM_LIMIT); });
     if (attr_err != cudaSuccess) return (int)attr_err;
-    kernel<<<grid, TCQ_THREADS, smem_bytes, s>>>(map_w, map_x, p);
-    return (int)cudaGetLastError();
+    // `after_quantizer`: the launch directly before this one on the stream is this file's quantizer, which lets its
+    // dependents start early; the two overlap safely because the quantizer writes nothing this kernel reads before its wait
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(TCQ_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = after_quantizer ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, p);
 }
 
 // Row split, K split and ring depths for a shape; fills p.{ksplit, tile_rows, rows_per_cta, rows_extra, a_stages,
@@ -912,9 +930,9 @@ static int launch_gemv_tc_i8(const void* w, const void* x, void* y, int M, int N
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
 
-    if (M <= 4) return launch_gemv_tc_i8_tok<TYPE, T, 4>(map_w, map_x, p, grid, smem_bytes, s);
-    if (M <= 8) return launch_gemv_tc_i8_tok<TYPE, T, 8>(map_w, map_x, p, grid, smem_bytes, s);
-    return launch_gemv_tc_i8_tok<TYPE, T, 16>(map_w, map_x, p, grid, smem_bytes, s);
+    if (M <= 4) return launch_gemv_tc_i8_tok<TYPE, T, 4>(map_w, map_x, p, grid, smem_bytes, s, true);
+    if (M <= 8) return launch_gemv_tc_i8_tok<TYPE, T, 8>(map_w, map_x, p, grid, smem_bytes, s, true);
+    return launch_gemv_tc_i8_tok<TYPE, T, 16>(map_w, map_x, p, grid, smem_bytes, s, true);
 }
 
 // ---------------------------------------------------------------------------------------------
