@@ -1030,6 +1030,9 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
                 has_row[u] = r_in[u] < rows_here;
                 acc[u] = 0.0f;
             }
+            // a warp none of whose lanes has a row in this pass (the short last stage of a CTA's range) leaves the
+            // issue slots to the warps that have one
+            if (!__any_sync(0xffffffffu, has_row[0])) continue;
 #pragma unroll
             for (int j = 0; j < NREG; ++j) {
                 const int item = item0 + j * item_step;
