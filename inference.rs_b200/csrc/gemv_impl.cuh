@@ -362,25 +362,24 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
 #pragma unroll
                 for (int j = 0; j < 8; ++j) q[j] = (int)roundf(v[j] * id);
             } else {
-                // roundf(x / d) without eight IEEE divisions: one exact reciprocal, a residual-corrected quotient
-                // (within an ulp of the true one: under 4e-6 for |q| < 128), and the exact division only where that
-                // quotient lies within 1e-4 of a rounding boundary (one value in 5000), so the result is always the one
-                // the quantize launcher computes
-                // (the reciprocal only seeds the quotient, so the approximate one does; |q| <= 127.5, so the magic-number
-                // rounding applies)
+                // roundf(x / d) without eight IEEE divisions. x * (1 / d) + 1.5 * 2^23 leaves the nearest integer in the
+                // low mantissa bits (its low byte is the quant as stored) and, minus the constant, as a float; the exact
+                // remainder x - d * q then tells how far the true quotient is from q. Where that is under 0.4999 the
+                // correctly rounded quotient (within 4e-6 of the true one for |q| < 128) rounds to q as well; the others
+                // (one value in 5000, and every exact tie) are decided by the division itself, out of line.
                 const float rcp = amax == 0.0f ? 0.0f : __frcp_rn(d);
+                const float lim = 0.4999f * d;
                 unsigned near_half = 0u;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const float q0 = v[j] * rcp;
-                    const float q1 = fmaf(fmaf(-d, q0, v[j]), rcp, q0);
-                    const float qr = (q1 + 12582912.0f) - 12582912.0f;  // nearest integer
-                    q[j] = amax == 0.0f ? 0 : (int)qr;
-                    near_half |= (fabsf(q1 - qr) > 0.4999f) ? (1u << j) : 0u;
+                    const float t = fmaf(v[j], rcp, 12582912.0f);
+                    const float rem = fmaf(-d, t - 12582912.0f, v[j]);
+                    q[j] = (int)__float_as_uint(t);  // only the low byte is used
+                    near_half |= (fabsf(rem) > lim) ? (1u << j) : 0u;
                 }
-                // decided by the division itself, out of line: a lane rarely flags more than one of its values, so the
-                // warp goes round once per flagged value of its worst lane, not once per position any lane flagged
-                // (the block's warps meet at a barrier after this, so the slowest warp sets the time)
+                // a lane rarely flags more than one of its values, so the warp goes round once per flagged value of its
+                // worst lane, not once per position any lane flagged (the block's warps meet at a barrier after this,
+                // so the slowest warp sets the time)
                 while (near_half != 0u) {
                     const int j = __ffs(near_half) - 1;
                     near_half &= near_half - 1u;
@@ -394,15 +393,12 @@ __device__ __forceinline__ void stage_acts_raw(uint8_t* acts, const src_t* x, in
             }
             d_used = __half2float(__float2half_rn(d));
         }
-        int sum = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) sum += q[j];
+        // the low bytes four to a word, and the chunk's sum from the bytes as stored
+        const uint32_t w0 = __byte_perm(__byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040), 0x5410);
+        const uint32_t w1 = __byte_perm(__byte_perm((uint32_t)q[4], (uint32_t)q[5], 0x0040), __byte_perm((uint32_t)q[6], (uint32_t)q[7], 0x0040), 0x5410);
+        int sum = __dp4a((int)w0, 0x01010101, __dp4a((int)w1, 0x01010101, 0));
         sum += __shfl_xor_sync(gmask, sum, 1);
         sum += __shfl_xor_sync(gmask, sum, 2);
-        const uint32_t w0 = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) |
-                            ((uint32_t)(q[3] & 0xff) << 24);
-        const uint32_t w1 = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) |
-                            ((uint32_t)(q[7] & 0xff) << 24);
         if (!valid) continue;
         uint8_t* rec = acts + ((size_t)b * nrec + (c >> 3)) * ACT_REC_BYTES;
         const int h = (c >> 2) & 1;
