@@ -986,6 +986,7 @@ struct GemvGroupParams {
     int row_align[GEMV_GROUP_MAX];
     int units_per_cta[GEMV_GROUP_MAX];
     int units_extra[GEMV_GROUP_MAX];
+    int cta_shift[GEMV_GROUP_MAX];  // matrix m's partition starts at this CTA, so that each matrix's extra units go to other CTAs
     int nmat;
     const void* act;  // one raw activation row of K values
     int K;
@@ -1000,6 +1001,8 @@ struct GemvGroupParams {
 
 // rows [row0, row1) of matrix m that CTA `cta` owns
 __device__ __forceinline__ void group_rows(const GemvGroupParams& p, int m, int cta, int& row0, int& row1) {
+    cta -= p.cta_shift[m];
+    if (cta < 0) cta += (int)gridDim.x;
     const int unit0 = cta * p.units_per_cta[m] + min(cta, p.units_extra[m]);
     row0 = unit0 * p.row_align[m];
     row1 = (unit0 + p.units_per_cta[m] + (cta < p.units_extra[m] ? 1 : 0)) * p.row_align[m];
@@ -1394,7 +1397,7 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w, i
     // fused exchange (out_piece_rows > 1): every CTA's row range is whole 8-byte pieces of the output, and the CTA keeps
     // its outputs in shared memory until it exchanges them
     if (out_piece_rows > 1) p.row_align = p.row_align * out_piece_rows / gcd_int(p.row_align, out_piece_rows);
-    const long long units = (N + p.row_align - 1) / p.row_align;
+    long long units = (N + p.row_align - 1) / p.row_align;
     long long grid = rt.sm_count;
     if (grid > units) grid = units;
     if (grid < 1) grid = 1;
@@ -1468,6 +1471,19 @@ static inline GemvPlan plan_gemv(int type, int K, int N, int B, const void* w, i
     if (S < 2) return plan;  // does not fit: simple kernel
     p.nstages = S;
     R = p.rows_per_stage;
+    // A CTA with several stages of rows gets them in whole stages: a ragged last stage costs a CTA a full turn of the
+    // stage loop for a few rows (twice in a grouped launch of two such matrices), which is more than the extra stage
+    // that some CTAs then have over the others.
+    // Only where few CTAs end up with the extra stage (they then draw more than their share of HBM): with 3 or 4 stages
+    // each for half of the CTAs (Q6_K 14336 x 4096) it is slower. And only for short launches: over the 27 stages per CTA
+    // of an output head the ragged stage is amortised, and a dozen CTAs left alone with a 100 KB stage cost 2 us.
+    if (out_piece_rows == 1 && (long long)N / R >= 2 * grid) {
+        const long long stages = ((long long)N + R - 1) / R;
+        if (stages % grid <= grid / 4 && stages / grid < 8) {
+            p.row_align = R;
+            units = stages;
+        }
+    }
     p.ar_offset = (int)plan.smem;
     plan.smem += ar_bytes;
     plan.grid = (int)grid;
@@ -1657,10 +1673,13 @@ static inline int launch_gemv_group(int nmat, const int* types, const void* cons
         if (one.p.stage_bytes > max_stage) max_stage = one.p.stage_bytes;
         if (one.p.rows_per_stage > max_R) max_R = one.p.rows_per_stage;
     }
+    int shift = 0;
     for (int m = 0; m < nmat; ++m) {
         const long long units = (p.N[m] + p.row_align[m] - 1) / p.row_align[m];
         p.units_per_cta[m] = (int)(units / grid);
         p.units_extra[m] = (int)(units % grid);
+        p.cta_shift[m] = exchange ? 0 : shift;  // (the first matrix stays in place: the L2 prefetch of a successor assumes it)
+        shift = (shift + p.units_extra[m]) % grid;
     }
     p.warps_per_row = wpr;
     p.items_per_lane = ipl;
