@@ -1019,29 +1019,28 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
     if constexpr (NREG > 0) {
         // two rows per warp in flight, computed unconditionally on clamped addresses and masked (see gemv_staged_kernel)
         constexpr int U = NREG == 1 ? 2 : 1;
-        for (int pass0 = 0; pass0 < rows_here; pass0 += U * rows_per_pass) {
-            int r_in[U];
-            bool has_row[U];
-            float acc[U];
+        // one turn for UU rows per warp: rows pass0 + my_slot + u * rows_per_pass
+        auto turn = [&](auto uu_tag, int pass0) {
+            constexpr int UU = decltype(uu_tag)::value;
+            int r_in[UU];
+            bool has_row[UU];
+            float acc[UU];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
+            for (int u = 0; u < UU; ++u) {
                 r_in[u] = pass0 + my_slot + u * rows_per_pass;
                 has_row[u] = r_in[u] < rows_here;
                 acc[u] = 0.0f;
             }
-            // a warp none of whose lanes has a row in this pass (the short last stage of a CTA's range) leaves the
-            // issue slots to the warps that have one
-            if (!__any_sync(0xffffffffu, has_row[0])) continue;
 #pragma unroll
             for (int j = 0; j < NREG; ++j) {
                 const int item = item0 + j * item_step;
                 const bool item_ok = item < items;
                 const int item_c = item_ok ? item : 0;
-                Weights<TYPE> W[U];
+                Weights<TYPE> W[UU];
 #pragma unroll
-                for (int u = 0; u < U; ++u) W[u].load(st + (uint32_t)(has_row[u] ? r_in[u] : 0) * (uint32_t)row_bytes, item_c);
+                for (int u = 0; u < UU; ++u) W[u].load(st + (uint32_t)(has_row[u] ? r_in[u] : 0) * (uint32_t)row_bytes, item_c);
 #pragma unroll
-                for (int u = 0; u < U; ++u) {
+                for (int u = 0; u < UU; ++u) {
                     const float d = dot(W[u], areg[j]);
                     acc[u] += (alive && has_row[u] && item_ok) ? d : 0.0f;
                 }
@@ -1050,18 +1049,18 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
 #pragma unroll
                 for (int m = 16; m > 0; m >>= 1) {
 #pragma unroll
-                    for (int u = 0; u < U; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
+                    for (int u = 0; u < UU; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
                 }
             } else {
 #pragma unroll
                 for (int m = 8; m > 0; m >>= 1)
                     if (m < islots) {
 #pragma unroll
-                        for (int u = 0; u < U; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
+                        for (int u = 0; u < UU; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], m);
                     }
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
+            for (int u = 0; u < UU; ++u) {
                 if (lane_i == 0 && has_row[u]) {
                     if (WPR == 1) {
                         dst[rbase + r_in[u]] = from_float<dst_t>(acc[u]);
@@ -1080,6 +1079,15 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
                     }
                 }
             }
+        };
+        for (int pass0 = 0; pass0 < rows_here; pass0 += U * rows_per_pass) {
+            // a warp none of whose lanes has a row in this pass (the short last stage of a CTA's range) leaves the
+            // issue slots to the warps that have one; a warp without a second row takes the turn for one row
+            if (!__any_sync(0xffffffffu, pass0 + my_slot < rows_here)) continue;
+            if (U == 2 && !__any_sync(0xffffffffu, pass0 + my_slot + rows_per_pass < rows_here))
+                turn(std::integral_constant<int, 1>{}, pass0);
+            else
+                turn(std::integral_constant<int, U>{}, pass0);
         }
     } else {
         for (int pass0 = 0; pass0 < rows_here; pass0 += rows_per_pass) {
