@@ -1010,7 +1010,7 @@ __device__ __forceinline__ void group_rows(const GemvGroupParams& p, int m, int 
     if (row1 < row0) row1 = row0;
 }
 
-template <int TYPE, typename dst_t, int NREG>
+template <int TYPE, typename dst_t, int NREG, bool ONE_ROW_TURNS>
 __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint32_t st, int row_bytes, int rows_here, int rbase,
                                                  int my_slot, int rows_per_pass, int item0, int item_step, int items, int islots,
                                                  int lane_i, int WPR, int wslice, int IPL, uint32_t acts_addr,
@@ -1082,9 +1082,11 @@ __device__ __forceinline__ void group_stage_rows(const GemvGroupParams& p, uint3
         };
         for (int pass0 = 0; pass0 < rows_here; pass0 += U * rows_per_pass) {
             // a warp none of whose lanes has a row in this pass (the short last stage of a CTA's range) leaves the
-            // issue slots to the warps that have one; a warp without a second row takes the turn for one row
+            // issue slots to the warps that have one. A warp without a second row takes the turn for one row where that
+            // saves the most, on Q6_K rows: a second copy of the loop body for every type and in the variant with the
+            // fused exchange as well made the tensor-parallel chain, where the two variants alternate, 7 % slower.
             if (!__any_sync(0xffffffffu, pass0 + my_slot < rows_here)) continue;
-            if (U == 2 && !__any_sync(0xffffffffu, pass0 + my_slot + rows_per_pass < rows_here))
+            if (U == 2 && ONE_ROW_TURNS && TYPE == TYPE_Q6_K && !__any_sync(0xffffffffu, pass0 + my_slot + rows_per_pass < rows_here))
                 turn(std::integral_constant<int, 1>{}, pass0);
             else
                 turn(std::integral_constant<int, U>{}, pass0);
@@ -1275,13 +1277,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_group_kernel(const GemvG
             float* part_base = partial + (size_t)s * RMAX * WPR;
             int* cnt_base = counters + s * RMAX;
             if (mtype == TYPE_Q4_K)
-                group_stage_rows<TYPE_Q4_K, dst_t, NREG>(p, st, p.row_bytes[m], rows_here, r, my_slot, rows_per_pass, item0, item_step,
+                group_stage_rows<TYPE_Q4_K, dst_t, NREG, !AR>(p, st, p.row_bytes[m], rows_here, r, my_slot, rows_per_pass, item0, item_step,
                                                          items, islots, lane_i, WPR, wslice, IPL, acts_addr, areg, part_base, cnt_base, dst, alive);
             else if (mtype == TYPE_Q6_K)
-                group_stage_rows<TYPE_Q6_K, dst_t, NREG>(p, st, p.row_bytes[m], rows_here, r, my_slot, rows_per_pass, item0, item_step,
+                group_stage_rows<TYPE_Q6_K, dst_t, NREG, !AR>(p, st, p.row_bytes[m], rows_here, r, my_slot, rows_per_pass, item0, item_step,
                                                          items, islots, lane_i, WPR, wslice, IPL, acts_addr, areg, part_base, cnt_base, dst, alive);
             else
-                group_stage_rows<TYPE_Q8_0, dst_t, NREG>(p, st, p.row_bytes[m], rows_here, r, my_slot, rows_per_pass, item0, item_step,
+                group_stage_rows<TYPE_Q8_0, dst_t, NREG, !AR>(p, st, p.row_bytes[m], rows_here, r, my_slot, rows_per_pass, item0, item_step,
                                                          items, islots, lane_i, WPR, wslice, IPL, acts_addr, areg, part_base, cnt_base, dst, alive);
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
