@@ -75,6 +75,23 @@ def test_gemv_plans_respect_hardware_limits(tag, k, n, b):
     assert 1 <= plan["grid"] <= 148
 
 
+def test_short_launches_are_split_in_whole_stages_where_few_ctas_get_the_remainder():
+    """The row partition's unit: a whole ring stage for ffn_gate / ffn_up of the 8B model (3 stages per CTA, 4 CTAs with a
+    fourth), the 16-byte-aligned unit where half of the CTAs would get the extra stage (ffn_down) and for long launches
+    (the output head), where a ragged last stage is amortised."""
+    from inference_rs_b200 import ops
+    if ops.get_option("sm_count") != 148:
+        pytest.skip("the expectations are for 148 SMs")
+    gate = ops.gemv_plan(pkg.GgmlDType.Q4K, 4096, 14336, 1)
+    assert gate["staged"] and gate["row_align"] == gate["rows_per_stage"]
+    down = ops.gemv_plan(pkg.GgmlDType.Q6K, 14336, 4096, 1)
+    assert down["staged"] and down["row_align"] < down["rows_per_stage"]
+    head = ops.gemv_plan(pkg.GgmlDType.Q6K, 4096, 128256, 1)
+    assert head["staged"] and head["row_align"] < head["rows_per_stage"]
+    small = ops.gemv_plan(pkg.GgmlDType.Q4K, 4096, 4096, 1)
+    assert small["staged"] and small["row_align"] < small["rows_per_stage"]
+
+
 def test_trace_buffer_needs_a_trace_build():
     """The launch timelines are a build option; the default library says so instead of silently ignoring the buffer."""
     import ctypes
