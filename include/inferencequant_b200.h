@@ -371,8 +371,9 @@ int b200q_dequantize(int type, int elem, const void* w, void* out, long long nro
 int b200q_get_rows(int type, int elem, const void* w, const int32_t* ids, void* out, long long n_ids, int K, long long nrows_w,
                    void* stream);
 
-/* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, row alignment,
- *        item slots per lane, register-resident slots} */
+/* out = {staged kernel?, grid, dynamic smem bytes, stages, rows per stage, warps per row, stage bytes, rows per unit of
+ *        the CTAs' row partition (the 16-byte alignment unit, or a whole stage for short launches), item slots per lane,
+ *        register-resident slots} */
 int b200q_gemv_plan(int type, int K, int N, int b_size, int out[10]);
 
 #ifdef __cplusplus
