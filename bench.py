@@ -1010,7 +1010,7 @@ def main():
                      "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": dom_us, "algorithmic_bytes": dom_bytes, "traffic": dom_traffic,
                      "traffic_note": "dram read + write of one launch under ncu with the L2 prefetch of the next matrix off; with it on, "
-                                     "a launch also fetches up to 148 x 256 KB of the NEXT launch's rows, which that launch then "
+                                     "a launch also fetches up to 148 x l2_prefetch_bytes of the NEXT launch's rows, which that launch then "
                                      "does not read from DRAM: over a layer's four launches the DRAM traffic measured in the chain "
                                      "equals the algorithmic bytes (profiles/gemv_group_q4k_gate_up.txt)"},
         "clocks": clocks.summary(),
