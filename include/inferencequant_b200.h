@@ -266,8 +266,9 @@ int b200q_gemv(int type, int elem, const void* w, const void* x, void* dst, int 
  * reads `next_w`" (GGUF type next_type, next_N rows of next_K values). Every decode GEMV launch on `w` - through part 1's
  * launch_mmvq_gguf_*_plain symbols as well as b200q_gemv / b200q_gemv_group (keyed by the group's last matrix) - then
  * has each CTA, once its last weight copy is issued, ask L2 (cp.async.bulk.prefetch.L2) for the first
- * "l2_prefetch_bytes" (option, default 64 KB) of the row range the same CTA of the next launch will stream first, so
- * that HBM keeps streaming through the tail of one launch and the gap before the next. A decoder's projections run in
+ * "l2_prefetch_bytes" (option; default 64 KB with the "pdl" option on, 256 KB without; -1 restores that default) of
+ * the row range the same CTA of the next launch will stream first, so that HBM keeps streaming through the tail of one
+ * launch and the gap before the next. A decoder's projections run in
  * a fixed order, so the host registers the chain layer by layer; the hint only moves bytes into L2 early and never
  * changes a result. next_w == NULL forgets `w`; b200q_clear_weight_successors forgets everything (call it before the
  * weights are freed). The table is read-mostly: setting it while other threads launch is safe (a lock), but a launch

@@ -59,8 +59,8 @@ int b200q_set_option(const char* name, int value) {
     } else if (!std::strcmp(name, "gemm_direct")) {
         rt.gemm_direct = value ? 1 : 0;
     } else if (!std::strcmp(name, "l2_prefetch_bytes")) {
-        if (value < 0) return set_error(B200Q_ERR_INVALID, "l2_prefetch_bytes must be >= 0");
-        rt.l2_prefetch_bytes = value & ~15;
+        if (value < -1) return set_error(B200Q_ERR_INVALID, "l2_prefetch_bytes must be >= 0, or -1 for the default of the launch mode");
+        rt.l2_prefetch_bytes = value < 0 ? -1 : (value & ~15);
     } else if (!std::strcmp(name, "gemv_one_kernel")) {
         rt.gemv_one_kernel = value ? 1 : 0;
     } else if (!std::strcmp(name, "gemv_passes")) {
@@ -89,7 +89,7 @@ int b200q_get_option(const char* name, int* value) {
     else if (!std::strcmp(name, "gemv_pass_limit_bytes")) *value = rt.gemv_pass_limit;
     else if (!std::strcmp(name, "gemm_direct")) *value = rt.gemm_direct;
     else if (!std::strcmp(name, "tc_ksplit")) *value = rt.tc_ksplit;
-    else if (!std::strcmp(name, "l2_prefetch_bytes")) *value = rt.l2_prefetch_bytes;
+    else if (!std::strcmp(name, "l2_prefetch_bytes")) *value = l2_prefetch_bytes_effective(rt);
     else if (!std::strcmp(name, "sm_count")) *value = rt.sm_count;
     else if (!std::strcmp(name, "smem_optin")) *value = rt.smem_optin;
     else return set_error(B200Q_ERR_INVALID, "unknown option");

@@ -1526,7 +1526,8 @@ static inline NextPrefetch plan_next_prefetch(const void* w) {
     NextPrefetch n{};
     const RuntimeInfo& rt = runtime_info();
     WeightSuccessor succ;
-    if (rt.l2_prefetch_bytes < 16 || !find_weight_successor(w, &succ)) return n;
+    const int prefetch_bytes = l2_prefetch_bytes_effective(rt);
+    if (prefetch_bytes < 16 || !find_weight_successor(w, &succ)) return n;
     if (type_block_bytes(succ.type) == 0 || succ.K <= 0 || succ.N <= 0 || succ.K % type_block_elems(succ.type) != 0) return n;
     const GemvPlan next = plan_gemv(succ.type, succ.K, succ.N, 1, succ.w);
     if (!next.staged) return n;
@@ -1536,7 +1537,7 @@ static inline NextPrefetch plan_next_prefetch(const void* w) {
     n.units_per_cta = next.p.units_per_cta;
     n.units_extra = next.p.units_extra;
     n.grid = next.grid;
-    n.bytes = rt.l2_prefetch_bytes & ~15;
+    n.bytes = prefetch_bytes & ~15;
     return n;
 }
 

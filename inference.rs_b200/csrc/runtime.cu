@@ -11,7 +11,7 @@ namespace b200q {
 
 __device__ unsigned int g_status_word[4] = {0, 0, 0, 0};
 
-static RuntimeInfo g_rt = {0, 0, 0, 0, 0, 40 * 1024, 0, 1, 1, 1, 0, 48 * 1024, 64 * 1024};
+static RuntimeInfo g_rt = {0, 0, 0, 0, 0, 40 * 1024, 0, 1, 1, 1, 0, 48 * 1024, -1};
 static std::atomic<int> g_launch_status{0};
 
 static void query_device() {

@@ -27,8 +27,15 @@ struct RuntimeInfo {
                            // between fewer kernels (1; 0 = the per-type kernels)
     int gemv_passes;       // decode GEMV planner: passes of all warps a stage holds (0 = the planner's own choice; 1 or 2)
     int gemv_pass_limit;   // decode GEMV planner: bytes one pass of all warps may cover before rows get more warps
-    int l2_prefetch_bytes; // decode GEMV: bytes of the registered successor matrix each CTA asks L2 to fetch (0 = off)
+    int l2_prefetch_bytes; // decode GEMV: bytes of the registered successor matrix each CTA asks L2 to fetch (0 = off;
+                           // -1 = by the launch mode, see l2_prefetch_bytes_effective)
 };
+
+// With programmatic dependent launch the next launch's own CTAs start their weight stream while this launch ends, and a
+// large prefetch competes with them: 64 KB measured best there, 256 KB without it.
+inline int l2_prefetch_bytes_effective(const RuntimeInfo& rt) {
+    return rt.l2_prefetch_bytes >= 0 ? rt.l2_prefetch_bytes : (rt.use_pdl ? 64 * 1024 : 256 * 1024);
+}
 
 // "After a launch on weight matrix w, the next launch on this stream will read matrix next_w": registered once by the
 // host when it loads a model (the order of a decoder's projections is static), read by every GEMV launch. A CTA that

@@ -55,6 +55,15 @@ def test_options_and_errors_round_trip():
     with pytest.raises(kl.KernelLibraryError, match="unknown option"):
         ops.set_option("no_such_option", 1)
     assert ops.get_option("sm_count") > 0
+    # the L2 prefetch size follows the launch mode until it is set, and again after -1
+    assert ops.get_option("l2_prefetch_bytes") == 256 * 1024
+    ops.set_option("pdl", 1)
+    assert ops.get_option("l2_prefetch_bytes") == 64 * 1024
+    ops.set_option("l2_prefetch_bytes", 4100)
+    assert ops.get_option("l2_prefetch_bytes") == 4096
+    ops.set_option("l2_prefetch_bytes", -1)
+    ops.set_option("pdl", 0)
+    assert ops.get_option("l2_prefetch_bytes") == 256 * 1024
 
 
 @pytest.mark.parametrize("tag,k,n,b", [("Q4K", 4096, 4096, 1), ("Q6K", 14336, 4096, 4), ("Q8_0", 4096, 128256, 8),
